@@ -1,0 +1,164 @@
+/*
+ * logos_attn.h -- C ABI of the B200 (sm_100a) attention engine for LOGOS.
+ *
+ * Scope: the multi-head-attention hot path of the LOGOS model -- causal
+ * prefill attention, Shunyam window(+landmark) attention, the Nikhilam INT8
+ * KV cache (quantize, append, decode) and the Navier-Stokes Q-advection /
+ * V-diffusion prologue.  Each entry point names the reference interface it
+ * stands in for (paths relative to the LOGOS source tree).
+ *
+ * Conventions (they follow the reference call site, cuda/ModelGPU.cu:892-988):
+ *  - all tensor pointers are DEVICE pointers unless the name ends in _host;
+ *  - the caller owns every buffer; the engine never frees or keeps them;
+ *  - work is issued on the context's stream (default: the legacy default
+ *    stream, as in the reference) and is NOT synchronised before return,
+ *    except for the *_host entry points which return finished results;
+ *  - every function returns a logos_status; no C++ exception crosses the ABI;
+ *  - hot calls never allocate: scratch comes from the context's workspace
+ *    (logos_ctx_reserve / logos_ctx_set_workspace).
+ * There is no CPU fallback: without a CUDA device the context cannot be
+ * created and every call fails with LOGOS_ERR_NO_DEVICE.
+ */
+#ifndef LOGOS_ATTN_H
+#define LOGOS_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LOGOS_ATTN_ABI_VERSION 1
+
+typedef struct logos_ctx logos_ctx;
+
+typedef enum {
+    LOGOS_OK = 0,
+    LOGOS_ERR_INVALID_ARG = 1,   /* null pointer, non-positive extent, bad enum      */
+    LOGOS_ERR_UNSUPPORTED = 2,   /* valid request the engine does not implement      */
+    LOGOS_ERR_WORKSPACE = 3,     /* context workspace too small for this call        */
+    LOGOS_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed             */
+    LOGOS_ERR_NO_DEVICE = 5,     /* no usable sm_100 device                          */
+    LOGOS_ERR_ALIGNMENT = 6      /* pointer or extent breaks a 16-byte requirement   */
+} logos_status;
+
+typedef enum { LOGOS_F32 = 0, LOGOS_BF16 = 1, LOGOS_F16 = 2 } logos_dtype;
+
+/* V-diffusion variant.  CAUSAL is the GPU model's one-sided stencil
+ * (cuda/ModelGPU.cu:463-471); CENTRAL is the CPU model's two-sided stencil with
+ * mirror boundaries (include/Attention.hpp:173-181). */
+typedef enum { LOGOS_DIFFUSE_NONE = 0, LOGOS_DIFFUSE_CAUSAL = 1, LOGOS_DIFFUSE_CENTRAL = 2 } logos_diffuse;
+
+/* The attention-related fields of GPUPhysicsConfig (cuda/ModelGPU.cuh:67-82)
+ * and of AttentionHead (include/Attention.hpp:205-214). */
+typedef struct {
+    float scale;        /* score multiplier, 1/sqrt(DH) at the reference call site        */
+    int   causal;       /* 1: key j > query i is masked                                    */
+    int   window;       /* Shunyam window; the rule is active iff window > 0 && seq > window
+                           (include/Attention.hpp:228, cuda/ModelGPU.cu:966)               */
+    int   stride;       /* Shunyam landmark stride (every j % stride == 0 is visible);
+                           <= 0 means no landmarks, a pure sliding window                  */
+    float ns_eta;       /* Q-advection strength, Q_adv[i] = Q[i] + eta (Q[i] - Q[i-1])     */
+    float ns_nu;        /* V-diffusion viscosity (used when diffuse_mode != NONE)          */
+    float ns_alpha;     /* out = (1-alpha) standard + alpha NS; 1 = the GPU model, 0 = off */
+    int   diffuse_mode; /* logos_diffuse                                                   */
+} logos_attn_params;
+
+/* ---- context ------------------------------------------------------------ */
+
+int logos_abi_version(void);
+const char* logos_status_string(int status);
+
+/* Binds to CUDA device `device` (must be compute capability 10.x). */
+int logos_ctx_create(int device, logos_ctx** out);
+int logos_ctx_destroy(logos_ctx* ctx);
+/* cudaStream_t as void*; NULL selects the legacy default stream (reference behaviour:
+ * every launch in cuda/ModelGPU.cu and cuda/VedicGEMM.cu is on stream 0). */
+int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream);
+/* Grows the context-owned workspace to at least `bytes` (cudaMalloc; not a hot call). */
+int logos_ctx_reserve(logos_ctx* ctx, size_t bytes);
+/* Uses caller memory as workspace instead (256-byte aligned device memory). */
+int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes);
+/* Text of the last failure on this context (owned by the context). */
+const char* logos_last_error(const logos_ctx* ctx);
+
+/* ---- attention ---------------------------------------------------------- */
+
+/* Stand-in for cuda_flash_attention_fwd (cuda/VedicGEMM.cuh:236-243,
+ * cuda/VedicGEMM.cu:1065-1104): one head, fp32 row-major [seq x DH] device
+ * tensors, DH <= 128.  attn_ptr must be NULL (the reference forward never passes
+ * anything else, cuda/ModelGPU.cu:935,962); non-NULL returns LOGOS_ERR_UNSUPPORTED.
+ * `shunyam` is the caller's already-evaluated "rule active" flag, as in the reference. */
+int logos_flash_attention_fwd_f32(logos_ctx* ctx, const float* Q, const float* K, const float* V,
+                                  float* out, float* attn_ptr, int seq, int DH, float scale,
+                                  int causal, int shunyam, int window, int stride);
+
+/* Batched attention over B*H independent heads with the Navier-Stokes prologue
+ * fused in.  Replaces, per head, ns_advect_kernel + ns_diffuse_kernel
+ * (cuda/ModelGPU.cu:443-471) + cuda_flash_attention_fwd, and on the CPU side the
+ * attention part of AttentionHead::forward (include/Attention.hpp:225-265).
+ * Q,K,V: [B][H][S][DH] contiguous, dtype `in_dtype`; O: same shape, dtype `out_dtype`
+ * (the input dtype or LOGOS_F32). */
+int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                        const void* V, void* O, int B, int H, int S, int DH,
+                        const logos_attn_params* params);
+size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
+
+/* ---- Nikhilam INT8 KV cache --------------------------------------------- */
+
+/* Stand-in for nikhilam_compress (cuda/ModelGPU.cu:357-386: absmax_kernel,
+ * scale = (absmax + 1e-8) / 127.5, nikhilam_quantize_kernel), batched over
+ * n_tensors tensors of `elems` values each with ONE scale per tensor and no host
+ * round-trip.  Tensor t is read at src + t*src_stride elements and written at
+ * dst + t*dst_stride bytes; scales[t] receives the fp32 scale.  Bytes and scales
+ * are bit-identical to the reference arithmetic (IEEE division, round-half-even). */
+int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,
+                      int8_t* dst, int64_t dst_stride, float* scales, int n_tensors,
+                      int64_t elems);
+
+/* Stand-in for nikhilam_decompress / nikhilam_dequantize_kernel
+ * (cuda/ModelGPU.cu:343-351,388-395): dst = (float)q * scale. */
+int logos_kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const float* scales,
+                        float* dst, int64_t dst_stride, int n_tensors, int64_t elems);
+
+/* Quantize-on-append: writes the new token's K and V rows ([B][H][DH], dtype
+ * `dtype`) into the caches ([B][H][S_max][DH] int8) at row pos[b], using the
+ * scales already stored for each (b,h) tensor and saturating at +-127 -- the
+ * contract of nikhilam_quantize_kernel (cuda/ModelGPU.cu:329-340) applied to one
+ * row.  The reference has no incremental path (cuda/train_gpu.cu:2037-2046). */
+int logos_kv_append(logos_ctx* ctx, int dtype, const void* k_new, const void* v_new,
+                    int8_t* k_cache, int8_t* v_cache, const float* k_scale, const float* v_scale,
+                    const int32_t* pos, int B, int H, int S_max, int DH);
+
+/* Decode attention straight from the INT8 cache: for every (b,h) the query is the
+ * token at position len[b]-1 (already appended), K/V rows [0,len[b]) are streamed
+ * as int8, dequantized in registers with their per-tensor scales, and the last
+ * row of the attention defined by `params` is produced.  q, q_prev: FP16
+ * [B][H][DH] (q_prev = the previous token's query, needed by the advection term;
+ * may be NULL when ns_eta == 0).  out: FP32 [B][H][DH].  Replaces the full
+ * re-forward per generated token of cuda/train_gpu.cu:2037-2046; numerically it
+ * is nikhilam_decompress + ns kernels + the last row of cuda_flash_attention_fwd. */
+int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
+                      const int8_t* v_cache, const float* k_scale, const float* v_scale,
+                      const int32_t* len, int B, int H, int S_max, int DH,
+                      const logos_attn_params* params, float* out);
+size_t logos_decode_workspace_bytes(int B, int H, int S_max, int DH);
+
+/* One whole decode step with HOST buffers for the per-step data: copies q, q_prev,
+ * k_new, v_new (FP16 [B][H][DH]) and len (int32 [B], the length AFTER the append)
+ * to the device, appends at row len[b]-1, runs logos_decode_int8 and copies the
+ * FP32 result back to out_host; returns when out_host is complete.  The caches
+ * and scales stay resident on the device (they are engine state, like HeadCache in
+ * cuda/ModelGPU.cuh:42-49).  Staging memory comes from the workspace. */
+int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* q_prev_host,
+                                const void* k_new_host, const void* v_new_host,
+                                int8_t* k_cache, int8_t* v_cache, const float* k_scale,
+                                const float* v_scale, const int32_t* len_host, int B, int H,
+                                int S_max, int DH, const logos_attn_params* params,
+                                float* out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOGOS_ATTN_H */

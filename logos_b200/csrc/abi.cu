@@ -1,0 +1,244 @@
+// abi.cu -- the extern "C" surface declared in include/logos_attn.h: context
+// management, argument checks and dispatch to the kernels.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kAbsmaxSlots = 65536;
+
+bool params_ok(const logos_attn_params* p) {
+    return p && p->diffuse_mode >= LOGOS_DIFFUSE_NONE && p->diffuse_mode <= LOGOS_DIFFUSE_CENTRAL &&
+           p->ns_alpha >= 0.0f && p->ns_alpha <= 1.0f && p->window >= 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int logos_abi_version(void) { return LOGOS_ATTN_ABI_VERSION; }
+
+const char* logos_status_string(int status) {
+    switch (status) {
+        case LOGOS_OK: return "ok";
+        case LOGOS_ERR_INVALID_ARG: return "invalid argument";
+        case LOGOS_ERR_UNSUPPORTED: return "unsupported request";
+        case LOGOS_ERR_WORKSPACE: return "workspace too small";
+        case LOGOS_ERR_CUDA: return "CUDA error";
+        case LOGOS_ERR_NO_DEVICE: return "no sm_100 CUDA device";
+        case LOGOS_ERR_ALIGNMENT: return "misaligned pointer or extent";
+    }
+    return "unknown status";
+}
+
+int logos_ctx_create(int device, logos_ctx** out) {
+    if (!out) return LOGOS_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+        cudaGetLastError();
+        return LOGOS_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count) return LOGOS_ERR_INVALID_ARG;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return LOGOS_ERR_CUDA;
+    if (prop.major != 10) return LOGOS_ERR_NO_DEVICE;  // kernels are built for sm_100a only
+    if (cudaSetDevice(device) != cudaSuccess) return LOGOS_ERR_CUDA;
+    logos_ctx* ctx = new (std::nothrow) logos_ctx();
+    if (!ctx) return LOGOS_ERR_CUDA;
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(&ctx->absmax_scratch, sizeof(float) * kAbsmaxSlots) != cudaSuccess) {
+        delete ctx;
+        return LOGOS_ERR_CUDA;
+    }
+    ctx->absmax_slots = kAbsmaxSlots;
+    *out = ctx;
+    return LOGOS_OK;
+}
+
+int logos_ctx_destroy(logos_ctx* ctx) {
+    if (!ctx) return LOGOS_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->absmax_scratch) cudaFree(ctx->absmax_scratch);
+    delete ctx;
+    return LOGOS_OK;
+}
+
+int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    return LOGOS_OK;
+}
+
+int logos_ctx_reserve(logos_ctx* ctx, size_t bytes) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (ctx->workspace && ctx->workspace_bytes >= bytes) return LOGOS_OK;
+    LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    // Work queued on the stream may still use the old block.
+    LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    ctx->owns_workspace = false;
+    void* p = nullptr;
+    LOGOS_CUDA_TRY(ctx, cudaMalloc(&p, bytes));
+    // arrival counters at the head of the workspace must start at zero
+    LOGOS_CUDA_TRY(ctx, cudaMemset(p, 0, bytes));
+    ctx->workspace = p;
+    ctx->workspace_bytes = bytes;
+    ctx->owns_workspace = true;
+    return LOGOS_OK;
+}
+
+int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes) {
+    if (!ctx || (!device_ptr && bytes)) return LOGOS_ERR_INVALID_ARG;
+    if (reinterpret_cast<uintptr_t>(device_ptr) & 255u)
+        return logos::fail(ctx, LOGOS_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
+    ctx->workspace = device_ptr;
+    ctx->workspace_bytes = bytes;
+    ctx->owns_workspace = false;
+    if (device_ptr) LOGOS_CUDA_TRY(ctx, cudaMemset(device_ptr, 0, bytes));
+    return LOGOS_OK;
+}
+
+const char* logos_last_error(const logos_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+int logos_flash_attention_fwd_f32(logos_ctx* ctx, const float* Q, const float* K, const float* V,
+                                  float* out, float* attn_ptr, int seq, int DH, float scale,
+                                  int causal, int shunyam, int window, int stride) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!Q || !K || !V || !out || seq <= 0 || DH <= 0)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "flash_attention_fwd: bad pointer or extent");
+    if (attn_ptr)
+        return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED,
+                           "flash_attention_fwd: saving the seq x seq weights is not supported");
+    if (shunyam && (window <= 0 || stride <= 0))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG,
+                           "flash_attention_fwd: shunyam needs window > 0 and stride > 0");
+    logos_attn_params p;
+    p.scale = scale;
+    p.causal = causal;
+    // The reference caller passes "shunyam && seq > window" (cuda/ModelGPU.cu:966) and the
+    // kernel re-checks seq > window (cuda/VedicGEMM.cu:990); window 0 switches the rule off.
+    p.window = shunyam ? window : 0;
+    p.stride = stride;
+    p.ns_eta = 0.0f; p.ns_nu = 0.0f; p.ns_alpha = 0.0f;
+    p.diffuse_mode = LOGOS_DIFFUSE_NONE;
+    return logos::attention_simt(ctx, LOGOS_F32, LOGOS_F32, Q, K, V, out, 1, 1, seq, DH, &p);
+}
+
+size_t logos_attention_workspace_bytes(int B, int H, int S, int DH) {
+    (void)B; (void)H; (void)S; (void)DH;
+    return 0;
+}
+
+int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                        const void* V, void* O, int B, int H, int S, int DH,
+                        const logos_attn_params* params) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!Q || !K || !V || !O || B <= 0 || H <= 0 || S <= 0 || DH <= 0)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: bad pointer or extent");
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: bad parameter block");
+    if (!logos::dtype_ok(in_dtype) || !logos::dtype_ok(out_dtype))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: unknown dtype");
+    return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+}
+
+int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,
+                      int8_t* dst, int64_t dst_stride, float* scales, int n_tensors,
+                      int64_t elems) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::kv_quantize(ctx, src_dtype, src, src_stride, dst, dst_stride, scales, n_tensors, elems);
+}
+
+int logos_kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const float* scales,
+                        float* dst, int64_t dst_stride, int n_tensors, int64_t elems) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::kv_dequantize(ctx, src, src_stride, scales, dst, dst_stride, n_tensors, elems);
+}
+
+int logos_kv_append(logos_ctx* ctx, int dtype, const void* k_new, const void* v_new,
+                    int8_t* k_cache, int8_t* v_cache, const float* k_scale, const float* v_scale,
+                    const int32_t* pos, int B, int H, int S_max, int DH) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::kv_append(ctx, dtype, k_new, v_new, k_cache, v_cache, k_scale, v_scale, pos, B, H, S_max, DH);
+}
+
+size_t logos_decode_workspace_bytes(int B, int H, int S_max, int DH) {
+    // split-K partials + arrival counters, plus staging for the *_host entry point
+    size_t stage = (size_t)(B > 0 ? B : 0) * (H > 0 ? H : 0) * (DH > 0 ? DH : 0) * (4 * 2 + 4) +
+                   (size_t)(B > 0 ? B : 0) * 8 + 1024;
+    return logos::decode_workspace_bytes(B, H, S_max, DH) + stage;
+}
+
+int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
+                      const int8_t* v_cache, const float* k_scale, const float* v_scale,
+                      const int32_t* len, int B, int H, int S_max, int DH,
+                      const logos_attn_params* params, float* out) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad parameter block");
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
+}
+
+int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* q_prev_host,
+                                const void* k_new_host, const void* v_new_host,
+                                int8_t* k_cache, int8_t* v_cache, const float* k_scale,
+                                const float* v_scale, const int32_t* len_host, int B, int H,
+                                int S_max, int DH, const logos_attn_params* params,
+                                float* out_host) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!q_host || !k_new_host || !v_new_host || !len_host || !out_host || B <= 0 || H <= 0 || DH <= 0)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: bad pointer or extent");
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: bad parameter block");
+    const size_t vec = (size_t)B * H * DH;           // elements per [B][H][DH] tensor
+    const size_t kernel_ws = logos::decode_workspace_bytes(B, H, S_max, DH);
+    const size_t need = logos_decode_workspace_bytes(B, H, S_max, DH);
+    if (!ctx->workspace || ctx->workspace_bytes < need)
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "decode_step_host: workspace of %zu bytes needed, %zu reserved",
+                           need, ctx->workspace_bytes);
+    for (int b = 0; b < B; ++b)
+        if (len_host[b] < 1 || len_host[b] > S_max)
+            return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: len[%d]=%d outside [1,%d]", b,
+                               len_host[b], S_max);
+    // staging layout behind the kernel workspace: q | q_prev | k_new | v_new (fp16), out (fp32),
+    // len | pos (int32)
+    char* base = (char*)ctx->workspace + ((kernel_ws + 255) & ~(size_t)255);
+    __half* d_q = (__half*)base;
+    __half* d_qp = d_q + vec;
+    __half* d_k = d_qp + vec;
+    __half* d_v = d_k + vec;
+    float* d_out = (float*)(d_v + vec);
+    int32_t* d_len = (int32_t*)(d_out + vec);
+    int32_t* d_pos = d_len + B;
+    cudaStream_t st = ctx->stream;
+    const size_t hb = vec * sizeof(__half);
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_q, q_host, hb, cudaMemcpyHostToDevice, st));
+    if (q_prev_host) LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_qp, q_prev_host, hb, cudaMemcpyHostToDevice, st));
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_k, k_new_host, hb, cudaMemcpyHostToDevice, st));
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, v_new_host, hb, cudaMemcpyHostToDevice, st));
+    // len and pos = len - 1 travel as one small copy
+    int32_t small[2 * 4096];
+    if (B > 4096) return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_step_host: B > 4096");
+    for (int b = 0; b < B; ++b) { small[b] = len_host[b]; small[B + b] = len_host[b] - 1; }
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_len, small, sizeof(int32_t) * 2 * B, cudaMemcpyHostToDevice, st));
+    int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_pos, B, H, S_max, DH);
+    if (rc != LOGOS_OK) return rc;
+    rc = logos::decode_int8(ctx, d_q, q_prev_host ? d_qp : nullptr, k_cache, v_cache, k_scale, v_scale, d_len, B,
+                            H, S_max, DH, params, d_out);
+    if (rc != LOGOS_OK) return rc;
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, d_out, vec * sizeof(float), cudaMemcpyDeviceToHost, st));
+    LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(st));
+    return LOGOS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+// common.cuh -- context object, error plumbing and small device helpers shared by
+// the kernels of the attention engine.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/logos_attn.h"
+
+struct logos_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    void* workspace = nullptr;        // scratch used by hot calls
+    size_t workspace_bytes = 0;
+    bool owns_workspace = false;
+    float* absmax_scratch = nullptr;  // per-tensor absmax words for kv_quantize
+    int absmax_slots = 0;
+    char err[512] = {0};
+};
+
+namespace logos {
+
+inline int fail(logos_ctx* ctx, int status, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+#define LOGOS_CUDA_TRY(ctx, expr)                                                         \
+    do {                                                                                  \
+        cudaError_t e__ = (expr);                                                         \
+        if (e__ != cudaSuccess)                                                           \
+            return ::logos::fail((ctx), LOGOS_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,   \
+                                 cudaGetErrorString(e__), __FILE__, __LINE__);            \
+    } while (0)
+
+#define LOGOS_LAUNCH_CHECK(ctx, what)                                                     \
+    do {                                                                                  \
+        cudaError_t e__ = cudaGetLastError();                                             \
+        if (e__ != cudaSuccess)                                                           \
+            return ::logos::fail((ctx), LOGOS_ERR_CUDA, "launch of %s failed: %s", what,  \
+                                 cudaGetErrorString(e__));                                \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline size_t dtype_size(int dt) { return dt == LOGOS_F32 ? 4 : 2; }
+inline bool dtype_ok(int dt) { return dt == LOGOS_F32 || dt == LOGOS_BF16 || dt == LOGOS_F16; }
+
+// Rule switch shared by every kernel: Shunyam sparsity applies only to sequences
+// longer than the window (include/Attention.hpp:228, cuda/ModelGPU.cu:966).
+__host__ __device__ inline bool shunyam_active(int window, int seq) {
+    return window > 0 && seq > window;
+}
+
+// allowed(i,j) = j <= i (if causal) and (j >= i - window or j % stride == 0)
+// (cuda/VedicGEMM.cu:987-996, include/Attention.hpp:88-96).
+__device__ __forceinline__ bool key_allowed(int i, int j, bool causal, bool shunyam, int window,
+                                            int stride) {
+    if (causal && j > i) return false;
+    if (shunyam) {
+        bool in_window = (j >= i - window) && (j <= i);
+        bool landmark = (stride > 0) && (j % stride == 0);
+        if (!in_window && !landmark) return false;
+    }
+    return true;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace logos
+
+// Kernel-side entry points implemented in the other translation units.
+namespace logos {
+int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*, int, int64_t);
+int kv_dequantize(logos_ctx*, const int8_t*, int64_t, const float*, float*, int64_t, int, int64_t);
+int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const float*,
+              const float*, const int32_t*, int, int, int, int);
+int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
+                const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
+                float*);
+size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
+int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
+                   const void* V, void* O, int B, int H, int S, int DH,
+                   const logos_attn_params*);
+}  // namespace logos

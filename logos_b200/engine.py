@@ -1,0 +1,135 @@
+"""Torch-tensor front ends over the C ABI.
+
+Torch is plumbing here: it owns device memory and streams; every operation below
+is one call into liblogos_attn.so.  Names follow the reference: `MultiHeadAttention`
+-style forward on [B,H,S,DH] tensors, `nikhilam_compress` / `nikhilam_decompress`,
+`kv_append`, `decode_int8`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import lib as L
+
+_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.float16: L.F16}
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+class Engine:
+    """One context per process and GPU (logos_ctx)."""
+
+    def __init__(self, device: int | None = None):
+        self.lib = L.load_library()
+        if not torch.cuda.is_available():
+            raise L.LogosError(L.ERR_NO_DEVICE, "no CUDA device: the engine has no CPU path")
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        h = C.c_void_p()
+        self._check(self.lib.logos_ctx_create(self.device, C.byref(h)), None)
+        self.h = h
+        self.use_stream(torch.cuda.current_stream(self.device))
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.logos_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, h="self"):
+        if rc != L.OK:
+            msg = self.lib.logos_status_string(rc).decode()
+            if h == "self" and getattr(self, "h", None):
+                msg += ": " + self.lib.logos_last_error(self.h).decode()
+            raise L.LogosError(rc, msg)
+
+    def use_stream(self, stream: torch.cuda.Stream):
+        self._check(self.lib.logos_ctx_set_stream(self.h, C.c_void_p(stream.cuda_stream)))
+
+    def reserve(self, nbytes: int):
+        self._check(self.lib.logos_ctx_reserve(self.h, int(nbytes)))
+
+    # ---- attention ---------------------------------------------------------
+    def flash_attention_fwd_f32(self, Q, K, V, scale, causal=True, shunyam=False, window=0, stride=0):
+        """cuda_flash_attention_fwd: one head, fp32 [seq, DH]."""
+        seq, DH = Q.shape
+        out = torch.empty_like(Q)
+        self._check(self.lib.logos_flash_attention_fwd_f32(
+            self.h, _ptr(Q), _ptr(K), _ptr(V), _ptr(out), None, seq, DH, float(scale), int(causal),
+            int(shunyam), int(window), int(stride)))
+        return out
+
+    def attention(self, Q, K, V, params: L.Params, out_dtype=None, out=None):
+        """Q,K,V: [B,H,S,DH] contiguous -> O [B,H,S,DH]."""
+        B, H, S, DH = Q.shape
+        assert Q.is_contiguous() and K.is_contiguous() and V.is_contiguous()
+        out_dtype = out_dtype or Q.dtype
+        if out is None:
+            out = torch.empty((B, H, S, DH), dtype=out_dtype, device=Q.device)
+        self._check(self.lib.logos_attention_fwd(self.h, _DT[Q.dtype], _DT[out.dtype], _ptr(Q), _ptr(K),
+                                                _ptr(V), _ptr(out), B, H, S, DH, C.byref(params)))
+        return out
+
+    # ---- Nikhilam INT8 KV ----------------------------------------------------
+    def nikhilam_compress(self, x, cache=None, rows=None):
+        """x: [..., S, DH] (any leading dims = independent tensors) -> (int8 like x, scales[...]).
+
+        With `cache` ([n, S_max, DH] int8) the bytes go to rows [0, S) of each cache tensor."""
+        S, DH = x.shape[-2:]
+        n = x.numel() // (S * DH)
+        x = x.contiguous()
+        scales = torch.empty(x.shape[:-2], dtype=torch.float32, device=x.device)
+        if cache is None:
+            q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+            dst_stride = S * DH
+        else:
+            q = cache
+            dst_stride = cache.shape[-2] * cache.shape[-1]
+        self._check(self.lib.logos_kv_quantize(self.h, _DT[x.dtype], _ptr(x), S * DH, _ptr(q), dst_stride,
+                                              _ptr(scales), n, S * DH))
+        return q, scales
+
+    def nikhilam_decompress(self, q, scales, rows=None):
+        """q: [..., S_max, DH] int8, scales [...] -> fp32 of rows [0, rows)."""
+        S_max, DH = q.shape[-2:]
+        rows = S_max if rows is None else rows
+        n = q.numel() // (S_max * DH)
+        out = torch.empty(q.shape[:-2] + (rows, DH), dtype=torch.float32, device=q.device)
+        self._check(self.lib.logos_kv_dequantize(self.h, _ptr(q), S_max * DH, _ptr(scales), _ptr(out),
+                                                rows * DH, n, rows * DH))
+        return out
+
+    def kv_append(self, k_new, v_new, k_cache, v_cache, k_scale, v_scale, pos):
+        B, H, S_max, DH = k_cache.shape
+        self._check(self.lib.logos_kv_append(self.h, _DT[k_new.dtype], _ptr(k_new), _ptr(v_new), _ptr(k_cache),
+                                            _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(pos), B, H,
+                                            S_max, DH))
+
+    def decode_workspace_bytes(self, B, H, S_max, DH):
+        return self.lib.logos_decode_workspace_bytes(B, H, S_max, DH)
+
+    def decode_int8(self, q, q_prev, k_cache, v_cache, k_scale, v_scale, lens, params: L.Params, out=None):
+        B, H, S_max, DH = k_cache.shape
+        if out is None:
+            out = torch.empty((B, H, DH), dtype=torch.float32, device=q.device)
+        self._check(self.lib.logos_decode_int8(self.h, _ptr(q), _ptr(q_prev), _ptr(k_cache), _ptr(v_cache),
+                                              _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H, S_max, DH,
+                                              C.byref(params), _ptr(out)))
+        return out
+
+    def decode_step_host(self, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, lens, params,
+                         out):
+        """All of q, q_prev, k_new, v_new, lens, out are HOST (ideally pinned) tensors."""
+        B, H, S_max, DH = k_cache.shape
+        self._check(self.lib.logos_decode_step_int8_host(
+            self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache),
+            _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
+        return out

@@ -1,0 +1,75 @@
+"""ctypes binding of the C ABI in include/logos_attn.h.
+
+Loading fails loudly: there is no CPU fallback, so a missing or unloadable
+`liblogos_attn.so` raises instead of degrading.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from functools import lru_cache
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "liblogos_attn.so")
+
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_ALIGNMENT = range(7)
+F32, BF16, F16 = 0, 1, 2
+DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
+
+
+class LogosError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"logos_attn status {status}: {message}")
+        self.status = status
+
+
+class Params(C.Structure):
+    """logos_attn_params."""
+    _fields_ = [("scale", C.c_float), ("causal", C.c_int), ("window", C.c_int),
+                ("stride", C.c_int), ("ns_eta", C.c_float), ("ns_nu", C.c_float),
+                ("ns_alpha", C.c_float), ("diffuse_mode", C.c_int)]
+
+    @classmethod
+    def make(cls, scale, causal=True, window=0, stride=0, ns_eta=0.0, ns_nu=0.0, ns_alpha=1.0,
+             diffuse_mode=DIFFUSE_NONE) -> "Params":
+        return cls(float(scale), int(causal), int(window), int(stride), float(ns_eta),
+                   float(ns_nu), float(ns_alpha), int(diffuse_mode))
+
+
+# name -> (restype, argtypes); every symbol include/logos_attn.h declares
+_vp, _i, _f, _i64, _sz = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_size_t
+_PP = C.POINTER(Params)
+SIGNATURES = {
+    "logos_abi_version": (_i, []),
+    "logos_status_string": (C.c_char_p, [_i]),
+    "logos_ctx_create": (_i, [_i, C.POINTER(_vp)]),
+    "logos_ctx_destroy": (_i, [_vp]),
+    "logos_ctx_set_stream": (_i, [_vp, _vp]),
+    "logos_ctx_reserve": (_i, [_vp, _sz]),
+    "logos_ctx_set_workspace": (_i, [_vp, _vp, _sz]),
+    "logos_last_error": (C.c_char_p, [_vp]),
+    "logos_flash_attention_fwd_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),
+    "logos_attention_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
+    "logos_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_kv_quantize": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i, _i64]),
+    "logos_kv_dequantize": (_i, [_vp, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
+    "logos_kv_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "logos_decode_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
+    "logos_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_decode_step_int8_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                                        _i, _i, _PP, _vp]),
+}
+
+
+@lru_cache(maxsize=None)
+def load_library() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise LogosError(ERR_NO_DEVICE,
+                         f"{LIB_PATH} is missing: build it with `python -m logos_b200.build` "
+                         "(nvcc, sm_100a); there is no CPU fallback")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    return lib

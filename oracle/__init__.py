@@ -110,6 +110,8 @@ def ref():
                                            C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                                            C.c_float, f32p, C.c_int]
     L.ref_hardware_threads.restype = C.c_int
+    L.ref_seed.argtypes = [C.c_uint]
+    L.ref_fill_random.argtypes = [f32p, C.c_int, C.c_int, C.c_float, C.c_float]
     return L
 
 

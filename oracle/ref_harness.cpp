@@ -165,6 +165,35 @@ void ref_attention_full_batch(const float* Q, const float* K, const float* V, in
     for (auto& th : pool) th.join();
 }
 
+// n independent heads through navier_stokes_attention alone (alpha == 1, the GPU model's
+// setting: no standard path is computed), full causal mask taken from the reference's
+// own cache.  Q,K,V,out: [n][seq][dk].
+void ref_ns_attention_batch(const float* Q, const float* K, const float* V, int n, int seq,
+                            int dk, float eta, float nu, float* out, int threads) {
+    const Tensor& mask = causal_mask_cached(seq);
+    float T = std::sqrt(static_cast<float>(dk));
+    int nt = threads < 1 ? 1 : (threads < n ? threads : n);
+    std::vector<std::thread> pool;
+    size_t sz = (size_t)seq * dk;
+    for (int t = 0; t < nt; ++t)
+        pool.emplace_back([=, &mask] {
+            for (int i = t; i < n; i += nt)
+                put(navier_stokes_attention(make(Q + i * sz, seq, dk), make(K + i * sz, seq, dk),
+                                            make(V + i * sz, seq, dk), mask, T, eta, nu),
+                    out + i * sz);
+        });
+    for (auto& th : pool) th.join();
+}
+
+// Tensor::fill_random after logos_rng::set_global_seed (Tensor.hpp:14-45,97-104): the
+// generator behind the seeded fixtures of the reference's unit tests.
+void ref_seed(unsigned seed) { logos_rng::set_global_seed(seed); }
+void ref_fill_random(float* out, int rows, int cols, float lo, float hi) {
+    Tensor t({rows, cols});
+    t.fill_random(lo, hi);
+    put(t, out);
+}
+
 int ref_hardware_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

@@ -1,0 +1,169 @@
+"""INT8-KV decode attention on the GPU against the CPU oracle (dequantize + Navier-Stokes
+terms + last attention row), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from logos_b200 import lib as L
+from logos_b200 import synthetic as syn
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+
+MODES = [L.DIFFUSE_NONE, L.DIFFUSE_CAUSAL, L.DIFFUSE_CENTRAL]
+
+
+def make_cache(B, H, S_max, lens, seed):
+    """Pre-quantization K/V ~ N(0,1) with 1 % x8 outliers, quantized per (b,h) over the valid rows."""
+    DH = 64
+    k = syn.normal_with_outliers((B, H, S_max, DH), seed, 1)
+    v = syn.normal_with_outliers((B, H, S_max, DH), seed, 2)
+    kq = np.zeros((B, H, S_max, DH), np.int8)
+    vq = np.zeros_like(kq)
+    ks = np.zeros((B, H), np.float32)
+    vs = np.zeros_like(ks)
+    for b in range(B):
+        for h in range(H):
+            n = lens[b]
+            kq[b, h, :n], ks[b, h] = O.nikhilam_compress(k[b, h, :n])
+            vq[b, h, :n], vs[b, h] = O.nikhilam_compress(v[b, h, :n])
+    return kq, vq, ks, vs
+
+
+def run_case(engine, B, H, S_max, lens, params, seed, tight=2e-5):
+    DH = 64
+    lens = np.asarray(lens, np.int32)
+    kq, vq, ks, vs = make_cache(B, H, S_max, lens, seed)
+    q = syn.normal((B, H, DH), seed, 3).astype(np.float16)
+    qp = syn.normal((B, H, DH), seed, 4).astype(np.float16)
+    engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
+    dev = lambda a: torch.from_numpy(a).cuda()
+    out = engine.decode_int8(dev(q), dev(qp), dev(kq), dev(vq), dev(ks), dev(vs), dev(lens), params)
+    op = O.attn_params(params.scale, params.causal, params.window, params.stride, params.ns_eta, params.ns_nu,
+                       params.ns_alpha, params.diffuse_mode)
+    n = B * H
+    want = O.decode_int8_batch(q.astype(np.float32).reshape(n, DH), qp.astype(np.float32).reshape(n, DH),
+                               kq.reshape(n, S_max, DH), vq.reshape(n, S_max, DH), ks.reshape(n), vs.reshape(n),
+                               np.repeat(lens, H), op).reshape(B, H, DH)
+    got = out.cpu().numpy()
+    assert_close(got, want, f"decode lens={list(lens)}")
+    assert np.abs(got - want).max() < tight * max(1.0, np.abs(want).max()), np.abs(got - want).max()
+    return got
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("alpha", [1.0, 0.3])
+def test_dense_small_and_ragged(engine, mode, alpha):
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, alpha, mode)
+    run_case(engine, 4, 2, 128, [1, 2, 63, 128], p, seed=11)
+    run_case(engine, 3, 3, 320, [65, 200, 320], p, seed=12)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_dense_split_k(engine, mode):
+    # few pairs and a long context: the engine splits the key axis into many chunks
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, mode)
+    run_case(engine, 2, 2, 4096, [4096, 1500], p, seed=13)
+    run_case(engine, 1, 1, 8192, [8192], p, seed=14)
+    # chunk boundaries: lengths one below / at / one above a multiple of every chunk size
+    run_case(engine, 6, 1, 2048, [127, 128, 129, 1023, 1024, 1025], p, seed=15)
+
+
+def test_dense_blend_split_k(engine):
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 0.3, L.DIFFUSE_CENTRAL)
+    run_case(engine, 2, 2, 4096, [4096, 777], p, seed=16)
+
+
+def test_ns_off_variants(engine):
+    # alpha 0 or eta = nu = 0 is plain softmax attention over the dequantized cache
+    for p in (L.Params.make(0.125, True, 0, 0, 0.0, 0.0, 1.0, L.DIFFUSE_NONE),
+              L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 0.0, L.DIFFUSE_CAUSAL)):
+        run_case(engine, 2, 2, 512, [512, 100], p, seed=17)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("alpha", [1.0, 0.3])
+def test_shunyam_window_and_landmarks(engine, mode, alpha):
+    # window 64 / stride 16 is the reference's production setting (cuda/train_gpu.cu:1172-1173);
+    # lens at and around the window switch the rule on and off (seq > window)
+    p = L.Params.make(0.125, True, 64, 16, 0.1, 0.05, alpha, mode)
+    run_case(engine, 6, 2, 1024, [1, 64, 65, 66, 500, 1024], p, seed=18)
+    p = L.Params.make(0.125, True, 8, 5, 0.1, 0.05, alpha, mode)      # stride does not divide anything
+    run_case(engine, 4, 2, 256, [9, 10, 77, 256], p, seed=19)
+    p = L.Params.make(0.125, True, 32, 0, 0.1, 0.05, alpha, mode)     # pure window: no landmarks
+    run_case(engine, 3, 2, 256, [33, 100, 256], p, seed=20)
+
+
+def test_full_size_benchmark_shape(engine):
+    """64 sequences x 16 heads x 8192 cached tokens (1 GiB of int8 K+V): a sample of pairs
+    against the oracle, plus a property that needs no oracle -- permuting the cached
+    tokens of a pair (keys and values together) leaves plain softmax attention unchanged."""
+    B, H, S, DH = 64, 16, 8192, 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    kq = torch.randint(-127, 128, (B, H, S, DH), dtype=torch.int8, device="cuda", generator=g)
+    vq = torch.randint(-127, 128, (B, H, S, DH), dtype=torch.int8, device="cuda", generator=g)
+    ks = torch.rand((B, H), device="cuda", generator=g) * 0.02 + 0.01
+    vs = torch.rand((B, H), device="cuda", generator=g) * 0.02 + 0.01
+    q = torch.randn((B, H, DH), device="cuda", generator=g).half()
+    qp = torch.randn((B, H, DH), device="cuda", generator=g).half()
+    lens = torch.full((B,), S, dtype=torch.int32, device="cuda")
+    engine.reserve(engine.decode_workspace_bytes(B, H, S, DH))
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    out = engine.decode_int8(q, qp, kq, vq, ks, vs, lens, p).cpu().numpy()
+    op = O.attn_params(0.125, True, 0, 0, 0.1, 0.05, 1.0, O.DIFFUSE_CAUSAL)
+    for (b, h) in [(0, 0), (17, 5), (63, 15)]:
+        want = O.decode_int8_batch(q[b, h][None].float().cpu().numpy(), qp[b, h][None].float().cpu().numpy(),
+                                   kq[b, h][None].cpu().numpy(), vq[b, h][None].cpu().numpy(),
+                                   [ks[b, h].item()], [vs[b, h].item()], [S], op)
+        assert_close(out[b, h], want[0], f"pair {(b, h)}")
+    # permutation invariance of plain attention (no advection, no diffusion)
+    p0 = L.Params.make(0.125, True, 0, 0, 0.0, 0.0, 1.0, L.DIFFUSE_NONE)
+    a = engine.decode_int8(q, None, kq, vq, ks, vs, lens, p0).cpu().numpy()
+    perm = torch.randperm(S, device="cuda", generator=g)
+    kq.copy_(kq[:, :, perm].clone())
+    vq.copy_(vq[:, :, perm].clone())
+    b_ = engine.decode_int8(q, None, kq, vq, ks, vs, lens, p0).cpu().numpy()
+    assert np.abs(a - b_).max() < 1e-5
+
+
+def test_host_step_entry_point(engine):
+    """logos_decode_step_int8_host == append + decode on device tensors."""
+    B, H, S_max, DH = 4, 4, 512, 64
+    lens0 = np.array([10, 100, 300, 511], np.int32)
+    kq, vq, ks, vs = make_cache(B, H, S_max, lens0, 21)
+    dev = lambda a: torch.from_numpy(a).cuda()
+    kc, vc, ksd, vsd = dev(kq), dev(vq), dev(ks), dev(vs)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = torch.randn(B, H, DH).half().pin_memory()
+    qp = torch.randn(B, H, DH).half().pin_memory()
+    kn = torch.randn(B, H, DH).half().pin_memory()
+    vn = torch.randn(B, H, DH).half().pin_memory()
+    lens = torch.from_numpy(lens0 + 1).pin_memory()
+    out = torch.empty(B, H, DH).pin_memory()
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
+    engine.decode_step_host(q, qp, kn, vn, kc, vc, ksd, vsd, lens, p, out)
+    engine.kv_append(kn.cuda(), vn.cuda(), kc2, vc2, ksd, vsd, dev(lens0))
+    want = engine.decode_int8(q.cuda(), qp.cuda(), kc2, vc2, ksd, vsd, lens.cuda(), p)
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    assert torch.equal(out, want.cpu())
+
+
+def test_argument_errors(engine):
+    B, H, S, DH = 1, 1, 64, 64
+    z8 = torch.zeros((B, H, S, DH), dtype=torch.int8, device="cuda")
+    one = torch.ones((B, H), device="cuda")
+    q = torch.zeros((B, H, DH), dtype=torch.float16, device="cuda")
+    lens = torch.ones(B, dtype=torch.int32, device="cuda")
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    with pytest.raises(L.LogosError) as e:
+        engine.decode_int8(q, None, z8, z8, one, one, lens, p)      # advection needs q_prev
+    assert e.value.status == L.ERR_INVALID_ARG
+    bad = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, 7)
+    with pytest.raises(L.LogosError):
+        engine.decode_int8(q, q, z8, z8, one, one, lens, bad)
+    z8_32 = torch.zeros((B, H, S, 32), dtype=torch.int8, device="cuda")
+    with pytest.raises(L.LogosError) as e:
+        engine.decode_int8(q, q, z8_32, z8_32, one, one, lens, p)
+    assert e.value.status == L.ERR_UNSUPPORTED
