@@ -281,7 +281,7 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": total_bytes / (step_ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 KV, fp16 Q, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "int8_kv_decode_b64_h16_ctx8192_dh64", "batch": B, "heads": H, "ctx": S_MAX, "dh": DH,
+        "config": {"workload": f"int8_kv_decode_b{B}_h16_ctx8192_dh64", "batch": B, "heads": H, "ctx": S_MAX, "dh": DH,
                    "ns_eta": ETA, "ns_nu": NU, "diffusion": "causal", "parallelism": f"heads/{world}",
                    "l2": (f"inputs larger than L2: {per_set >> 20} MiB of cache per GPU per pass, "
                           f"{n_sets} cache set(s) visited in rotation")},
@@ -310,8 +310,12 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=B,
+                    help="sequences in the batch; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.batch != B:
+        globals()["B"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:

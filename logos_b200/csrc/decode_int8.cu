@@ -9,10 +9,9 @@
 // (cuda/ModelGPU.cu:343-351,443-471, cuda/VedicGEMM.cu:901-1062); the reference
 // itself has no incremental decode (cuda/train_gpu.cu:2037-2046).
 //
-// The path is HBM-bound (one byte of K and one of V per key and channel, ~2 FMA per
-// byte), so it runs on the SIMT pipes: every lane issues 16-byte loads, a warp-wide
-// load covers 8 consecutive 64-byte rows (512 contiguous bytes), four such loads are
-// kept in flight per lane, and int8 -> fp32 happens in registers.
+// The path is HBM-bound: one byte of K and one of V per key and channel, read once
+// with 16- and 8-byte vector loads (several in flight per lane) straight into the
+// registers that feed the arithmetic; nothing is staged, nothing is re-read.
 //
 // Dense contexts are split over the key axis (split-K): CTA (s, bh) handles keys
 // [s*chunk, (s+1)*chunk) of pair bh, writes (max, sum, 64 partial outputs) to the
@@ -168,14 +167,91 @@ __device__ __forceinline__ float block_reduce_acc(float* acc, float (*red)[kDH])
 
 // ---------------------------------------------------------------------------
 // Dense context: every cached key is visible.
+//
+// Both contractions run as exact integer dot products on the tensor cores
+// (mma.sync m16n8k32, int8 x int8 -> int32), because a first SIMT version that
+// converted every byte to fp32 was bound by instruction issue at 41 % of DRAM
+// bandwidth (about 100 instructions per 16-byte vector).  The float operand of
+// each contraction is cut into three int8 "digits" of a 24-bit fixed-point number,
+// which the 8-wide N (or 16-high M) dimension of the MMA carries for free:
+//   scores : A = 16 keys x 32 channels of K bytes, B = query digits (columns 0-2:
+//            advected query, 3-5: plain query for the blend), C = digit dot products;
+//   output : A = weight digits (rows 0-2 / 3-5) x 32 keys, B = V bytes transposed in
+//            registers to key-major (8 byte-permutes per 4x4 block), C = digit sums.
+// int32 accumulation is exact; the digits are recombined in fp32 once per CTA.
+// The fixed-point grids (2^-22 of the largest |q| channel, 2^-23 of the largest
+// weight) are finer than fp32 rounding of the same sums.
+
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint2 ld_stream8(const int8_t* p) {
+    uint2 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+
+// rows r0..r3 hold 4 consecutive bytes each; out[j] = byte j of (r0, r1, r2, r3)
+__device__ __forceinline__ void transpose4x4(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
+                                             uint32_t* out) {
+    uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r2, r3, 0x5140);
+    uint32_t t2 = __byte_perm(r0, r1, 0x7362), t3 = __byte_perm(r2, r3, 0x7362);
+    out[0] = __byte_perm(t0, t1, 0x5410);
+    out[1] = __byte_perm(t0, t1, 0x7632);
+    out[2] = __byte_perm(t2, t3, 0x5410);
+    out[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// byte `idx` of four words packed into one word (word e -> byte e)
+__device__ __forceinline__ uint32_t pack_byte(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
+                                              int idx) {
+    uint32_t sel = (uint32_t)idx | ((uint32_t)(4 + idx) << 4);
+    uint32_t lo = __byte_perm(w0, w1, sel), hi = __byte_perm(w2, w3, sel);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+// Signed base-256 digits of a fixed-point integer: v = d0*65536 + d1*256 + d2, d1,d2 in [-128,127].
+__device__ __forceinline__ int signed_digit(int v, int which) {
+    int d2 = ((v + 128) & 255) - 128;
+    int r = (v - d2) >> 8;
+    int d1 = ((r + 128) & 255) - 128;
+    int d0 = (r - d1) >> 8;
+    return which == 0 ? d0 : (which == 1 ? d1 : d2);
+}
+
+constexpr int kDenseWarps = 4;                  // warps per CTA, each with its own key range
+constexpr int kDenseThreads = kDenseWarps * 32;
+constexpr int kSubMax = kMaxChunk / kDenseWarps;  // keys per warp (256)
+constexpr int kDigitPitch = kSubMax / 4 + 4;    // words per digit row (+4: no bank aliasing)
+constexpr float kQGrid = 4194303.0f;            // 2^22 - 1 levels for the largest |q| channel
+constexpr float kWGrid = 8388608.0f;            // 2^23 levels per unit weight
+
+// Every warp streams its own contiguous range of keys (two passes: K then V) and
+// only meets the other warps of the CTA once, to merge (max, sum, output).  Inside
+// the passes there is no block-wide barrier, and the next 32-key tile is always in
+// flight while the current one is consumed.
 template <bool BLEND>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kDenseThreads, 4)
 decode_dense_kernel(const DecodeArgs a) {
     constexpr int PATHS = BLEND ? 2 : 1;
-    __shared__ float p_ns[kMaxChunk + 2];             // p_ns[1 + t], zero halo at both ends
-    __shared__ float p_std[BLEND ? kMaxChunk : 1];
-    __shared__ float red[kWarps];
-    __shared__ float red_acc[kWarps][kDH];
+    constexpr int ND = 3 * PATHS;                                   // digit rows / columns in use
+    __shared__ float sc[kDenseWarps][PATHS][kSubMax + 2];           // [1 + r], zero halo at both ends
+    __shared__ uint32_t wdig[kDenseWarps][ND][kDigitPitch];         // weight digits, 4 keys per word
+    __shared__ float part[kDenseWarps][PATHS][kPartial];            // per-warp (max, sum, out[64])
     __shared__ unsigned int is_last;
 
     const int bh = blockIdx.y, split = blockIdx.x, n_splits = gridDim.x;
@@ -185,118 +261,264 @@ decode_dense_kernel(const DecodeArgs a) {
     const int pos = len - 1;
     const int c0 = split * a.chunk;
     const int c1 = min(len, c0 + a.chunk);
-    const int n = c1 - c0;  // keys of this CTA (<= 0: nothing to do but report)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row_in_warp = lane >> 2, part = lane & 3;
+    const int g = lane >> 2, t = lane & 3;   // MMA fragment coordinates: group, thread-in-group
+    const int sub = a.chunk / kDenseWarps;   // keys per warp, a multiple of 32
+    const int w0 = c0 + warp * sub;
+    const int w1 = min(c1, w0 + sub);
+    const int nw = w1 - w0;                  // keys of this warp (<= 0: nothing to do but report)
 
-    const int8_t* kbase = a.k_cache + (int64_t)bh * a.S_max * kDH + part * 16;
-    const int8_t* vbase = a.v_cache + (int64_t)bh * a.S_max * kDH + part * 16;
+    const int8_t* kbase = a.k_cache + (int64_t)bh * a.S_max * kDH + (int64_t)w0 * kDH;
+    const int8_t* vbase = a.v_cache + (int64_t)bh * a.S_max * kDH + (int64_t)w0 * kDH;
+    float* p_ns = sc[warp][0];
+    float* p_std = sc[warp][PATHS - 1];
 
-    float m_ns = -INFINITY, l_ns = 0.0f, m_std = -INFINITY, l_std = 0.0f;
-    float o_ns = 0.0f, o_std = 0.0f;  // channel tid (tid < 64) after the reductions
-
-    if (n > 0) {
-        float qn[16], qs[BLEND ? 16 : 1];
-        load_query<BLEND>(a, bh, pos, part, qn, qs);
-
-        // ---- scores ----
-        for (int r0 = warp * kRowsPerWarp; r0 < n; r0 += kRowsPerIter * kUnroll) {
-            uint4 w[kUnroll];
+    if (nw > 0) {
+        // first K tile goes out before any arithmetic
+        uint4 ka[4], kb[4];
+        auto load_k = [&](uint4 (&buf)[4], int r0) {
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                int r = r0 + u * kRowsPerIter + row_in_warp;
-                w[u] = (r < n) ? ld_stream(kbase + (int64_t)(c0 + r) * kDH) : make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < 4; ++u) {
+                int r = r0 + g + 8 * u;
+                buf[u] = (r < nw) ? ld_stream(kbase + (int64_t)r * kDH + 16 * t) : make_uint4(0, 0, 0, 0);
             }
+        };
+        load_k(ka, 0);
+
+        // ---- query digits: lane (g,t) holds digit g of channels 16t..16t+15 ----
+        uint32_t qb[4];
+        float qstep_ns, qstep_std = 0.0f;
+        {
+            float qn[16], qs[BLEND ? 16 : 1];
+            load_query<BLEND>(a, bh, pos, t, qn, qs);
+            float mx = 0.0f, mx2 = 0.0f;
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                int r = r0 + u * kRowsPerIter + row_in_warp;
-                float s = dot16(w[u], qn);
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                float s2 = 0.0f;
+            for (int k = 0; k < 16; ++k) {
+                mx = fmaxf(mx, fabsf(qn[k]));
+                if (BLEND) mx2 = fmaxf(mx2, fabsf(qs[k]));
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            if (BLEND) {
+                mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 1));
+                mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, 2));
+            }
+            const float inv = mx > 0.0f ? kQGrid / mx : 0.0f;
+            const float inv2 = (BLEND && mx2 > 0.0f) ? kQGrid / mx2 : 0.0f;
+            qstep_ns = mx / kQGrid;
+            if (BLEND) qstep_std = mx2 / kQGrid;
+            const bool use_std = BLEND && g >= 3;
+            const int which = g % 3;
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float x = use_std ? qs[BLEND ? 4 * wd + e : 0] * inv2 : qn[4 * wd + e] * inv;
+                    int d = signed_digit(__float2int_rn(x), which);
+                    word |= ((uint32_t)d & 0xffu) << (8 * e);
+                }
+                qb[wd] = (g < ND) ? word : 0u;
+            }
+        }
+        // per-lane recombination weights of the score digits: C column 2t and 2t+1
+        const float ns_e = (t == 0) ? 65536.0f : (t == 1 ? 1.0f : 0.0f);
+        const float ns_o = (t == 0) ? 256.0f : 0.0f;
+        const float st_e = (t == 2) ? 256.0f : 0.0f;
+        const float st_o = (t == 1) ? 65536.0f : (t == 2 ? 1.0f : 0.0f);
+
+        // ---- scores: 32 keys per tile = two 16-key MMA pairs ----
+        auto score_tile = [&](const uint4 (&buf)[4], int r0) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const uint4& lo = buf[2 * hf];
+                const uint4& hi = buf[2 * hf + 1];
+                int ra = r0 + 16 * hf + g, rb = ra + 8;
+                int c[4] = {0, 0, 0, 0};
+                mma_s8s8(c, lo.x, hi.x, lo.y, hi.y, qb[0], qb[1]);
+                mma_s8s8(c, lo.z, hi.z, lo.w, hi.w, qb[2], qb[3]);
+                float sa = ns_e * (float)c[0] + ns_o * (float)c[1];
+                float sb = ns_e * (float)c[2] + ns_o * (float)c[3];
+                sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 1);
+                sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+                sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+                float ta = 0.0f, tb = 0.0f;
                 if (BLEND) {
-                    s2 = dot16(w[u], qs);
-                    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-                    s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+                    ta = st_e * (float)c[0] + st_o * (float)c[1];
+                    tb = st_e * (float)c[2] + st_o * (float)c[3];
+                    ta += __shfl_xor_sync(0xffffffffu, ta, 1);
+                    tb += __shfl_xor_sync(0xffffffffu, tb, 1);
+                    ta += __shfl_xor_sync(0xffffffffu, ta, 2);
+                    tb += __shfl_xor_sync(0xffffffffu, tb, 2);
                 }
-                if (part == 0 && r < n) {
-                    p_ns[1 + r] = s;
-                    if (BLEND) p_std[r] = s2;
+                if (t == 0) {
+                    if (ra < nw) p_ns[1 + ra] = sa * qstep_ns;
+                    if (rb < nw) p_ns[1 + rb] = sb * qstep_ns;
+                }
+                if (BLEND && t == 1) {
+                    if (ra < nw) p_std[1 + ra] = ta * qstep_std;
+                    if (rb < nw) p_std[1 + rb] = tb * qstep_std;
                 }
             }
+        };
+        for (int r0 = 0; r0 < nw; r0 += 64) {
+            load_k(kb, r0 + 32);
+            score_tile(ka, r0);
+            load_k(ka, r0 + 64);
+            if (r0 + 32 < nw) score_tile(kb, r0 + 32);   // warp-uniform
         }
-        if (tid == 0) { p_ns[0] = 0.0f; p_ns[1 + n] = 0.0f; }
-        __syncthreads();
 
-        // ---- softmax over this chunk ----
+        // first V tile goes out before the softmax
+        uint2 va[8], vb[8];
+        auto load_v = [&](uint2 (&buf)[8], int r0) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                int r = r0 + (u < 4 ? 4 * t + u : 16 + 4 * t + (u - 4));
+                buf[u] = (r < nw) ? ld_stream8(vbase + (int64_t)r * kDH + 8 * g) : make_uint2(0, 0);
+            }
+        };
+        load_v(va, 0);
+        if (lane == 0) { p_ns[0] = 0.0f; p_ns[1 + nw] = 0.0f; }
+        __syncwarp();
+
+        // ---- softmax over this warp's keys ----
         float mx = -INFINITY, mx2 = -INFINITY;
-        for (int t = tid; t < n; t += kThreads) {
-            mx = fmaxf(mx, p_ns[1 + t]);
-            if (BLEND) mx2 = fmaxf(mx2, p_std[t]);
+        for (int i = lane; i < nw; i += 32) {
+            mx = fmaxf(mx, p_ns[1 + i]);
+            if (BLEND) mx2 = fmaxf(mx2, p_std[1 + i]);
         }
-        m_ns = block_max(mx, red);
-        if (BLEND) m_std = block_max(mx2, red);
+        const float m_ns = warp_max(mx);
+        const float m_std = BLEND ? warp_max(mx2) : 0.0f;
         float sum = 0.0f, sum2 = 0.0f;
-        for (int t = tid; t < n; t += kThreads) {
-            float e = exp2f(p_ns[1 + t] - m_ns);
-            p_ns[1 + t] = e;
+        for (int i = lane; i < nw; i += 32) {
+            float e = exp2f(p_ns[1 + i] - m_ns);
+            p_ns[1 + i] = e;
             sum += e;
             if (BLEND) {
-                float e2 = exp2f(p_std[t] - m_std);
-                p_std[t] = e2;
+                float e2 = exp2f(p_std[1 + i] - m_std);
+                p_std[1 + i] = e2;
                 sum2 += e2;
             }
         }
-        l_ns = block_sum(sum, red);  // also orders the p_* writes before the reads below
-        if (BLEND) l_std = block_sum(sum2, red);
+        const float l_ns = warp_sum(sum);
+        const float l_std = BLEND ? warp_sum(sum2) : 0.0f;
+        __syncwarp();
 
-        // ---- weights * V ----
+        // ---- value weights (diffusion folded in) as three unsigned digits ----
         float cC = 1.0f, cL = 0.0f, cR = 0.0f, b0 = 0.0f, bN = 0.0f;
         if (a.diffuse_mode == LOGOS_DIFFUSE_CAUSAL) {
             cC = 1.0f - a.nu; cR = a.nu; b0 = a.nu;
         } else if (a.diffuse_mode == LOGOS_DIFFUSE_CENTRAL) {
             cC = 1.0f - a.nu; cR = cL = 0.5f * a.nu; b0 = bN = 0.5f * a.nu;
         }
-        float acc[16], acc2[BLEND ? 16 : 1];
+        const int groups = ((nw + 31) >> 5) << 3;  // 4-key words, padded to whole 32-key tiles
+        for (int grp = lane; grp < groups; grp += 32) {
+            uint32_t W[4], W2[4];
 #pragma unroll
-        for (int k = 0; k < 16; ++k) acc[k] = 0.0f;
-        if (BLEND) {
-#pragma unroll
-            for (int k = 0; k < 16; ++k) acc2[k] = 0.0f;
-        }
-        for (int r0 = warp * kRowsPerWarp; r0 < n; r0 += kRowsPerIter * kUnroll) {
-            uint4 w[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                int r = r0 + u * kRowsPerIter + row_in_warp;
-                w[u] = (r < n) ? ld_stream(vbase + (int64_t)(c0 + r) * kDH) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                int r = r0 + u * kRowsPerIter + row_in_warp;
-                if (r < n) {
+            for (int e = 0; e < 4; ++e) {
+                int r = 4 * grp + e;
+                float wgt = 0.0f, wgt2 = 0.0f;
+                if (r < nw) {
                     float pc = p_ns[1 + r];
-                    float wgt = cC * pc + cR * p_ns[2 + r] + cL * p_ns[r];
-                    int j = c0 + r;
+                    wgt = cC * pc + cR * p_ns[2 + r] + cL * p_ns[r];
+                    int j = w0 + r;
                     if (j == 0) wgt += b0 * pc;
                     if (j == len - 1) wgt += bN * pc;
-                    axpy16(w[u], wgt, acc);
-                    if (BLEND) axpy16(w[u], p_std[r], acc2);
+                    if (BLEND) wgt2 = p_std[1 + r];
                 }
+                W[e] = min(__float2uint_rn(wgt * kWGrid), 0xFFFFFFu);
+                W2[e] = BLEND ? min(__float2uint_rn(wgt2 * kWGrid), 0xFFFFFFu) : 0u;
+            }
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+                wdig[warp][d][grp] = pack_byte(W[0], W[1], W[2], W[3], 2 - d);
+                if (BLEND) wdig[warp][BLEND ? 3 + d : 0][grp] = pack_byte(W2[0], W2[1], W2[2], W2[3], 2 - d);
             }
         }
-        // halo rows: the row before the chunk takes cR * p(first key), the row after
-        // it takes cL * p(last key)
-        if (warp == 0 && lane < 4 && c0 > 0 && cR != 0.0f) {
-            uint4 w = ld_stream(vbase + (int64_t)(c0 - 1) * kDH);
-            axpy16(w, cR * p_ns[1], acc);
+        __syncwarp();
+
+        // ---- weights x V: 32 keys per tile, 8 MMAs (one per 8 channels) ----
+        int acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0; }
+        const uint32_t* my_dig = wdig[warp][g < ND ? g : 0];
+        auto value_tile = [&](const uint2 (&buf)[8], int r0) {
+            int grp = r0 >> 2;
+            uint32_t a0 = (g < ND) ? my_dig[grp + t] : 0u;
+            uint32_t a2 = (g < ND) ? my_dig[grp + 4 + t] : 0u;
+            uint32_t blo[8], bhi[8];
+            transpose4x4(buf[0].x, buf[1].x, buf[2].x, buf[3].x, blo);
+            transpose4x4(buf[0].y, buf[1].y, buf[2].y, buf[3].y, blo + 4);
+            transpose4x4(buf[4].x, buf[5].x, buf[6].x, buf[7].x, bhi);
+            transpose4x4(buf[4].y, buf[5].y, buf[6].y, buf[7].y, bhi + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mma_u8s8(acc[j], a0, 0u, a2, 0u, blo[j], bhi[j]);
+        };
+        for (int r0 = 0; r0 < nw; r0 += 64) {
+            load_v(vb, r0 + 32);
+            value_tile(va, r0);
+            load_v(va, r0 + 64);
+            if (r0 + 32 < nw) value_tile(vb, r0 + 32);   // warp-uniform
         }
-        if (warp == 1 && lane < 4 && c1 < len && cL != 0.0f) {
-            uint4 w = ld_stream(vbase + (int64_t)c1 * kDH);
-            axpy16(w, cL * p_ns[n], acc);
+        // halo rows in fp32 (lanes 0-3, 16 channels each): the row before the range takes
+        // cR * p(first key), the row after it takes cL * p(last key)
+        float hal[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) hal[k] = 0.0f;
+        if (lane < 4) {
+            if (w0 > 0 && cR != 0.0f) axpy16(ld_stream(vbase - kDH + 16 * lane), cR * p_ns[1], hal);
+            if (w1 < len && cL != 0.0f) axpy16(ld_stream(vbase + (int64_t)nw * kDH + 16 * lane), cL * p_ns[nw], hal);
         }
-        o_ns = block_reduce_acc(acc, red_acc);
-        if (BLEND) o_std = block_reduce_acc(acc2, red_acc);
+        // digit rows -> fp32: row g carries 65536 / 256 / 1 of path (g / 3)
+        const float ns_w = (g == 0) ? 65536.0f : (g == 1 ? 256.0f : (g == 2 ? 1.0f : 0.0f));
+        const float st_w = (g == 3) ? 65536.0f : (g == 4 ? 256.0f : (g == 5 ? 1.0f : 0.0f));
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float f = (float)acc[j][h];
+                float vn = f * ns_w, vst = BLEND ? f * st_w : 0.0f;
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) {
+                    vn += __shfl_xor_sync(0xffffffffu, vn, off);
+                    if (BLEND) vst += __shfl_xor_sync(0xffffffffu, vst, off);
+                }
+                if (g == 0) {   // C column 2t+h of tile j is channel 8*(2t+h) + j
+                    part[warp][0][2 + 16 * t + 8 * h + j] = vn * (1.0f / kWGrid) + hal[8 * h + j];
+                    if (BLEND) part[warp][PATHS - 1][2 + 16 * t + 8 * h + j] = vst * (1.0f / kWGrid);
+                }
+            }
+        if (lane == 0) {
+            part[warp][0][0] = m_ns; part[warp][0][1] = l_ns;
+            if (BLEND) { part[warp][PATHS - 1][0] = m_std; part[warp][PATHS - 1][1] = l_std; }
+        }
+    } else {
+        for (int i = lane; i < PATHS * kPartial; i += 32) {
+            int pth = i / kPartial, k = i - pth * kPartial;
+            part[warp][pth][k] = (k == 0) ? -INFINITY : 0.0f;
+        }
+    }
+    __syncthreads();
+
+    // ---- merge the warps of this CTA: thread d owns channel d ----
+    float m_c[PATHS], l_c[PATHS], o_c[PATHS];
+    if (tid < kDH) {
+#pragma unroll
+        for (int pth = 0; pth < PATHS; ++pth) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kDenseWarps; ++w) M = fmaxf(M, part[w][pth][0]);
+            float num = 0.0f, den = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kDenseWarps; ++w) {
+                float mw = part[w][pth][0];
+                float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+                den = fmaf(f, part[w][pth][1], den);
+                num = fmaf(f, part[w][pth][2 + tid], num);
+            }
+            m_c[pth] = M; l_c[pth] = den; o_c[pth] = num;
+        }
     }
 
     const float vs = a.v_scale[bh];
@@ -304,11 +526,10 @@ decode_dense_kernel(const DecodeArgs a) {
 
     if (n_splits == 1) {
         if (tid < kDH) {
-            float r_ns = (l_ns > 0.0f) ? o_ns / l_ns : 0.0f;
-            float r = r_ns;
+            float r = (l_c[0] > 0.0f) ? o_c[0] / l_c[0] : 0.0f;
             if (BLEND) {
-                float r_std = (l_std > 0.0f) ? o_std / l_std : 0.0f;
-                r = (1.0f - a.alpha) * r_std + a.alpha * r_ns;
+                float r_std = (l_c[PATHS - 1] > 0.0f) ? o_c[PATHS - 1] / l_c[PATHS - 1] : 0.0f;
+                r = (1.0f - a.alpha) * r_std + a.alpha * r;
             }
             outp[tid] = r * vs;
         }
@@ -318,12 +539,11 @@ decode_dense_kernel(const DecodeArgs a) {
     // ---- publish this split's partial, merge if last ----
     float* mine = a.partials + ((int64_t)bh * n_splits + split) * PATHS * kPartial;
     if (tid < kDH) {
-        mine[2 + tid] = o_ns;
-        if (BLEND) mine[kPartial + 2 + tid] = o_std;
-    }
-    if (tid == 0) {
-        mine[0] = m_ns; mine[1] = l_ns;
-        if (BLEND) { mine[kPartial] = m_std; mine[kPartial + 1] = l_std; }
+#pragma unroll
+        for (int pth = 0; pth < PATHS; ++pth) {
+            mine[pth * kPartial + 2 + tid] = o_c[pth];
+            if (tid == 0) { mine[pth * kPartial] = m_c[pth]; mine[pth * kPartial + 1] = l_c[pth]; }
+        }
     }
     __threadfence();
     __syncthreads();
@@ -354,7 +574,7 @@ decode_dense_kernel(const DecodeArgs a) {
             r_path[pth] = (den > 0.0f) ? num / den : 0.0f;
         }
         float r = r_path[0];
-        if (BLEND) r = (1.0f - a.alpha) * r_path[1] + a.alpha * r_path[0];
+        if (BLEND) r = (1.0f - a.alpha) * r_path[PATHS - 1] + a.alpha * r_path[0];
         outp[tid] = r * vs;
     }
 }
@@ -578,8 +798,8 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
         a.counters = nullptr; a.partials = nullptr;
     }
     dim3 grid(n_splits, BH);
-    if (blend) decode_dense_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(a);
-    else       decode_dense_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(a);
+    if (blend) decode_dense_kernel<true><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
+    else       decode_dense_kernel<false><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
     LOGOS_LAUNCH_CHECK(ctx, "decode_dense_kernel");
     return LOGOS_OK;
 }

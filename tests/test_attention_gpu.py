@@ -52,15 +52,15 @@ def test_flash_fwd_f32_vs_oracle_and_reference_kernel(engine, seq, DH):
     K[syn.normal((seq, DH), 1, 9) > 2.3] *= 8          # outlier channels
     scale = float(1 / np.sqrt(DH))
     R = O.refgpu()
+    Qd, Kd, Vd = dev(Q), dev(K), dev(V)
     for (shun, w, s) in [(False, 0, 0), (True, 32, 8), (True, 64, 16), (True, 8, 5)]:
         active = shun and seq > w
-        got = engine.flash_attention_fwd_f32(dev(Q), dev(K), dev(V), scale, True, active, w, s).cpu().numpy()
+        got = engine.flash_attention_fwd_f32(Qd, Kd, Vd, scale, True, active, w, s).cpu().numpy()
         p = O.attn_params(scale, True, w if active else 0, s, 0.0, 0.0, 0.0, O.DIFFUSE_NONE)
         assert_close(got, O.attention_rows(Q, K, V, p), f"seq={seq} DH={DH} shunyam={(shun, w, s)}", 2e-5, 1e-5)
         if R is not None:
             ref = torch.empty((seq, DH), device="cuda")
-            rc = R.refgpu_flash_attention_fwd(dev(Q).data_ptr(), dev(K).data_ptr(), dev(V).data_ptr(),
-                                              ref.data_ptr(), seq, DH, scale, 1, int(active), max(w, 1), max(s, 1))
+            rc = R.refgpu_flash_attention_fwd(Qd.data_ptr(), Kd.data_ptr(), Vd.data_ptr(), ref.data_ptr(), seq, DH, scale, 1, int(active), max(w, 1), max(s, 1))
             torch.cuda.synchronize()
             assert rc == 0
             assert_close(got, ref.cpu().numpy(), "vs reference CUDA kernel", 2e-5, 1e-5)
