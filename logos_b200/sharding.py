@@ -34,9 +34,11 @@ def all_gather_heads(local: torch.Tensor, world: int, group=None) -> torch.Tenso
     if world == 1:
         return local
     local = local.contiguous()
-    parts = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(parts, local, group=group)
-    # parts[r] is rank r's [B, H_loc, ...]; interleave back along the head axis
+    flat = torch.empty((world * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype,
+                       device=local.device)
+    dist.all_gather_into_tensor(flat, local, group=group)
+    # rows [r*B, (r+1)*B) are rank r's [B, H_loc, ...]; interleave back along the head axis
+    parts = flat.view((world,) + tuple(local.shape))
     return parts.movedim(0, 1).reshape(local.shape[0], world * local.shape[1], *local.shape[2:])
 
 
