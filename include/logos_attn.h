@@ -40,7 +40,9 @@ typedef enum {
     LOGOS_ERR_WORKSPACE = 3,     /* context workspace too small for this call        */
     LOGOS_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed             */
     LOGOS_ERR_NO_DEVICE = 5,     /* no usable sm_100 device                          */
-    LOGOS_ERR_ALIGNMENT = 6      /* pointer or extent breaks a 16-byte requirement   */
+    LOGOS_ERR_ALIGNMENT = 6,     /* pointer or extent breaks a 16-byte requirement   */
+    LOGOS_ERR_SCRATCH_LIMIT = 7  /* request exceeds the fixed scratch of
+                                    logos_decode_int8_noalloc                        */
 } logos_status;
 
 typedef enum { LOGOS_F32 = 0, LOGOS_BF16 = 1, LOGOS_F16 = 2 } logos_dtype;
@@ -157,6 +159,28 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
                                 const float* v_scale, const int32_t* len_host, int B, int H,
                                 int S_max, int DH, const logos_attn_params* params,
                                 float* out_host);
+
+/* Dense INT8-KV decode for callers that cannot allocate device memory when they
+ * decode -- a host that gave the whole device to its own memory pool, a serving loop
+ * that forbids allocation after start-up, or an embedding that never creates a
+ * logos_ctx (creating one allocates).  It has no counterpart in the reference.
+ * Same arguments and result as logos_decode_int8 with params->window == 0, but no
+ * context: work goes to `cuda_stream` (cudaStream_t as void*, NULL = default stream)
+ * on the CURRENT device, and the split-K scratch is a fixed 4.3 MB array inside the
+ * library (held by every GPU that loads it until the process exits) instead of a
+ * workspace.  Limits: B*H <= 4096 pairs and B*H * key-splits * (2 if 0 < ns_alpha < 1
+ * else 1) <= 16384 partial records, where key-splits = ceil(S_max / chunk) and chunk is
+ * between 128 and 1024 keys (64 x 16 x 8192 needs 8192 records); larger requests return
+ * LOGOS_ERR_SCRATCH_LIMIT, window > 0 returns LOGOS_ERR_UNSUPPORTED.  The call makes no
+ * cudaMalloc / cudaFree and uses no allocating library routine.  The first call on a
+ * device looks up the array's device address; make that first call before any stream
+ * capture.  All calls share the one array and it keeps the previous call's contents
+ * (the call clears the counters it needs on its stream), so calls that overlap on a
+ * GPU -- two streams, two threads -- race: issue them on one stream, one at a time. */
+int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_prev,
+                              const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
+                              const float* v_scale, const int32_t* len, int B, int H, int S_max,
+                              int DH, const logos_attn_params* params, float* out);
 
 #ifdef __cplusplus
 }

@@ -29,6 +29,7 @@ const char* logos_status_string(int status) {
         case LOGOS_ERR_CUDA: return "CUDA error";
         case LOGOS_ERR_NO_DEVICE: return "no sm_100 CUDA device";
         case LOGOS_ERR_ALIGNMENT: return "misaligned pointer or extent";
+        case LOGOS_ERR_SCRATCH_LIMIT: return "request exceeds the fixed scratch of the no-allocation entry point";
     }
     return "unknown status";
 }

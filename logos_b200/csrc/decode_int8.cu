@@ -805,3 +805,117 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
 }
 
 }  // namespace logos
+
+// ---------------------------------------------------------------------------
+// Dense decode for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they decode:
+// code running inside a memory pool that owns the whole device, a serving loop that
+// forbids allocation after start-up, or an embedding that never creates a logos_ctx
+// (context creation allocates).  For them the split-K scratch of the dense kernel
+// lives in the fixed device array below, which every GPU that loads this library
+// holds until the process exits.  The array keeps whatever the previous call left in
+// it; only the arrival counters have to start at zero and they are cleared on the
+// caller's stream by every call.  Two calls that overlap on one GPU (different
+// streams, or different host threads) share the array and race.
+namespace logos {
+namespace {
+
+constexpr int kNoAllocMaxPairs = 4096;        // (sequence, head) pairs per call
+constexpr int kNoAllocMaxPartials = 16384;    // pairs x key splits x paths per call
+constexpr size_t kNoAllocCounterBytes = kNoAllocMaxPairs * sizeof(unsigned int);
+constexpr size_t kNoAllocBytes = kNoAllocCounterBytes + (size_t)kNoAllocMaxPartials * kPartial * sizeof(float);
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+struct NoAllocDevice {
+    void* scratch = nullptr;
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[kNoAllocMaxDevices];
+
+int noalloc_setup(int* dev_out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+        cudaGetLastError();
+        return LOGOS_ERR_NO_DEVICE;
+    }
+    *dev_out = dev;
+    if (g_noalloc_dev[dev].scratch) return LOGOS_OK;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+        cudaGetLastError();
+        return LOGOS_ERR_CUDA;
+    }
+    int sms = 0, major = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return LOGOS_ERR_CUDA;
+    }
+    if (major != 10) return LOGOS_ERR_NO_DEVICE;
+    g_noalloc_dev[dev].sm_count = sms;
+    g_noalloc_dev[dev].scratch = p;   // written last: a non-null pointer means set-up is complete
+    return LOGOS_OK;
+}
+
+}  // namespace
+}  // namespace logos
+
+extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_prev,
+                                         const int8_t* k_cache, const int8_t* v_cache,
+                                         const float* k_scale, const float* v_scale,
+                                         const int32_t* len, int B, int H, int S_max, int DH,
+                                         const logos_attn_params* p, float* out) {
+    using namespace logos;
+    if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || !out || !p || B <= 0 ||
+        H <= 0 || S_max <= 0)
+        return LOGOS_ERR_INVALID_ARG;
+    if (DH != kDH || p->window > 0) return LOGOS_ERR_UNSUPPORTED;   // dense contexts only
+    if (!aligned16(k_cache) || !aligned16(v_cache)) return LOGOS_ERR_ALIGNMENT;
+    if (p->diffuse_mode < 0 || p->diffuse_mode > 2 || p->ns_alpha < 0.0f || p->ns_alpha > 1.0f)
+        return LOGOS_ERR_INVALID_ARG;
+    if (p->ns_eta != 0.0f && p->ns_alpha > 0.0f && !q_prev) return LOGOS_ERR_INVALID_ARG;
+    int dev = 0;
+    int rc = noalloc_setup(&dev);
+    if (rc != LOGOS_OK) return rc;
+    const NoAllocDevice& nd = g_noalloc_dev[dev];
+
+    const bool ns_any = p->ns_alpha > 0.0f &&
+                        (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
+    const bool blend = ns_any && p->ns_alpha < 1.0f;
+    const int64_t BH = (int64_t)B * H;
+    if (BH > kNoAllocMaxPairs) return LOGOS_ERR_SCRATCH_LIMIT;
+    int chunk = kMaxChunk;   // same rule as the context entry point: about eight CTAs per SM
+    while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)nd.sm_count * 8) chunk >>= 1;
+    const int n_splits = (S_max + chunk - 1) / chunk;
+    if (BH * n_splits * (blend ? 2 : 1) > kNoAllocMaxPartials) return LOGOS_ERR_SCRATCH_LIMIT;
+
+    DecodeArgs a;
+    a.q = (const __half*)q; a.q_prev = (const __half*)q_prev;
+    a.k_cache = k_cache; a.v_cache = v_cache;
+    a.k_scale = k_scale; a.v_scale = v_scale;
+    a.len = len; a.out = out;
+    a.H = H; a.S_max = S_max; a.chunk = chunk;
+    a.scale = p->scale; a.window = 0; a.stride = 0;
+    a.eta = ns_any ? p->ns_eta : 0.0f;
+    a.nu = ns_any ? p->ns_nu : 0.0f;
+    a.diffuse_mode = ns_any ? p->diffuse_mode : LOGOS_DIFFUSE_NONE;
+    a.alpha = p->ns_alpha;
+    a.counters = (unsigned int*)nd.scratch;
+    a.partials = (float*)((char*)nd.scratch + kNoAllocCounterBytes);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    if (n_splits > 1 &&
+        cudaMemsetAsync(a.counters, 0, (size_t)BH * sizeof(unsigned int), st) != cudaSuccess) {
+        cudaGetLastError();
+        return LOGOS_ERR_CUDA;
+    }
+    dim3 grid(n_splits, (unsigned)BH);
+    if (blend) decode_dense_kernel<true><<<grid, kDenseThreads, 0, st>>>(a);
+    else       decode_dense_kernel<false><<<grid, kDenseThreads, 0, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? LOGOS_OK : LOGOS_ERR_CUDA;
+}

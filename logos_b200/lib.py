@@ -13,6 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "liblogos_attn.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_ALIGNMENT = range(7)
+ERR_SCRATCH_LIMIT = 7
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
 
@@ -56,6 +57,7 @@ SIGNATURES = {
     "logos_kv_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_decode_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
     "logos_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_decode_int8_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
     "logos_decode_step_int8_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                                         _i, _i, _PP, _vp]),
 }
