@@ -41,8 +41,9 @@ typedef enum {
     LOGOS_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed             */
     LOGOS_ERR_NO_DEVICE = 5,     /* no usable sm_100 device                          */
     LOGOS_ERR_ALIGNMENT = 6,     /* pointer or extent breaks a 16-byte requirement   */
-    LOGOS_ERR_SCRATCH_LIMIT = 7  /* request exceeds the fixed scratch of
+    LOGOS_ERR_SCRATCH_LIMIT = 7, /* request exceeds the fixed scratch of
                                     logos_decode_int8_noalloc                        */
+    LOGOS_ERR_KERNEL_TIMEOUT = 8 /* a bounded wait inside a kernel ran out           */
 } logos_status;
 
 typedef enum { LOGOS_F32 = 0, LOGOS_BF16 = 1, LOGOS_F16 = 2 } logos_dtype;
@@ -82,6 +83,10 @@ int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream);
 int logos_ctx_reserve(logos_ctx* ctx, size_t bytes);
 /* Uses caller memory as workspace instead (256-byte aligned device memory). */
 int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes);
+/* Waits for the context's stream and reports LOGOS_ERR_KERNEL_TIMEOUT if a kernel gave up
+ * on one of its bounded internal waits since the last check (its output is then invalid).
+ * The reference has no such channel: its kernels have no internal waits. */
+int logos_ctx_synchronize(logos_ctx* ctx);
 /* Text of the last failure on this context (owned by the context). */
 const char* logos_last_error(const logos_ctx* ctx);
 
@@ -106,6 +111,14 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
                         const void* V, void* O, int B, int H, int S, int DH,
                         const logos_attn_params* params);
 size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
+
+/* Hardware bring-up check of the tensor-core building blocks (TMA tile load with 128-byte
+ * swizzle, tcgen05.mma from shared-memory descriptors, TMEM read-back) on one 128-row tile;
+ * no counterpart in the reference.  dtype: LOGOS_BF16 or LOGOS_F16.
+ *   mode 0: D[128][128] = A[128][64] * B[128][64]^T        (the S = Q K^T operand layouts)
+ *   mode 1: D[128][64]  = A[128][128] * B[128][64]         (the O = W V operand layouts)
+ * D is fp32, row-major.  Check the result with logos_ctx_synchronize. */
+int logos_selftest_umma(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D);
 
 /* ---- Nikhilam INT8 KV cache --------------------------------------------- */
 

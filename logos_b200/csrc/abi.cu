@@ -1,5 +1,6 @@
 // abi.cu -- the extern "C" surface declared in include/logos_attn.h: context
 // management, argument checks and dispatch to the kernels.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -29,6 +30,7 @@ const char* logos_status_string(int status) {
         case LOGOS_ERR_CUDA: return "CUDA error";
         case LOGOS_ERR_NO_DEVICE: return "no sm_100 CUDA device";
         case LOGOS_ERR_ALIGNMENT: return "misaligned pointer or extent";
+        case LOGOS_ERR_KERNEL_TIMEOUT: return "a bounded wait inside a kernel ran out";
         case LOGOS_ERR_SCRATCH_LIMIT: return "request exceeds the fixed scratch of the no-allocation entry point";
     }
     return "unknown status";
@@ -56,6 +58,14 @@ int logos_ctx_create(int device, logos_ctx** out) {
         return LOGOS_ERR_CUDA;
     }
     ctx->absmax_slots = kAbsmaxSlots;
+    if (cudaMalloc(&ctx->tc_status, sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->tc_status, 0, sizeof(int)) != cudaSuccess) {
+        cudaFree(ctx->absmax_scratch);
+        delete ctx;
+        return LOGOS_ERR_CUDA;
+    }
+    const char* force = getenv("LOGOS_ATTN_FORCE_GENERAL");
+    ctx->force_general = force && force[0] == '1';
     *out = ctx;
     return LOGOS_OK;
 }
@@ -65,6 +75,7 @@ int logos_ctx_destroy(logos_ctx* ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->absmax_scratch) cudaFree(ctx->absmax_scratch);
+    if (ctx->tc_status) cudaFree(ctx->tc_status);
     delete ctx;
     return LOGOS_OK;
 }
@@ -109,6 +120,18 @@ int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes) {
     return LOGOS_OK;
 }
 
+int logos_ctx_synchronize(logos_ctx* ctx) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    int flag = 0;
+    LOGOS_CUDA_TRY(ctx, cudaMemcpy(&flag, ctx->tc_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+        cudaMemset(ctx->tc_status, 0, sizeof(int));
+        return logos::fail(ctx, LOGOS_ERR_KERNEL_TIMEOUT, "a bounded wait inside a kernel ran out; results of that call are invalid");
+    }
+    return LOGOS_OK;
+}
+
 const char* logos_last_error(const logos_ctx* ctx) { return ctx ? ctx->err : "null context"; }
 
 int logos_flash_attention_fwd_f32(logos_ctx* ctx, const float* Q, const float* K, const float* V,
@@ -135,6 +158,11 @@ int logos_flash_attention_fwd_f32(logos_ctx* ctx, const float* Q, const float* K
     return logos::attention_simt(ctx, LOGOS_F32, LOGOS_F32, Q, K, V, out, 1, 1, seq, DH, &p);
 }
 
+int logos_selftest_umma(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::umma_selftest(ctx, mode, dtype, A, B, D);
+}
+
 size_t logos_attention_workspace_bytes(int B, int H, int S, int DH) {
     (void)B; (void)H; (void)S; (void)DH;
     return 0;
@@ -150,6 +178,8 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: bad parameter block");
     if (!logos::dtype_ok(in_dtype) || !logos::dtype_ok(out_dtype))
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: unknown dtype");
+    if (!ctx->force_general && logos::attention_tc_eligible(in_dtype, out_dtype, DH, params, S))
+        return logos::attention_tc(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
     return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
 }
 

@@ -1,0 +1,662 @@
+// attn_tcgen05.cu -- causal / sliding-window prefill attention on the 5th-generation
+// tensor cores (tcgen05 + TMEM + TMA), BF16 or FP16 inputs, DH = 64.
+//
+// What it computes, per head: the attention of cuda_flash_attention_fwd
+// (cuda/VedicGEMM.cu:901-1062 of LOGOS) on Q_adv and V_s, where Q_adv is the advected
+// query (ns_advect_kernel, cuda/ModelGPU.cu:443-451) and V_s the causally diffused value
+// (ns_diffuse_kernel, cuda/ModelGPU.cu:463-471) -- both fused here, no extra pass:
+//   * Q_adv = Q + eta (Q - Q_prev) is formed once per CTA in fp32 from the TMA-loaded Q
+//     tile and the same tile loaded one row higher, and kept as an exact pair of 16-bit
+//     tiles (hi + lo), so QK^T costs two MMAs per k-step instead of a re-rounded Q_adv;
+//   * V_s is never formed: the stencil is moved onto the softmax weights,
+//       sum_j p_j V_s[j] = sum_r ((1-nu) p_r + nu p_{r+1}) V[r]   (+ nu p_0 V[0]),
+//     which a softmax thread applies to the row it holds in registers.  KV tiles are
+//     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
+//
+// CTA = one 128-row query tile of one head, 192 threads:
+//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t); reads S with
+//              tcgen05.ld, writes the weights to shared memory (128B-swizzled, K-major,
+//              in the type of V: FP16, or BF16 as an exact hi + lo pair) and finally
+//              O / l to global memory;
+//   warp 4     TMA producer (one lane): Q, Q_prev once, then K and V tiles into a
+//              two-stage ring;
+//   warp 5     MMA issuer (one lane): S = Q_adv K^T (M128 N128 K16 x 4 x {hi,lo}) into one of
+//              two TMEM buffers, O += W V (M128 N64 K16 x 8), completion via tcgen05.commit.
+// TMEM: columns [0,128) and [128,256) hold S (double-buffered), [256,320) hold O.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the CTA raises an abort
+// flag, all roles leave their loops, TMEM is freed and the status word tells the host.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace logos {
+namespace {
+
+constexpr int kBM = 128;              // query rows per CTA
+constexpr int kBN = 128;              // keys per tile
+constexpr int kD = 64;                // head dimension
+constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
+constexpr int kStages = 2;
+constexpr int kTcThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
+
+// shared memory map (bytes from a 1024-aligned base)
+constexpr int kOffQhi = 0;
+constexpr int kOffQlo = kOffQhi + kTileBytes;
+constexpr int kOffK = kOffQlo + kTileBytes;                    // kStages tiles
+constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
+constexpr int kOffP = kOffV + kStages * kTileBytes;            // weights 128 x 128 x 16 bit = 32 KiB
+constexpr int kOffP2 = kOffP + 2 * kTileBytes;                 // low half of the weights (BF16 inputs)
+constexpr int kOffBar = kOffP2 + 2 * kTileBytes;
+constexpr int kNumBars = 16;
+constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
+
+enum Bar { B_QLOAD = 0, B_QREADY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL0, B_SFULL1,
+           B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PVDONE };
+
+struct TcArgs {
+    void* O;
+    int S, out_is_f32, in_is_f16;
+    float c;            // scale * log2(e)
+    float eta, nu;
+    int diffuse;        // 0 none, 1 causal
+    int window;         // > 0: sliding window active (pure window, no landmarks)
+    int* status;        // device word: non-zero = a wait ran out
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// Bits: [0,14) start >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor for kind::f16 with fp32 accumulation, M = 128.
+// Bits: [4,6) D format (1 = F32), [7,10) A format, [10,13) B format (0 = F16, 1 = BF16),
+// 15 A major, 16 B major (0 = K, 1 = MN), [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int b_mn_major, int n) {
+    return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ float lo16_to_f32(uint32_t w, bool f16) {
+    return f16 ? __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)))
+               : __uint_as_float(w << 16);
+}
+__device__ __forceinline__ float hi16_to_f32(uint32_t w, bool f16) {
+    return f16 ? __half2float(__ushort_as_half((unsigned short)(w >> 16))) : __uint_as_float(w & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t f32_to_16(float x, bool f16) {
+    return f16 ? (uint32_t)__half_as_ushort(__float2half_rn(x))
+               : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ float from16(uint32_t h, bool f16) {
+    return f16 ? __half2float(__ushort_as_half((unsigned short)h)) : __uint_as_float(h << 16);
+}
+
+// -------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kTcThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                  const __grid_constant__ CUtensorMap mapV, const TcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + kOffBar;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBar + kNumBars * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + kNumBars * 8 + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query tiles first
+    const int bh = blockIdx.y;
+    const int q0 = qt * kBM;
+    const int S = a.S;
+    const bool f16 = a.in_is_f16 != 0;
+    const bool has_lo = a.eta != 0.0f;
+
+    // KV tiles visited: from the diagonal tile down to the first tile the window reaches
+    const int jt_hi = min(qt, (S - 1) / kBN);
+    // (one key below the window's first key still feeds the diffusion stencil)
+    const int jt_lo = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
+    const int n_tiles = jt_hi - jt_lo + 1;
+
+    if (tid == 0) {
+        mbar_init(bar(B_QLOAD), 1);
+        mbar_init(bar(B_QREADY), 128);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(B_KVFULL0 + s), 1);
+            mbar_init(bar(B_KVEMPTY0 + s), 1);
+            mbar_init(bar(B_SFULL0 + s), 1);
+            mbar_init(bar(B_SEMPTY0 + s), 128);
+        }
+        mbar_init(bar(B_PFULL), 128);
+        mbar_init(bar(B_PVDONE), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {   // TMEM allocation is warp-wide; this warp also frees it
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_S0 = tmem, tmem_O = tmem + 256;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            mbar_expect_tx(bar(B_QLOAD), has_lo ? 2 * kTileBytes : kTileBytes);
+            tma_load_3d(sbase + kOffQhi, &mapQ, 0, q0, bh, bar(B_QLOAD));
+            if (has_lo) tma_load_3d(sbase + kOffQlo, &mapQ, 0, q0 - 1, bh, bar(B_QLOAD));
+            for (int i = 0; i < n_tiles; ++i) {
+                const int st = i % kStages, jt = jt_hi - i;
+                if (i >= kStages && !mbar_wait(bar(B_KVEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(bar(B_KVFULL0 + st), 2 * kTileBytes);
+                tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KVFULL0 + st));
+                tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_KVFULL0 + st));
+            }
+        }
+    } else if (warp == 5) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            const int fmt = f16 ? 0 : 1;
+            const uint32_t idesc_qk = instr_desc(fmt, fmt, 0, kBN);
+            const uint32_t idesc_pv = instr_desc(fmt, fmt, 1 /* V is MN-major */, kD);
+            bool ok = mbar_wait(bar(B_QREADY), 0, abort_flag);
+            auto issue_pv = [&](int i) {   // O (+)= W(i) V(i)
+                const int st = i % kStages;
+                if (!mbar_wait(bar(B_PFULL), i & 1, abort_flag)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < kBN / 16; ++k) {
+                    // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom
+                    uint64_t ad = smem_desc(sbase + kOffP + (k >> 2) * kTileBytes + (k & 3) * 32);
+                    // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
+                    uint64_t bd = smem_desc(sbase + kOffV + st * kTileBytes + k * 2048);
+                    tc_mma_f16(tmem_O, ad, bd, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+                    if (!f16)   // BF16 weights travel as an exact hi + lo pair
+                        tc_mma_f16(tmem_O, smem_desc(sbase + kOffP2 + (k >> 2) * kTileBytes + (k & 3) * 32), bd,
+                                   idesc_pv, 1u);
+                }
+                tc_commit(bar(B_PVDONE));
+                tc_commit(bar(B_KVEMPTY0 + st));
+                return true;
+            };
+            for (int i = 0; ok && i < n_tiles; ++i) {
+                const int st = i % kStages, sb = i & 1;
+                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+                if (i >= 2 && !mbar_wait(bar(B_SEMPTY0 + sb), ((i >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_S0 + (uint32_t)sb * 128u;
+#pragma unroll
+                for (int k = 0; k < kD / 16; ++k) {
+                    uint64_t bd = smem_desc(sbase + kOffK + st * kTileBytes + k * 32);
+                    tc_mma_f16(d, smem_desc(sbase + kOffQhi + k * 32), bd, idesc_qk, k > 0 ? 1u : 0u);
+                    if (has_lo) tc_mma_f16(d, smem_desc(sbase + kOffQlo + k * 32), bd, idesc_qk, 1u);
+                }
+                tc_commit(bar(B_SFULL0 + sb));
+                if (i >= 1 && !issue_pv(i - 1)) { ok = false; break; }
+            }
+            if (ok) issue_pv(n_tiles - 1);
+        }
+    } else {
+        // ================= softmax warps: thread = query row =================
+        const int r = tid;                         // row in tile = TMEM lane
+        const int i_glob = q0 + r;
+        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        bool ok = mbar_wait(bar(B_QLOAD), 0, abort_flag);
+
+        // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place ----
+        if (ok && has_lo) {
+            unsigned char* qh = smem + kOffQhi + r * 128;
+            unsigned char* ql = smem + kOffQlo + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int pc = (c ^ (r & 7)) * 16;
+                uint4 cur = *reinterpret_cast<uint4*>(qh + pc);
+                uint4 prv = *reinterpret_cast<uint4*>(ql + pc);
+                uint32_t* cw = reinterpret_cast<uint32_t*>(&cur);
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&prv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float q_a = lo16_to_f32(cw[e], f16), q_b = hi16_to_f32(cw[e], f16);
+                    float p_a = (i_glob > 0) ? lo16_to_f32(pw[e], f16) : q_a;
+                    float p_b = (i_glob > 0) ? hi16_to_f32(pw[e], f16) : q_b;
+                    float a_a = q_a + a.eta * (q_a - p_a), a_b = q_b + a.eta * (q_b - p_b);
+                    uint32_t h_a = f32_to_16(a_a, f16), h_b = f32_to_16(a_b, f16);
+                    uint32_t l_a = f32_to_16(a_a - from16(h_a, f16), f16);
+                    uint32_t l_b = f32_to_16(a_b - from16(h_b, f16), f16);
+                    cw[e] = h_a | (h_b << 16);
+                    pw[e] = l_a | (l_b << 16);
+                }
+                *reinterpret_cast<uint4*>(qh + pc) = cur;
+                *reinterpret_cast<uint4*>(ql + pc) = prv;
+            }
+            fence_async_smem();
+        }
+        mbar_arrive(bar(B_QREADY));
+
+        float m_run = -INFINITY;     // running reference maximum (log2 domain)
+        float l_run = 0.0f;          // running sum of the (rounded) weights
+        float s_carry = -INFINITY;   // scaled score of the first key of the tile above
+        const float c = a.c;
+        const float nu = (a.diffuse == 1) ? a.nu : 0.0f;
+        const float one_m_nu = 1.0f - nu;
+
+        for (int i = 0; ok && i < n_tiles; ++i) {
+            const int sb = i & 1, jt = jt_hi - i, k0 = jt * kBN;
+            if (!mbar_wait(bar(B_SFULL0 + sb), (i >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            float s[kBN];
+            const uint32_t ts = tmem_S0 + (uint32_t)sb * 128u + lane_addr;
+            tc_ld32(ts, s);
+            tc_ld32(ts + 32, s + 32);
+            tc_ld32(ts + 64, s + 64);
+            tc_ld32(ts + 96, s + 96);
+            tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(B_SEMPTY0 + sb));
+
+            // scale into the log2 domain and mask
+            const bool edge = (k0 + kBN - 1 > q0) || (k0 + kBN > S) || (a.window > 0 && k0 < q0 + kBM - 1 - a.window);
+            float mx = -INFINITY;
+            if (edge) {
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) {
+                    const int jg = k0 + j;
+                    const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
+                    s[j] = allowed ? s[j] * c : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) {
+                    s[j] *= c;
+                    mx = fmaxf(mx, s[j]);
+                }
+            }
+            // move the reference maximum only when it would grow by more than the threshold
+            // (weights stay below 2^8, well inside FP16); the decision is warp-wide because
+            // the O correction is a warp-collective TMEM access
+            const bool want = (mx > m_run + kRescaleThreshold) || (m_run == -INFINITY && mx > -INFINITY);
+            const bool any = __any_sync(0xffffffffu, want && i > 0 && m_run > -INFINITY);
+            float m_new = want ? mx : m_run;
+            if (any && m_new < mx) m_new = mx;       // correcting anyway: take the exact maximum
+            // before touching O or the weight buffer the previous O += W V must be complete
+            if (i > 0 && !mbar_wait(bar(B_PVDONE), (i - 1) & 1, abort_flag)) { ok = false; break; }
+            if (any) {
+                tc_fence_after();
+                const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
+                float o[32];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    tc_ld32(tmem_O + lane_addr + 32 * h, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= f;
+                    tc_st32(tmem_O + lane_addr + 32 * h, o);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                l_run *= f;
+            } else if (m_run == -INFINITY) {
+                l_run = 0.0f;
+            }
+            m_run = m_new;
+
+            // weights with the diffusion stencil folded in, in the type of V (the MMA takes one
+            // type for both operands): FP16 directly, BF16 as hi + lo; row sum of what was stored
+            const float p_above = (s_carry > -INFINITY && m_run > -INFINITY) ? ex2(s_carry - m_run) : 0.0f;
+            s_carry = s[0];
+            unsigned char* prow = smem + kOffP + r * 128;
+            float nxt = p_above;                       // p of key j+1 while walking down from j = 127
+            float lsum = 0.0f;
+#pragma unroll
+            for (int ch = 15; ch >= 0; --ch) {        // 16-byte chunks of 8 keys, highest first
+                uint32_t w[4], w2[4];
+#pragma unroll
+                for (int e = 3; e >= 0; --e) {
+                    const int j1 = ch * 8 + 2 * e + 1, j0 = j1 - 1;
+                    const float p1 = (m_run > -INFINITY) ? ex2(s[j1] - m_run) : 0.0f;
+                    const float p0 = (m_run > -INFINITY) ? ex2(s[j0] - m_run) : 0.0f;
+                    float w1 = one_m_nu * p1 + nu * nxt;
+                    float w0 = one_m_nu * p0 + nu * p1;
+                    if (k0 + j0 == 0) w0 += nu * p0;  // V_s[0] = V[0]
+                    nxt = p0;
+                    if (f16) {
+                        __half2 hw = __floats2half2_rn(w0, w1);
+                        float2 back = __half22float2(hw);
+                        lsum += back.x + back.y;
+                        w[e] = *reinterpret_cast<uint32_t*>(&hw);
+                    } else {
+                        const uint32_t h0 = f32_to_16(w0, false), h1 = f32_to_16(w1, false);
+                        const float r0 = w0 - from16(h0, false), r1 = w1 - from16(h1, false);
+                        const uint32_t g0 = f32_to_16(r0, false), g1 = f32_to_16(r1, false);
+                        lsum += (from16(h0, false) + from16(g0, false)) + (from16(h1, false) + from16(g1, false));
+                        w[e] = h0 | (h1 << 16);
+                        w2[e] = g0 | (g1 << 16);
+                    }
+                }
+                const int atom = ch >> 3, cc = ch & 7;
+                *reinterpret_cast<uint4*>(prow + atom * kTileBytes + ((cc ^ (r & 7)) * 16)) =
+                    make_uint4(w[0], w[1], w[2], w[3]);
+                if (!f16)
+                    *reinterpret_cast<uint4*>(prow + (kOffP2 - kOffP) + atom * kTileBytes + ((cc ^ (r & 7)) * 16)) =
+                        make_uint4(w2[0], w2[1], w2[2], w2[3]);
+            }
+            l_run += lsum;
+            fence_async_smem();
+            mbar_arrive(bar(B_PFULL));
+        }
+
+        // ---- epilogue: O / l ----
+        if (ok && mbar_wait(bar(B_PVDONE), (n_tiles - 1) & 1, abort_flag)) {
+            tc_fence_after();
+            float o[64];
+            tc_ld32(tmem_O + lane_addr, o);
+            tc_ld32(tmem_O + lane_addr + 32, o + 32);
+            tc_wait_ld();
+            tc_fence_before();
+            if (i_glob < S) {
+                const float inv = (l_run > 1e-9f) ? 1.0f / l_run : 0.0f;   // cuda/VedicGEMM.cu:1049
+                const size_t row = ((size_t)bh * S + i_glob) * kD;
+                if (a.out_is_f32) {
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+                } else {
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
+                        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: every role comes here, aborted or not ----
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(a.status, 1);
+    if (warp == 5) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// -------------------------------------------------------------------------------------
+// Bring-up check of the building blocks above on one 128-row tile, one CTA, 128 threads.
+//   mode 0: D[128 x 128] = A[128 x 64] B[128 x 64]^T   A, B by TMA, both K-major (the S = Q K^T shape)
+//   mode 1: D[128 x 64]  = A[128 x 128] B[128 x 64]    A written by the threads into the swizzled
+//           K-major layout, B by TMA and used MN-major (the O = W V shape)
+__global__ void __launch_bounds__(128, 1)
+umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                     const unsigned short* __restrict__ a_rows, float* __restrict__ D, int mode, int fmt,
+                     int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    constexpr int offA = 0, offB = 2 * kTileBytes, offBar = 3 * kTileBytes;
+    const uint32_t bar_load = sbase + offBar, bar_mma = sbase + offBar + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + offBar + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + offBar + 32);
+    const int tid = threadIdx.x, warp = tid >> 5;
+
+    if (tid == 0) {
+        mbar_init(bar_load, 1);
+        mbar_init(bar_mma, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(128u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (tid == 0) {
+        mbar_expect_tx(bar_load, mode == 0 ? 2 * kTileBytes : kTileBytes);
+        if (mode == 0) tma_load_3d(sbase + offA, &mapA, 0, 0, 0, bar_load);
+        tma_load_3d(sbase + offB, &mapB, 0, 0, 0, bar_load);
+    }
+    if (mode == 1) {   // row tid of A: 128 values = 16 chunks of 16 bytes, two 64-column atoms
+        const uint4* src = reinterpret_cast<const uint4*>(a_rows + (size_t)tid * 128);
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) {
+            const int atom = ch >> 3, cc = ch & 7;
+            *reinterpret_cast<uint4*>(smem + offA + atom * kTileBytes + tid * 128 + ((cc ^ (tid & 7)) * 16)) = src[ch];
+        }
+        fence_async_smem();
+    }
+    bool ok = mbar_wait(bar_load, 0, abort_flag);
+    __syncthreads();
+    if (tid == 0 && ok) {
+        tc_fence_after();
+        if (mode == 0) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 0, 128);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                tc_mma_f16(tmem, smem_desc(sbase + offA + k * 32), smem_desc(sbase + offB + k * 32), idesc, k > 0 ? 1u : 0u);
+        } else {
+            const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                tc_mma_f16(tmem, smem_desc(sbase + offA + (k >> 2) * kTileBytes + (k & 3) * 32),
+                           smem_desc(sbase + offB + k * 2048), idesc, k > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_mma);
+    }
+    ok = ok && mbar_wait(bar_mma, 0, abort_flag);
+    if (ok) {
+        tc_fence_after();
+        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        const int ncol = mode == 0 ? 128 : 64;
+        float v[32];
+        for (int c0 = 0; c0 < ncol; c0 += 32) {
+            tc_ld32(tmem + lane_addr + c0, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) D[(size_t)tid * ncol + c0 + j] = v[j];
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(status, 1);
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// [BH][S][64] 16-bit tensor, box = 128 rows x 64 channels of one head, 128-byte swizzle
+bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)S, (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)S * kD * 2};
+    cuuint32_t box[3] = {(cuuint32_t)kD, (cuuint32_t)kBM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
+    if (!A || !B || !D || (mode != 0 && mode != 1) || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "selftest: bad argument");
+    const bool f16 = dtype == LOGOS_F16;
+    CUtensorMap ma, mb;
+    // mode 1 does not load A by TMA; its map then simply aliases B's
+    if (!make_map(&ma, mode == 0 ? A : B, 1, kBM, f16) || !make_map(&mb, B, 1, kBM, f16))
+        return fail(ctx, LOGOS_ERR_CUDA, "selftest: cuTensorMapEncodeTiled failed");
+    const int smem = 3 * kTileBytes + 64 + 1024;
+    LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    umma_selftest_kernel<<<1, 128, smem, ctx->stream>>>(ma, mb, (const unsigned short*)A, D, mode, f16 ? 0 : 1,
+                                                        ctx->tc_status);
+    LOGOS_LAUNCH_CHECK(ctx, "umma_selftest_kernel");
+    return LOGOS_OK;
+}
+
+bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S) {
+    if (DH != kD) return false;
+    if (in_dtype != LOGOS_BF16 && in_dtype != LOGOS_F16) return false;
+    if (out_dtype != in_dtype && out_dtype != LOGOS_F32) return false;
+    if (!p->causal) return false;
+    const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
+    if (ns_any && p->ns_alpha < 1.0f) return false;                 // blend: two attention passes
+    if (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CENTRAL) return false;
+    if (ns_any && (p->ns_nu < 0.0f || p->ns_nu > 1.0f)) return false;
+    if (shunyam_active(p->window, S) && p->stride > 0) return false;  // landmarks: general kernel
+    return true;
+}
+
+int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
+                 void* O, int B, int H, int S, int DH, const logos_attn_params* p) {
+    (void)DH;
+    const int BH = B * H;
+    if (BH > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention: B*H > 65535");
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O))
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "attention: tensors must be 16-byte aligned");
+    if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "attention: status word missing");
+    const bool f16 = in_dtype == LOGOS_F16;
+    CUtensorMap mq, mk, mv;
+    if (!make_map(&mq, Q, BH, S, f16) || !make_map(&mk, K, BH, S, f16) || !make_map(&mv, V, BH, S, f16))
+        return fail(ctx, LOGOS_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed");
+    const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
+    TcArgs a;
+    a.O = O; a.S = S;
+    a.out_is_f32 = out_dtype == LOGOS_F32;
+    a.in_is_f16 = f16;
+    a.c = p->scale * 1.4426950408889634f;
+    a.eta = ns_any ? p->ns_eta : 0.0f;
+    a.nu = ns_any ? p->ns_nu : 0.0f;
+    a.diffuse = (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CAUSAL) ? 1 : 0;
+    a.window = shunyam_active(p->window, S) ? p->window : 0;
+    a.status = ctx->tc_status;
+    LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    dim3 grid((S + kBM - 1) / kBM, BH);
+    prefill_tc_kernel<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
+    LOGOS_LAUNCH_CHECK(ctx, "prefill_tc_kernel");
+    return LOGOS_OK;
+}
+
+}  // namespace logos

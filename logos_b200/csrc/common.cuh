@@ -21,6 +21,8 @@ struct logos_ctx {
     bool owns_workspace = false;
     float* absmax_scratch = nullptr;  // per-tensor absmax words for kv_quantize
     int absmax_slots = 0;
+    int* tc_status = nullptr;         // device word raised by a kernel whose bounded wait ran out
+    bool force_general = false;       // LOGOS_ATTN_FORCE_GENERAL=1: never use the tensor-core prefill kernel
     char err[512] = {0};
 };
 
@@ -112,4 +114,8 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
                    const logos_attn_params*);
+int umma_selftest(logos_ctx*, int mode, int dtype, const void* A, const void* B, float* D);
+bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
+int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
+                 void* O, int B, int H, int S, int DH, const logos_attn_params*);
 }  // namespace logos

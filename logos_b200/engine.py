@@ -54,6 +54,10 @@ class Engine:
     def use_stream(self, stream: torch.cuda.Stream):
         self._check(self.lib.logos_ctx_set_stream(self.h, C.c_void_p(stream.cuda_stream)))
 
+    def synchronize(self):
+        """Waits for the stream; raises if a kernel reported that one of its internal waits ran out."""
+        self._check(self.lib.logos_ctx_synchronize(self.h))
+
     def reserve(self, nbytes: int):
         self._check(self.lib.logos_ctx_reserve(self.h, int(nbytes)))
 

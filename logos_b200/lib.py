@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(PKG, "liblogos_attn.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_ALIGNMENT = range(7)
 ERR_SCRATCH_LIMIT = 7
+ERR_KERNEL_TIMEOUT = 8
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
 
@@ -48,9 +49,11 @@ SIGNATURES = {
     "logos_ctx_set_stream": (_i, [_vp, _vp]),
     "logos_ctx_reserve": (_i, [_vp, _sz]),
     "logos_ctx_set_workspace": (_i, [_vp, _vp, _sz]),
+    "logos_ctx_synchronize": (_i, [_vp]),
     "logos_last_error": (C.c_char_p, [_vp]),
     "logos_flash_attention_fwd_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),
     "logos_attention_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
+    "logos_selftest_umma": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "logos_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_kv_quantize": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i, _i64]),
     "logos_kv_dequantize": (_i, [_vp, _vp, _i64, _vp, _vp, _i64, _i, _i64]),

@@ -27,3 +27,18 @@ def engine():
     eng = Engine(0)
     yield eng
     eng.close()
+
+
+@pytest.fixture(scope="session")
+def engine_general():
+    """A context that never takes the tensor-core prefill kernel (exact fp32 arithmetic path)."""
+    import torch
+    from logos_b200.engine import Engine
+    assert torch.cuda.is_available(), "gpu tests need a CUDA device"
+    os.environ["LOGOS_ATTN_FORCE_GENERAL"] = "1"
+    try:
+        eng = Engine(0)
+    finally:
+        del os.environ["LOGOS_ATTN_FORCE_GENERAL"]
+    yield eng
+    eng.close()

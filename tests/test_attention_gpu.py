@@ -94,7 +94,8 @@ CASES = [
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("S", [1, 33, 64, 65, 200])
-def test_batched_all_switches(engine, dtype, S):
+def test_batched_all_switches(engine_general, dtype, S):
+    engine = engine_general
     B, H, DH = 2, 3, 64
     Q, K, V = (syn.normal((B, H, S, DH), 2, t) for t in (1, 2, 3))
     K[syn.normal((B, H, S, DH), 2, 9) > 2.3] *= 8

@@ -1,0 +1,44 @@
+"""Bring-up check of the tcgen05 / TMA / TMEM building blocks on one tile, through the C ABI.
+Each case runs in the order a bring-up needs: the K-major x K-major product first, then the
+K-major x MN-major one."""
+import pytest
+import torch
+
+from logos_b200 import lib as L
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(engine, mode, dtype):
+    g = torch.Generator(device="cuda").manual_seed(7 + mode)
+    code = L.BF16 if dtype == torch.bfloat16 else L.F16
+    if mode == 0:
+        A = torch.randn((128, 64), device="cuda", generator=g).to(dtype)
+        B = torch.randn((128, 64), device="cuda", generator=g).to(dtype)
+        want = A.float() @ B.float().T
+    else:
+        A = torch.rand((128, 128), device="cuda", generator=g).to(dtype)
+        B = torch.randn((128, 64), device="cuda", generator=g).to(dtype)
+        want = A.float() @ B.float()
+    D = torch.full(want.shape, float("nan"), device="cuda")
+    rc = engine.lib.logos_selftest_umma(engine.h, mode, code, A.data_ptr(), B.data_ptr(), D.data_ptr())
+    assert rc == L.OK, engine.lib.logos_last_error(engine.h)
+    engine.synchronize()
+    err = (D - want).abs().max().item()
+    assert err < 1e-3, f"mode {mode} {dtype}: max-abs {err}"
+
+
+def test_qk_shape_bf16(engine):
+    _run(engine, 0, torch.bfloat16)
+
+
+def test_pv_shape_bf16(engine):
+    _run(engine, 1, torch.bfloat16)
+
+
+def test_qk_shape_f16(engine):
+    _run(engine, 0, torch.float16)
+
+
+def test_pv_shape_f16(engine):
+    _run(engine, 1, torch.float16)
