@@ -172,6 +172,68 @@ def run_reference(args) -> None:
     print(json.dumps(base))
 
 
+PREFILL = {"name": "causal_prefill_b4_h16_s4096_dh64_bf16", "B": 4, "S": 4096, "window": 0, "outliers": False}
+WINDOW = {"name": "shunyam_window64_b8_h16_s8192_dh64_bf16", "B": 8, "S": 8192, "window": 64, "outliers": True}
+
+
+def measured_peak_tflops():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured burst"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_over_ranks) -> dict:
+    """Device-resident prefill / window attention over this rank's heads (BF16 in, BF16 out,
+    Navier-Stokes prologue fused: eta 0.1, causal diffusion nu 0.05), outputs all-gathered."""
+    import torch
+    from logos_b200 import lib as L
+    from logos_b200.sharding import all_gather_heads, head_range
+    lo, hi = head_range(H, rank, world)
+    Hl, Bc, S = hi - lo, cfg["B"], cfg["S"]
+    g = torch.Generator(device=dev).manual_seed(2000 + rank)
+    sets = []
+    for _ in range(2):   # two input sets in rotation: a pass never finds its inputs in L2
+        Q, K, V = (torch.randn((Bc, Hl, S, DH), device=dev, generator=g) for _ in range(3))
+        if cfg["outliers"]:
+            K[torch.rand(K.shape, device=dev, generator=g) < 0.01] *= 8
+        sets.append(tuple(t.bfloat16() for t in (Q, K, V)))
+        del Q, K, V
+    O = torch.empty((Bc, Hl, S, DH), dtype=torch.bfloat16, device=dev)
+    p = L.Params.make(1.0 / 8.0, True, cfg["window"], 0, ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
+
+    def step(i):
+        Q, K, V = sets[i % 2]
+        eng.attention(Q, K, V, p, out=O)
+        if world > 1:
+            all_gather_heads(O, world)
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for i in range(steps):
+        step(warmup + i)
+    ev[1].record()
+    barrier()
+    eng.synchronize()
+    ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / steps)
+    out = {"workload": cfg["name"], "ms_per_step": ms, "n_gpus": world}
+    if cfg["window"]:
+        nbytes = 4 * Bc * H * S * DH * 2                       # Q, K, V read once, O written once
+        peak, kind = measured_peak_gbs()
+        out.update({"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "bound": "hbm", "peak": peak,
+                    "peak_kind": kind, "frac": nbytes / (ms * 1e-3) / 1e9 / (peak * world)})
+    else:
+        flops = 4.0 * Bc * H * S * S * DH / 2                  # causal-halved convention
+        peak, kind = measured_peak_tflops()
+        out.update({"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (causal-halved)", "bound": "tensor",
+                    "peak": peak, "peak_kind": kind, "frac": flops / (ms * 1e-3) / 1e12 / (peak * world)})
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -194,6 +256,36 @@ def run_ours(args) -> None:
     eng = Engine(local_rank)
     lo, hi = head_range(H, rank, world)
     Hl = hi - lo
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.workload in ("prefill", "window"):
+        cfg = dict(PREFILL if args.workload == "prefill" else WINDOW)
+        if args.batch != 64:   # profiling case: fewer sequences than the configuration
+            cfg["B"] = args.batch
+            cfg["name"] += f"_batch{args.batch}"
+        r = measure_attention(eng, dev, world, rank, cfg, args.steps, args.warmup, barrier, max_over_ranks)
+        if rank == 0:
+            print(json.dumps({"metric": cfg["name"], "value": r["value"], "unit": r["unit"], "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                              "data": "synthetic", "config": {"workload": cfg["name"]},
+                              "roofline": {"bound": r["bound"], "achieved": r["value"], "peak": r["peak"],
+                                           "peak_kind": r["peak_kind"], "frac": r["frac"], "traffic": None},
+                              "gpu_launches": args.steps}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- caches: enough independent sets that a pass never finds its bytes in L2 ----
     per_set = 2 * B * Hl * S_MAX * DH
@@ -224,18 +316,6 @@ def run_ours(args) -> None:
     hq, hqp, hkn, hvn = (t.cpu().pin_memory() for t in (q, qp, kn, vn))
     hlens = lens.cpu().pin_memory()
     hout = torch.empty((B, H, DH), dtype=torch.float32).pin_memory()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
     # ---- device-resident step: `value` ----
     for i in range(args.warmup):
@@ -295,6 +375,12 @@ def run_ours(args) -> None:
                      "kernel_ms": kern_ms, "traffic": None},
         "clocks": clocks,
     }
+    if not args.no_secondary:
+        # the other two kernels of the path, device-resident, a few steps each
+        del decoders
+        torch.cuda.empty_cache()
+        line["secondary"] = [measure_attention(eng, dev, world, rank, cfg, max(3, args.steps // 4), 3, barrier,
+                                               max_over_ranks) for cfg in (PREFILL, WINDOW)]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_port_baseline()
@@ -310,6 +396,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "window"],
+                    help="decode is the benchmark; prefill / window time the other kernels alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()

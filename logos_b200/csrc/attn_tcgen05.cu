@@ -13,16 +13,17 @@
 //     which a softmax thread applies to the row it holds in registers.  KV tiles are
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
-// CTA = one 128-row query tile of one head, 192 threads:
-//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t); reads S with
-//              tcgen05.ld, writes the weights to shared memory (128B-swizzled, K-major,
-//              in the type of V: FP16, or BF16 as an exact hi + lo pair) and finally
-//              O / l to global memory;
-//   warp 4     TMA producer (one lane): Q, Q_prev once, then K and V tiles into a
-//              two-stage ring;
-//   warp 5     MMA issuer (one lane): S = Q_adv K^T (M128 N128 K16 x 4 x {hi,lo}) into one of
-//              two TMEM buffers, O += W V (M128 N64 K16 x 8), completion via tcgen05.commit.
-// TMEM: columns [0,128) and [128,256) hold S (double-buffered), [256,320) hold O.
+// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 320 threads:
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: thread t owns query row t (= TMEM lane t); reads S
+//              with tcgen05.ld, writes FP16 weights to shared memory (128B-swizzled, K-major) and
+//              finally O / l to global memory.  The MMA takes one type for both operands, so for
+//              BF16 inputs the same threads first turn the V tile into FP16 in place (exact in
+//              FP16's normal range, saturating beyond it);
+//   warp 8     TMA producer (one lane): Q, Q_prev once, then K and V tiles into a two-stage ring;
+//   warp 9     MMA issuer (one lane): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
+//              (M128 N64 K16 x 8), completion via tcgen05.commit; the scores of the next tile are
+//              issued before the current tile's weights are waited for.
+// TMEM: columns [0,128) / [128,256) hold S of tile 0 / 1, [256,320) / [320,384) hold O.
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA raises an abort
 // flag, all roles leave their loops, TMEM is freed and the status word tells the host.
@@ -33,29 +34,29 @@
 namespace logos {
 namespace {
 
-constexpr int kBM = 128;              // query rows per CTA
+constexpr int kBM = 128;              // rows of one query tile (= TMEM lanes)
+constexpr int kBQ = 256;              // query rows per CTA: two tiles that share every K/V tile
 constexpr int kBN = 128;              // keys per tile
 constexpr int kD = 64;                // head dimension
 constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
 constexpr int kStages = 2;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;       // 8 softmax warps + TMA warp + MMA warp
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr int kOffQhi = 0;
-constexpr int kOffQlo = kOffQhi + kTileBytes;
-constexpr int kOffK = kOffQlo + kTileBytes;                    // kStages tiles
+constexpr int kOffQ = 0;                                       // per query tile: hi, lo (4 tiles)
+constexpr int kOffK = kOffQ + 4 * kTileBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffP = kOffV + kStages * kTileBytes;            // weights 128 x 128 x 16 bit = 32 KiB
-constexpr int kOffP2 = kOffP + 2 * kTileBytes;                 // low half of the weights (BF16 inputs)
-constexpr int kOffBar = kOffP2 + 2 * kTileBytes;
-constexpr int kNumBars = 16;
+constexpr int kOffP = kOffV + kStages * kTileBytes;            // per query tile: 128 x 128 FP16 weights = 32 KiB
+constexpr int kOffBar = kOffP + 4 * kTileBytes;
+constexpr int kNumBars = 20;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
-enum Bar { B_QLOAD = 0, B_QREADY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_SFULL0, B_SFULL1,
-           B_SEMPTY0, B_SEMPTY1, B_PFULL, B_PVDONE };
+enum Bar { B_QLOAD = 0, B_QREADY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_VREADY0, B_VREADY1,
+           B_SFULL0, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1 };
 
 struct TcArgs {
     void* O;
@@ -180,6 +181,7 @@ __device__ __forceinline__ float from16(uint32_t h, bool f16) {
 }
 
 // -------------------------------------------------------------------------------------
+template <bool DIFF>
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const TcArgs a) {
@@ -192,34 +194,51 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + kNumBars * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query tiles first
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query blocks first
     const int bh = blockIdx.y;
-    const int q0 = qt * kBM;
+    const int q0 = qb * kBQ;                               // first row of query tile 0; tile 1 starts 128 later
     const int S = a.S;
     const bool f16 = a.in_is_f16 != 0;
     const bool has_lo = a.eta != 0.0f;
 
-    // KV tiles visited: from the diagonal tile down to the first tile the window reaches
-    const int jt_hi = min(qt, (S - 1) / kBN);
-    // (one key below the window's first key still feeds the diffusion stencil)
-    const int jt_lo = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
-    const int n_tiles = jt_hi - jt_lo + 1;
+    // Global iteration i visits KV tile jt_hi - i.  Query tile g (rows q0 + 128 g ...) takes part in
+    // iterations [i_first[g], i_last[g]]: above its diagonal and below its window it has nothing to do.
+    const int jt_max = (S - 1) / kBN;
+    const int jt_hi = min((q0 + kBQ - 1) / kBN, jt_max);
+    int jt_top[2], jt_bot[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const int r0 = q0 + g * kBM;
+        jt_top[g] = min(r0 / kBN, jt_max);                                   // diagonal tile of this query tile
+        jt_bot[g] = (a.window > 0) ? max(0, r0 - a.window - 1) / kBN : 0;    // one key below the window feeds the stencil
+    }
+    const int jt_lo = min(jt_bot[0], jt_bot[1]);
+    const int n_iter = jt_hi - jt_lo + 1;
+    const bool tile1_live = (q0 + kBM) < S;                // query tile 1 may lie wholly beyond the sequence
+    auto active = [&](int g, int i) {
+        const int jt = jt_hi - i;
+        return (g == 0 || tile1_live) && jt <= jt_top[g] && jt >= jt_bot[g];
+    };
+    auto first_iter = [&](int g) { return jt_hi - jt_top[g]; };
 
     if (tid == 0) {
         mbar_init(bar(B_QLOAD), 1);
-        mbar_init(bar(B_QREADY), 128);
+        mbar_init(bar(B_QREADY), 256);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_KVFULL0 + s), 1);
             mbar_init(bar(B_KVEMPTY0 + s), 1);
-            mbar_init(bar(B_SFULL0 + s), 1);
-            mbar_init(bar(B_SEMPTY0 + s), 128);
+            mbar_init(bar(B_VREADY0 + s), 256);
         }
-        mbar_init(bar(B_PFULL), 128);
-        mbar_init(bar(B_PVDONE), 1);
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(bar(B_SFULL0 + g), 1);
+            mbar_init(bar(B_SEMPTY0 + g), 128);
+            mbar_init(bar(B_PFULL0 + g), 128);
+            mbar_init(bar(B_PVDONE0 + g), 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {   // TMEM allocation is warp-wide; this warp also frees it
+    if (warp == kMmaWarp) {   // TMEM allocation is warp-wide; this warp also frees it
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(kTmemCols)
                      : "memory");
@@ -229,15 +248,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_S0 = tmem, tmem_O = tmem + 256;
+    // columns: S of tile 0 [0,128), S of tile 1 [128,256), O of tile 0 [256,320), O of tile 1 [320,384)
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            mbar_expect_tx(bar(B_QLOAD), has_lo ? 2 * kTileBytes : kTileBytes);
-            tma_load_3d(sbase + kOffQhi, &mapQ, 0, q0, bh, bar(B_QLOAD));
-            if (has_lo) tma_load_3d(sbase + kOffQlo, &mapQ, 0, q0 - 1, bh, bar(B_QLOAD));
-            for (int i = 0; i < n_tiles; ++i) {
+            const int nq = (has_lo ? 2 : 1) * (tile1_live ? 2 : 1);
+            mbar_expect_tx(bar(B_QLOAD), nq * kTileBytes);
+            for (int g = 0; g < (tile1_live ? 2 : 1); ++g) {
+                tma_load_3d(sbase + kOffQ + (2 * g) * kTileBytes, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD));
+                if (has_lo)
+                    tma_load_3d(sbase + kOffQ + (2 * g + 1) * kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD));
+            }
+            for (int i = 0; i < n_iter; ++i) {
                 const int st = i % kStages, jt = jt_hi - i;
                 if (i >= kStages && !mbar_wait(bar(B_KVEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(bar(B_KVFULL0 + st), 2 * kTileBytes);
@@ -245,60 +268,76 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_KVFULL0 + st));
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ================= MMA issuer =================
         if (lane == 0) {
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_qk = instr_desc(fmt, fmt, 0, kBN);
-            const uint32_t idesc_pv = instr_desc(fmt, fmt, 1 /* V is MN-major */, kD);
+            const uint32_t idesc_pv = instr_desc(0, 0, 1 /* V is MN-major */, kD);   // FP16 weights x FP16 V
             bool ok = mbar_wait(bar(B_QREADY), 0, abort_flag);
-            auto issue_pv = [&](int i) {   // O (+)= W(i) V(i)
-                const int st = i % kStages;
-                if (!mbar_wait(bar(B_PFULL), i & 1, abort_flag)) return false;
+            auto issue_qk = [&](int g, int i) {   // S_g = Q_adv,g K(i)^T
+                const int st = i % kStages, k = i - first_iter(g);
+                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) return false;
+                if (k > 0 && !mbar_wait(bar(B_SEMPTY0 + g), (k - 1) & 1, abort_flag)) return false;
                 tc_fence_after();
+                const uint32_t d = tmem + (uint32_t)g * 128u;
+                const uint32_t qhi = sbase + kOffQ + (2 * g) * kTileBytes, qlo = qhi + kTileBytes;
 #pragma unroll
-                for (int k = 0; k < kBN / 16; ++k) {
-                    // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom
-                    uint64_t ad = smem_desc(sbase + kOffP + (k >> 2) * kTileBytes + (k & 3) * 32);
-                    // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
-                    uint64_t bd = smem_desc(sbase + kOffV + st * kTileBytes + k * 2048);
-                    tc_mma_f16(tmem_O, ad, bd, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-                    if (!f16)   // BF16 weights travel as an exact hi + lo pair
-                        tc_mma_f16(tmem_O, smem_desc(sbase + kOffP2 + (k >> 2) * kTileBytes + (k & 3) * 32), bd,
-                                   idesc_pv, 1u);
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint64_t bd = smem_desc(sbase + kOffK + st * kTileBytes + kk * 32);
+                    tc_mma_f16(d, smem_desc(qhi + kk * 32), bd, idesc_qk, kk > 0 ? 1u : 0u);
+                    if (has_lo) tc_mma_f16(d, smem_desc(qlo + kk * 32), bd, idesc_qk, 1u);
                 }
-                tc_commit(bar(B_PVDONE));
-                tc_commit(bar(B_KVEMPTY0 + st));
+                tc_commit(bar(B_SFULL0 + g));
                 return true;
             };
-            for (int i = 0; ok && i < n_tiles; ++i) {
-                const int st = i % kStages, sb = i & 1;
-                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
-                if (i >= 2 && !mbar_wait(bar(B_SEMPTY0 + sb), ((i >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+            auto issue_pv = [&](int g, int i) {   // O_g (+)= W_g(i) V(i)
+                const int st = i % kStages, k = i - first_iter(g);
+                if (!mbar_wait(bar(B_PFULL0 + g), k & 1, abort_flag)) return false;
+                if (!f16 && !mbar_wait(bar(B_VREADY0 + st), (i / kStages) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t d = tmem_S0 + (uint32_t)sb * 128u;
+                const uint32_t d = tmem + 256u + (uint32_t)g * 64u;
+                const uint32_t pbase = sbase + kOffP + g * 2 * kTileBytes;
 #pragma unroll
-                for (int k = 0; k < kD / 16; ++k) {
-                    uint64_t bd = smem_desc(sbase + kOffK + st * kTileBytes + k * 32);
-                    tc_mma_f16(d, smem_desc(sbase + kOffQhi + k * 32), bd, idesc_qk, k > 0 ? 1u : 0u);
-                    if (has_lo) tc_mma_f16(d, smem_desc(sbase + kOffQlo + k * 32), bd, idesc_qk, 1u);
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom;
+                    // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
+                    tc_mma_f16(d, smem_desc(pbase + (kk >> 2) * kTileBytes + (kk & 3) * 32),
+                               smem_desc(sbase + kOffV + st * kTileBytes + kk * 2048), idesc_pv,
+                               (k > 0 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(B_SFULL0 + sb));
-                if (i >= 1 && !issue_pv(i - 1)) { ok = false; break; }
+                tc_commit(bar(B_PVDONE0 + g));
+                return true;
+            };
+            for (int g = 0; ok && g < 2; ++g)
+                if (active(g, 0)) ok = issue_qk(g, 0);
+            for (int i = 0; ok && i < n_iter; ++i) {
+                // scores of the next tile first: they only need the previous scores to have left TMEM
+                for (int g = 0; ok && g < 2; ++g)
+                    if (i + 1 < n_iter && active(g, i + 1)) ok = issue_qk(g, i + 1);
+                for (int g = 0; ok && g < 2; ++g)
+                    if (active(g, i)) ok = issue_pv(g, i);
+                if (ok) {
+                    if (!f16 && !active(0, i) && !active(1, i))   // nobody multiplied: still wait for the converters
+                        ok = mbar_wait(bar(B_VREADY0 + (i % kStages)), (i / kStages) & 1, abort_flag);
+                    tc_commit(bar(B_KVEMPTY0 + (i % kStages)));
+                }
             }
-            if (ok) issue_pv(n_tiles - 1);
         }
     } else {
         // ================= softmax warps: thread = query row =================
-        const int r = tid;                         // row in tile = TMEM lane
-        const int i_glob = q0 + r;
-        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        const int g = warp >> 2;                   // query tile of this thread
+        const int r = tid & 127;                   // row in tile = TMEM lane
+        const int i_glob = q0 + g * kBM + r;
+        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
+        const uint32_t tmem_S = tmem + (uint32_t)g * 128u + lane_addr;
+        const uint32_t tmem_O = tmem + 256u + (uint32_t)g * 64u + lane_addr;
         bool ok = mbar_wait(bar(B_QLOAD), 0, abort_flag);
 
         // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place ----
-        if (ok && has_lo) {
-            unsigned char* qh = smem + kOffQhi + r * 128;
-            unsigned char* ql = smem + kOffQlo + r * 128;
+        if (ok && has_lo && (g == 0 || tile1_live)) {
+            unsigned char* qh = smem + kOffQ + (2 * g) * kTileBytes + r * 128;
+            unsigned char* ql = qh + kTileBytes;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const int pc = (c ^ (r & 7)) * 16;
@@ -329,121 +368,134 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         float l_run = 0.0f;          // running sum of the (rounded) weights
         float s_carry = -INFINITY;   // scaled score of the first key of the tile above
         const float c = a.c;
-        const float nu = (a.diffuse == 1) ? a.nu : 0.0f;
+        const float nu = DIFF ? a.nu : 0.0f;
         const float one_m_nu = 1.0f - nu;
+        const int softmax_tid = tid;                 // 0..255
+        int k_last = -1;
 
-        for (int i = 0; ok && i < n_tiles; ++i) {
-            const int sb = i & 1, jt = jt_hi - i, k0 = jt * kBN;
-            if (!mbar_wait(bar(B_SFULL0 + sb), (i >> 1) & 1, abort_flag)) { ok = false; break; }
+        for (int i = 0; ok && i < n_iter; ++i) {
+            const int st = i % kStages;
+            if (!f16) {
+                // BF16 V -> FP16 in place (exact for |v| in FP16's normal range, saturating beyond),
+                // so that weights and V share one type; 1024 16-byte chunks over 256 threads
+                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+                unsigned char* vt = smem + kOffV + st * kTileBytes;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4* pch = reinterpret_cast<uint4*>(vt + (softmax_tid + 256 * q) * 16);
+                    uint4 v = *pch;
+                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                    }
+                    *pch = v;
+                }
+                fence_async_smem();
+                mbar_arrive(bar(B_VREADY0 + st));
+            }
+            if (!active(g, i)) continue;
+            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN;
+            k_last = k;
+            if (!mbar_wait(bar(B_SFULL0 + g), k & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             float s[kBN];
-            const uint32_t ts = tmem_S0 + (uint32_t)sb * 128u + lane_addr;
-            tc_ld32(ts, s);
-            tc_ld32(ts + 32, s + 32);
-            tc_ld32(ts + 64, s + 64);
-            tc_ld32(ts + 96, s + 96);
+            tc_ld32(tmem_S, s);
+            tc_ld32(tmem_S + 32, s + 32);
+            tc_ld32(tmem_S + 64, s + 64);
+            tc_ld32(tmem_S + 96, s + 96);
             tc_wait_ld();
             tc_fence_before();
-            mbar_arrive(bar(B_SEMPTY0 + sb));
+            mbar_arrive(bar(B_SEMPTY0 + g));
 
-            // scale into the log2 domain and mask
-            const bool edge = (k0 + kBN - 1 > q0) || (k0 + kBN > S) || (a.window > 0 && k0 < q0 + kBM - 1 - a.window);
+            // mask on edge tiles only; maximum of the raw scores (c > 0)
+            const int r_first = q0 + g * kBM;
+            const bool edge = (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
+                              (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
             float mx = -INFINITY;
             if (edge) {
 #pragma unroll
                 for (int j = 0; j < kBN; ++j) {
                     const int jg = k0 + j;
                     const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
-                    s[j] = allowed ? s[j] * c : -INFINITY;
+                    s[j] = allowed ? s[j] : -INFINITY;
                     mx = fmaxf(mx, s[j]);
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < kBN; ++j) {
-                    s[j] *= c;
-                    mx = fmaxf(mx, s[j]);
-                }
+                for (int j = 0; j < kBN; ++j) mx = fmaxf(mx, s[j]);
             }
-            // move the reference maximum only when it would grow by more than the threshold
-            // (weights stay below 2^8, well inside FP16); the decision is warp-wide because
-            // the O correction is a warp-collective TMEM access
+            mx *= c;
+            // move the reference maximum only when it would grow by more than the threshold (weights
+            // stay below 2^8, well inside FP16); the decision is warp-wide because the O correction is
+            // a warp-collective TMEM access
             const bool want = (mx > m_run + kRescaleThreshold) || (m_run == -INFINITY && mx > -INFINITY);
-            const bool any = __any_sync(0xffffffffu, want && i > 0 && m_run > -INFINITY);
+            const bool any = __any_sync(0xffffffffu, want && k > 0 && m_run > -INFINITY);
             float m_new = want ? mx : m_run;
             if (any && m_new < mx) m_new = mx;       // correcting anyway: take the exact maximum
             // before touching O or the weight buffer the previous O += W V must be complete
-            if (i > 0 && !mbar_wait(bar(B_PVDONE), (i - 1) & 1, abort_flag)) { ok = false; break; }
+            if (k > 0 && !mbar_wait(bar(B_PVDONE0 + g), (k - 1) & 1, abort_flag)) { ok = false; break; }
             if (any) {
                 tc_fence_after();
                 const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
                 float o[32];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    tc_ld32(tmem_O + lane_addr + 32 * h, o);
+                    tc_ld32(tmem_O + 32 * h, o);
                     tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] *= f;
-                    tc_st32(tmem_O + lane_addr + 32 * h, o);
+                    tc_st32(tmem_O + 32 * h, o);
                 }
                 tc_wait_st();
                 tc_fence_before();
                 l_run *= f;
-            } else if (m_run == -INFINITY) {
-                l_run = 0.0f;
             }
             m_run = m_new;
+            const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;   // all scores are -inf in that case
 
-            // weights with the diffusion stencil folded in, in the type of V (the MMA takes one
-            // type for both operands): FP16 directly, BF16 as hi + lo; row sum of what was stored
-            const float p_above = (s_carry > -INFINITY && m_run > -INFINITY) ? ex2(s_carry - m_run) : 0.0f;
-            s_carry = s[0];
-            unsigned char* prow = smem + kOffP + r * 128;
+            // FP16 weights with the diffusion stencil folded in; row sum of the rounded values
+            const float p_above = DIFF ? ex2(s_carry + neg_m) : 0.0f;    // -inf carry gives 0
+            s_carry = s[0] * c;
+            unsigned char* prow = smem + kOffP + g * 2 * kTileBytes + r * 128;
             float nxt = p_above;                       // p of key j+1 while walking down from j = 127
             float lsum = 0.0f;
 #pragma unroll
             for (int ch = 15; ch >= 0; --ch) {        // 16-byte chunks of 8 keys, highest first
-                uint32_t w[4], w2[4];
+                uint32_t w[4];
 #pragma unroll
                 for (int e = 3; e >= 0; --e) {
                     const int j1 = ch * 8 + 2 * e + 1, j0 = j1 - 1;
-                    const float p1 = (m_run > -INFINITY) ? ex2(s[j1] - m_run) : 0.0f;
-                    const float p0 = (m_run > -INFINITY) ? ex2(s[j0] - m_run) : 0.0f;
-                    float w1 = one_m_nu * p1 + nu * nxt;
-                    float w0 = one_m_nu * p0 + nu * p1;
-                    if (k0 + j0 == 0) w0 += nu * p0;  // V_s[0] = V[0]
-                    nxt = p0;
-                    if (f16) {
-                        __half2 hw = __floats2half2_rn(w0, w1);
-                        float2 back = __half22float2(hw);
-                        lsum += back.x + back.y;
-                        w[e] = *reinterpret_cast<uint32_t*>(&hw);
-                    } else {
-                        const uint32_t h0 = f32_to_16(w0, false), h1 = f32_to_16(w1, false);
-                        const float r0 = w0 - from16(h0, false), r1 = w1 - from16(h1, false);
-                        const uint32_t g0 = f32_to_16(r0, false), g1 = f32_to_16(r1, false);
-                        lsum += (from16(h0, false) + from16(g0, false)) + (from16(h1, false) + from16(g1, false));
-                        w[e] = h0 | (h1 << 16);
-                        w2[e] = g0 | (g1 << 16);
+                    const float p1 = ex2(fmaf(s[j1], c, neg_m));
+                    const float p0 = ex2(fmaf(s[j0], c, neg_m));
+                    float w1 = p1, w0 = p0;
+                    if (DIFF) {
+                        w1 = fmaf(nu, nxt, one_m_nu * p1);
+                        w0 = fmaf(nu, p1, one_m_nu * p0);
+                        if (ch == 0 && e == 0 && k0 == 0) w0 = fmaf(nu, p0, w0);   // V_s[0] = V[0]
+                        nxt = p0;
                     }
+                    __half2 hw = __floats2half2_rn(w0, w1);
+                    float2 back = __half22float2(hw);
+                    lsum += back.x + back.y;
+                    w[e] = *reinterpret_cast<uint32_t*>(&hw);
                 }
                 const int atom = ch >> 3, cc = ch & 7;
                 *reinterpret_cast<uint4*>(prow + atom * kTileBytes + ((cc ^ (r & 7)) * 16)) =
                     make_uint4(w[0], w[1], w[2], w[3]);
-                if (!f16)
-                    *reinterpret_cast<uint4*>(prow + (kOffP2 - kOffP) + atom * kTileBytes + ((cc ^ (r & 7)) * 16)) =
-                        make_uint4(w2[0], w2[1], w2[2], w2[3]);
             }
             l_run += lsum;
             fence_async_smem();
-            mbar_arrive(bar(B_PFULL));
+            mbar_arrive(bar(B_PFULL0 + g));
         }
 
         // ---- epilogue: O / l ----
-        if (ok && mbar_wait(bar(B_PVDONE), (n_tiles - 1) & 1, abort_flag)) {
+        if (ok && k_last >= 0 && mbar_wait(bar(B_PVDONE0 + g), k_last & 1, abort_flag)) {
             tc_fence_after();
             float o[64];
-            tc_ld32(tmem_O + lane_addr, o);
-            tc_ld32(tmem_O + lane_addr + 32, o + 32);
+            tc_ld32(tmem_O, o);
+            tc_ld32(tmem_O + 32, o + 32);
             tc_wait_ld();
             tc_fence_before();
             if (i_glob < S) {
@@ -473,7 +525,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && tid == 0) atomicExch(a.status, 1);
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
@@ -620,7 +672,7 @@ bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn
     if (DH != kD) return false;
     if (in_dtype != LOGOS_BF16 && in_dtype != LOGOS_F16) return false;
     if (out_dtype != in_dtype && out_dtype != LOGOS_F32) return false;
-    if (!p->causal) return false;
+    if (!p->causal || !(p->scale > 0.0f)) return false;
     const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
     if (ns_any && p->ns_alpha < 1.0f) return false;                 // blend: two attention passes
     if (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CENTRAL) return false;
@@ -652,9 +704,14 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     a.diffuse = (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CAUSAL) ? 1 : 0;
     a.window = shunyam_active(p->window, S) ? p->window : 0;
     a.status = ctx->tc_status;
-    LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    dim3 grid((S + kBM - 1) / kBM, BH);
-    prefill_tc_kernel<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
+    dim3 grid((S + kBQ - 1) / kBQ, BH);
+    if (a.diffuse) {
+        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        prefill_tc_kernel<true><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
+    } else {
+        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        prefill_tc_kernel<false><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
+    }
     LOGOS_LAUNCH_CHECK(ctx, "prefill_tc_kernel");
     return LOGOS_OK;
 }
