@@ -13,14 +13,17 @@
 //     which a softmax thread applies to the row it holds in registers.  KV tiles are
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
-// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 320 threads:
-//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: thread t owns query row t (= TMEM lane t); reads S
-//              with tcgen05.ld, writes FP16 weights to shared memory (128B-swizzled, K-major) and
-//              finally O / l to global memory.  The MMA takes one type for both operands, so for
-//              BF16 inputs the same threads first turn the V tile into FP16 in place (exact in
+// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 576 threads:
+//   warps 0-7 / 8-15  softmax of tile 0 / tile 1.  A query row (= TMEM lane) is shared by two
+//              threads in different warps, each owning 64 of the tile's 128 score columns: they
+//              read S with tcgen05.ld, trade the half-row maximum and the stencil's boundary scores
+//              through shared memory, write FP16 weights to shared memory (128B-swizzled, K-major)
+//              and finally O / l to global memory.  The MMA takes one type for both operands, so
+//              for BF16 inputs the same threads first turn the V tile into FP16 in place (exact in
 //              FP16's normal range, saturating beyond it);
-//   warp 8     TMA producer (one lane): Q, Q_prev once, then K and V tiles into a two-stage ring;
-//   warp 9     MMA issuer (one lane): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
+//   warp 16    TMA producers: lane 0 loads Q, Q_prev once and then K tiles, lane 1 loads V tiles; K and
+//              V have separate two-stage rings (a K stage is free as soon as its scores are done);
+//   warp 17    MMA issuer (one lane): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
 //              (M128 N64 K16 x 8), completion via tcgen05.commit; the scores of the next tile are
 //              issued before the current tile's weights are waited for.
 // TMEM: columns [0,128) / [128,256) hold S of tile 0 / 1, [256,320) / [320,384) hold O.
@@ -40,8 +43,10 @@ constexpr int kBN = 128;              // keys per tile
 constexpr int kD = 64;                // head dimension
 constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
 constexpr int kStages = 2;
-constexpr int kTcThreads = 320;       // 8 softmax warps + TMA warp + MMA warp
-constexpr int kTmaWarp = 8, kMmaWarp = 9;
+constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
+constexpr int kSoftmaxThreads = 512;  // 16 softmax warps
+constexpr int kTcThreads = 576;       // + TMA warp + MMA warp
+constexpr int kTmaWarp = 16, kMmaWarp = 17;
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
@@ -51,12 +56,15 @@ constexpr int kOffQ = 0;                                       // per query tile
 constexpr int kOffK = kOffQ + 4 * kTileBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
 constexpr int kOffP = kOffV + kStages * kTileBytes;            // per query tile: 128 x 128 FP16 weights = 32 KiB
-constexpr int kOffBar = kOffP + 4 * kTileBytes;
-constexpr int kNumBars = 20;
+constexpr int kOffXch = kOffP + 4 * kTileBytes;               // row-pair exchange: [2][2][128] float4
+constexpr int kOffBar = kOffXch + 2 * 2 * kBM * 16;
+constexpr int kNumBars = 32;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
-enum Bar { B_QLOAD = 0, B_QREADY, B_KVFULL0, B_KVFULL1, B_KVEMPTY0, B_KVEMPTY1, B_VREADY0, B_VREADY1,
-           B_SFULL0, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1 };
+enum Bar { B_QLOAD = 0, B_QREADY, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1,
+           B_VREADY0, B_VREADY1,
+           B_SFULL0, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
+           B_PAIR0 /* eight: one per warp pair */ };
 
 struct TcArgs {
     void* O;
@@ -205,36 +213,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // iterations [i_first[g], i_last[g]]: above its diagonal and below its window it has nothing to do.
     const int jt_max = (S - 1) / kBN;
     const int jt_hi = min((q0 + kBQ - 1) / kBN, jt_max);
-    int jt_top[2], jt_bot[2];
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        const int r0 = q0 + g * kBM;
-        jt_top[g] = min(r0 / kBN, jt_max);                                   // diagonal tile of this query tile
-        jt_bot[g] = (a.window > 0) ? max(0, r0 - a.window - 1) / kBN : 0;    // one key below the window feeds the stencil
-    }
-    const int jt_lo = min(jt_bot[0], jt_bot[1]);
+    // diagonal tile of each query tile, and the lowest tile its window reaches (one key below the
+    // window still feeds the diffusion stencil)
+    const int jt_top0 = min(q0 / kBN, jt_max), jt_top1 = min((q0 + kBM) / kBN, jt_max);
+    const int jt_bot0 = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
+    const int jt_bot1 = (a.window > 0) ? max(0, q0 + kBM - a.window - 1) / kBN : 0;
+    const int jt_lo = min(jt_bot0, jt_bot1);
     const int n_iter = jt_hi - jt_lo + 1;
     const bool tile1_live = (q0 + kBM) < S;                // query tile 1 may lie wholly beyond the sequence
     auto active = [&](int g, int i) {
         const int jt = jt_hi - i;
-        return (g == 0 || tile1_live) && jt <= jt_top[g] && jt >= jt_bot[g];
+        return g == 0 ? (jt <= jt_top0 && jt >= jt_bot0) : (tile1_live && jt <= jt_top1 && jt >= jt_bot1);
     };
-    auto first_iter = [&](int g) { return jt_hi - jt_top[g]; };
+    auto first_iter = [&](int g) { return jt_hi - (g == 0 ? jt_top0 : jt_top1); };
 
     if (tid == 0) {
         mbar_init(bar(B_QLOAD), 1);
-        mbar_init(bar(B_QREADY), 256);
+        mbar_init(bar(B_QREADY), kSoftmaxThreads);
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar(B_KVFULL0 + s), 1);
-            mbar_init(bar(B_KVEMPTY0 + s), 1);
-            mbar_init(bar(B_VREADY0 + s), 256);
+            mbar_init(bar(B_KFULL0 + s), 1);
+            mbar_init(bar(B_KEMPTY0 + s), 1);
+            mbar_init(bar(B_VFULL0 + s), 1);
+            mbar_init(bar(B_VEMPTY0 + s), 1);
+            mbar_init(bar(B_VREADY0 + s), kSoftmaxThreads);
         }
         for (int g = 0; g < 2; ++g) {
             mbar_init(bar(B_SFULL0 + g), 1);
-            mbar_init(bar(B_SEMPTY0 + g), 128);
-            mbar_init(bar(B_PFULL0 + g), 128);
+            mbar_init(bar(B_SEMPTY0 + g), 256);
+            mbar_init(bar(B_PFULL0 + g), 256);
             mbar_init(bar(B_PVDONE0 + g), 1);
         }
+        for (int p = 0; p < 8; ++p) mbar_init(bar(B_PAIR0 + p), 64);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -260,12 +269,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 if (has_lo)
                     tma_load_3d(sbase + kOffQ + (2 * g + 1) * kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD));
             }
+            // K tiles: a stage is free again as soon as the scores that read it are done
             for (int i = 0; i < n_iter; ++i) {
                 const int st = i % kStages, jt = jt_hi - i;
-                if (i >= kStages && !mbar_wait(bar(B_KVEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(bar(B_KVFULL0 + st), 2 * kTileBytes);
-                tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KVFULL0 + st));
-                tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_KVFULL0 + st));
+                if (i >= kStages && !mbar_wait(bar(B_KEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
+                tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KFULL0 + st));
+            }
+        } else if (lane == 1) {
+            // V tiles on their own ring: needed later and freed later than K, so they never hold K back
+            for (int i = 0; i < n_iter; ++i) {
+                const int st = i % kStages, jt = jt_hi - i;
+                if (i >= kStages && !mbar_wait(bar(B_VEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
+                tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
             }
         }
     } else if (warp == kMmaWarp) {
@@ -277,7 +294,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             bool ok = mbar_wait(bar(B_QREADY), 0, abort_flag);
             auto issue_qk = [&](int g, int i) {   // S_g = Q_adv,g K(i)^T
                 const int st = i % kStages, k = i - first_iter(g);
-                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) return false;
+                if (!mbar_wait(bar(B_KFULL0 + st), (i / kStages) & 1, abort_flag)) return false;
                 if (k > 0 && !mbar_wait(bar(B_SEMPTY0 + g), (k - 1) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t d = tmem + (uint32_t)g * 128u;
@@ -294,7 +311,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             auto issue_pv = [&](int g, int i) {   // O_g (+)= W_g(i) V(i)
                 const int st = i % kStages, k = i - first_iter(g);
                 if (!mbar_wait(bar(B_PFULL0 + g), k & 1, abort_flag)) return false;
-                if (!f16 && !mbar_wait(bar(B_VREADY0 + st), (i / kStages) & 1, abort_flag)) return false;
+                if (!mbar_wait(bar((f16 ? B_VFULL0 : B_VREADY0) + st), (i / kStages) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t d = tmem + 256u + (uint32_t)g * 64u;
                 const uint32_t pbase = sbase + kOffP + g * 2 * kTileBytes;
@@ -311,36 +328,50 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             };
             for (int g = 0; ok && g < 2; ++g)
                 if (active(g, 0)) ok = issue_qk(g, 0);
+            if (ok) tc_commit(bar(B_KEMPTY0));
             for (int i = 0; ok && i < n_iter; ++i) {
                 // scores of the next tile first: they only need the previous scores to have left TMEM
-                for (int g = 0; ok && g < 2; ++g)
-                    if (i + 1 < n_iter && active(g, i + 1)) ok = issue_qk(g, i + 1);
+                if (i + 1 < n_iter) {
+                    for (int g = 0; ok && g < 2; ++g)
+                        if (active(g, i + 1)) ok = issue_qk(g, i + 1);
+                    if (ok) tc_commit(bar(B_KEMPTY0 + ((i + 1) % kStages)));
+                }
                 for (int g = 0; ok && g < 2; ++g)
                     if (active(g, i)) ok = issue_pv(g, i);
                 if (ok) {
-                    if (!f16 && !active(0, i) && !active(1, i))   // nobody multiplied: still wait for the converters
-                        ok = mbar_wait(bar(B_VREADY0 + (i % kStages)), (i / kStages) & 1, abort_flag);
-                    tc_commit(bar(B_KVEMPTY0 + (i % kStages)));
+                    if (!active(0, i) && !active(1, i))   // nobody multiplied: the tile must still have landed / been converted
+                        ok = mbar_wait(bar((f16 ? B_VFULL0 : B_VREADY0) + (i % kStages)), (i / kStages) & 1, abort_flag);
+                    tc_commit(bar(B_VEMPTY0 + (i % kStages)));
                 }
             }
         }
     } else {
-        // ================= softmax warps: thread = query row =================
-        const int g = warp >> 2;                   // query tile of this thread
-        const int r = tid & 127;                   // row in tile = TMEM lane
+        // ================= softmax warps: two threads per query row =================
+        // warp w: query tile g = w / 8, column half = (w / 4) % 2, TMEM lane quarter = w % 4.
+        // The two threads of a row sit in different warps; they trade the half-row maximum, the
+        // boundary scores of the diffusion stencil and finally the half-row sums through shared
+        // memory, synchronised by a 64-thread mbarrier of their warp pair (a bounded wait).
+        const int g = warp >> 3;
+        const int half = (warp >> 2) & 1;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;         // row in tile = TMEM lane
         const int i_glob = q0 + g * kBM + r;
-        const uint32_t lane_addr = ((uint32_t)((warp & 3) * 32)) << 16;
-        const uint32_t tmem_S = tmem + (uint32_t)g * 128u + lane_addr;
-        const uint32_t tmem_O = tmem + 256u + (uint32_t)g * 64u + lane_addr;
+        const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
+        const uint32_t tmem_S = tmem + (uint32_t)g * 128u + (uint32_t)half * 64u + lane_addr;
+        const uint32_t tmem_O = tmem + 256u + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
+        const uint32_t pair_bar = bar(B_PAIR0 + g * 4 + quarter);
+        float* xch = reinterpret_cast<float*>(smem + kOffXch);   // [parity][g][row][4]: max0, max1, score col 0, score col 64
+        int pair_phase = 0;
         bool ok = mbar_wait(bar(B_QLOAD), 0, abort_flag);
 
-        // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place ----
+        // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (4 chunks per thread) ----
         if (ok && has_lo && (g == 0 || tile1_live)) {
             unsigned char* qh = smem + kOffQ + (2 * g) * kTileBytes + r * 128;
             unsigned char* ql = qh + kTileBytes;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int pc = (c ^ (r & 7)) * 16;
+            for (int cq = 0; cq < 4; ++cq) {
+                const int cidx = half * 4 + cq;
+                const int pc = (cidx ^ (r & 7)) * 16;
                 uint4 cur = *reinterpret_cast<uint4*>(qh + pc);
                 uint4 prv = *reinterpret_cast<uint4*>(ql + pc);
                 uint32_t* cw = reinterpret_cast<uint32_t*>(&cur);
@@ -364,25 +395,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
         mbar_arrive(bar(B_QREADY));
 
-        float m_run = -INFINITY;     // running reference maximum (log2 domain)
-        float l_run = 0.0f;          // running sum of the (rounded) weights
-        float s_carry = -INFINITY;   // scaled score of the first key of the tile above
+        float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
+        float l_run = 0.0f;          // running sum of this thread's (rounded) weights
+        float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
         const float c = a.c;
         const float nu = DIFF ? a.nu : 0.0f;
         const float one_m_nu = 1.0f - nu;
-        const int softmax_tid = tid;                 // 0..255
         int k_last = -1;
 
         for (int i = 0; ok && i < n_iter; ++i) {
             const int st = i % kStages;
             if (!f16) {
                 // BF16 V -> FP16 in place (exact for |v| in FP16's normal range, saturating beyond),
-                // so that weights and V share one type; 1024 16-byte chunks over 256 threads
-                if (!mbar_wait(bar(B_KVFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+                // so that weights and V share one type; 1024 16-byte chunks over 512 threads
+                if (!mbar_wait(bar(B_VFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
                 unsigned char* vt = smem + kOffV + st * kTileBytes;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4* pch = reinterpret_cast<uint4*>(vt + (softmax_tid + 256 * q) * 16);
+                for (int q = 0; q < 2; ++q) {
+                    uint4* pch = reinterpret_cast<uint4*>(vt + (tid + kSoftmaxThreads * q) * 16);
                     uint4 v = *pch;
                     uint32_t* w = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
@@ -396,40 +426,52 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 mbar_arrive(bar(B_VREADY0 + st));
             }
             if (!active(g, i)) continue;
-            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN;
+            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN, kh = k0 + half * kHalf;
             k_last = k;
             if (!mbar_wait(bar(B_SFULL0 + g), k & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float s[kBN];
-            tc_ld32(tmem_S, s);
-            tc_ld32(tmem_S + 32, s + 32);
-            tc_ld32(tmem_S + 64, s + 64);
-            tc_ld32(tmem_S + 96, s + 96);
-            tc_wait_ld();
-            tc_fence_before();
-            mbar_arrive(bar(B_SEMPTY0 + g));
-
-            // mask on edge tiles only; maximum of the raw scores (c > 0)
+            // pass 1 over this thread's 64 score columns: maximum of the raw scores (c > 0); the scores
+            // are read again from TMEM in pass 2 instead of being held in 64 registers
             const int r_first = q0 + g * kBM;
             const bool edge = (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
                               (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
-            float mx = -INFINITY;
-            if (edge) {
+            auto mask32 = [&](float (&v)[32], int key0) {   // keys key0 .. key0+31 of this row
 #pragma unroll
-                for (int j = 0; j < kBN; ++j) {
-                    const int jg = k0 + j;
+                for (int j = 0; j < 32; ++j) {
+                    const int jg = key0 + j;
                     const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
-                    s[j] = allowed ? s[j] : -INFINITY;
-                    mx = fmaxf(mx, s[j]);
+                    v[j] = allowed ? v[j] : -INFINITY;
                 }
-            } else {
+            };
+            float mxh = -INFINITY, s_first = 0.0f;
 #pragma unroll
-                for (int j = 0; j < kBN; ++j) mx = fmaxf(mx, s[j]);
+            for (int hb = 0; hb < 2; ++hb) {
+                float v[32];
+                tc_ld32(tmem_S + 32 * hb, v);
+                tc_wait_ld();
+                if (edge) mask32(v, kh + 32 * hb);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mxh = fmaxf(mxh, v[j]);
+                if (hb == 0) s_first = v[0];
             }
-            mx *= c;
+            // trade with the other half of the row
+            float* x = xch + (((k & 1) * 2 + g) * kBM + r) * 4;
+            x[half] = mxh * c;
+            x[2 + half] = s_first * c;
+            mbar_arrive(pair_bar);
+            if (!mbar_wait(pair_bar, pair_phase & 1, abort_flag)) { ok = false; break; }
+            ++pair_phase;
+            const float mx = fmaxf(x[0], x[1]);
+            float s_above;                    // scaled score of the key right above this thread's columns
+            if (half == 0) {
+                s_above = x[3];               // column 64 of this tile
+            } else {
+                s_above = s_carry;            // column 0 of the tile above
+                s_carry = x[2];
+            }
             // move the reference maximum only when it would grow by more than the threshold (weights
             // stay below 2^8, well inside FP16); the decision is warp-wide because the O correction is
-            // a warp-collective TMEM access
+            // a warp-collective TMEM access, and identical in both warps of a pair (same rows, same data)
             const bool want = (mx > m_run + kRescaleThreshold) || (m_run == -INFINITY && mx > -INFINITY);
             const bool any = __any_sync(0xffffffffu, want && k > 0 && m_run > -INFINITY);
             float m_new = want ? mx : m_run;
@@ -440,14 +482,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 tc_fence_after();
                 const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
                 float o[32];
+                tc_ld32(tmem_O, o);
+                tc_wait_ld();
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    tc_ld32(tmem_O + 32 * h, o);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] *= f;
-                    tc_st32(tmem_O + 32 * h, o);
-                }
+                for (int j = 0; j < 32; ++j) o[j] *= f;
+                tc_st32(tmem_O, o);
                 tc_wait_st();
                 tc_fence_before();
                 l_run *= f;
@@ -456,65 +495,79 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;   // all scores are -inf in that case
 
             // FP16 weights with the diffusion stencil folded in; row sum of the rounded values
-            const float p_above = DIFF ? ex2(s_carry + neg_m) : 0.0f;    // -inf carry gives 0
-            s_carry = s[0] * c;
-            unsigned char* prow = smem + kOffP + g * 2 * kTileBytes + r * 128;
-            float nxt = p_above;                       // p of key j+1 while walking down from j = 127
+            float nxt = DIFF ? ex2(s_above + neg_m) : 0.0f;             // -inf gives 0
+            unsigned char* prow = smem + kOffP + (g * 2 + half) * kTileBytes + r * 128;
             float lsum = 0.0f;
 #pragma unroll
-            for (int ch = 15; ch >= 0; --ch) {        // 16-byte chunks of 8 keys, highest first
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 3; e >= 0; --e) {
-                    const int j1 = ch * 8 + 2 * e + 1, j0 = j1 - 1;
-                    const float p1 = ex2(fmaf(s[j1], c, neg_m));
-                    const float p0 = ex2(fmaf(s[j0], c, neg_m));
-                    float w1 = p1, w0 = p0;
-                    if (DIFF) {
-                        w1 = fmaf(nu, nxt, one_m_nu * p1);
-                        w0 = fmaf(nu, p1, one_m_nu * p0);
-                        if (ch == 0 && e == 0 && k0 == 0) w0 = fmaf(nu, p0, w0);   // V_s[0] = V[0]
-                        nxt = p0;
-                    }
-                    __half2 hw = __floats2half2_rn(w0, w1);
-                    float2 back = __half22float2(hw);
-                    lsum += back.x + back.y;
-                    w[e] = *reinterpret_cast<uint32_t*>(&hw);
+            for (int hb = 1; hb >= 0; --hb) {         // pass 2: upper 32 columns first, the stencil walks downwards
+                float v[32];
+                tc_ld32(tmem_S + 32 * hb, v);
+                tc_wait_ld();
+                if (hb == 0) {                        // the scores have left TMEM: the next S may be written
+                    tc_fence_before();
+                    mbar_arrive(bar(B_SEMPTY0 + g));
                 }
-                const int atom = ch >> 3, cc = ch & 7;
-                *reinterpret_cast<uint4*>(prow + atom * kTileBytes + ((cc ^ (r & 7)) * 16)) =
-                    make_uint4(w[0], w[1], w[2], w[3]);
+                if (edge) mask32(v, kh + 32 * hb);
+#pragma unroll
+                for (int cq = 3; cq >= 0; --cq) {     // 16-byte chunks of 8 keys, highest first
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 3; e >= 0; --e) {
+                        const int j1 = cq * 8 + 2 * e + 1, j0 = j1 - 1;
+                        const float p1 = ex2(fmaf(v[j1], c, neg_m));
+                        const float p0 = ex2(fmaf(v[j0], c, neg_m));
+                        float w1 = p1, w0 = p0;
+                        if (DIFF) {
+                            w1 = fmaf(nu, nxt, one_m_nu * p1);
+                            w0 = fmaf(nu, p1, one_m_nu * p0);
+                            if (hb == 0 && cq == 0 && e == 0 && kh == 0) w0 = fmaf(nu, p0, w0);   // V_s[0] = V[0]
+                            nxt = p0;
+                        }
+                        __half2 hw = __floats2half2_rn(w0, w1);
+                        float2 back = __half22float2(hw);
+                        lsum += back.x + back.y;
+                        w[e] = *reinterpret_cast<uint32_t*>(&hw);
+                    }
+                    const int ch = hb * 4 + cq;
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
             }
             l_run += lsum;
             fence_async_smem();
             mbar_arrive(bar(B_PFULL0 + g));
         }
 
-        // ---- epilogue: O / l ----
-        if (ok && k_last >= 0 && mbar_wait(bar(B_PVDONE0 + g), k_last & 1, abort_flag)) {
-            tc_fence_after();
-            float o[64];
-            tc_ld32(tmem_O, o);
-            tc_ld32(tmem_O + 32, o + 32);
-            tc_wait_ld();
-            tc_fence_before();
-            if (i_glob < S) {
-                const float inv = (l_run > 1e-9f) ? 1.0f / l_run : 0.0f;   // cuda/VedicGEMM.cu:1049
-                const size_t row = ((size_t)bh * S + i_glob) * kD;
-                if (a.out_is_f32) {
-                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
+        // ---- epilogue: O / l, 32 channels per thread ----
+        if (ok && k_last >= 0) {
+            float* x = xch + ((((k_last + 1) & 1) * 2 + g) * kBM + r) * 4;
+            x[half] = l_run;
+            mbar_arrive(pair_bar);
+            ok = mbar_wait(pair_bar, pair_phase & 1, abort_flag);
+            const float l_row = x[0] + x[1];
+            if (ok && mbar_wait(bar(B_PVDONE0 + g), k_last & 1, abort_flag)) {
+                tc_fence_after();
+                float o[32];
+                tc_ld32(tmem_O, o);
+                tc_wait_ld();
+                tc_fence_before();
+                if (i_glob < S) {
+                    const float inv = (l_row > 1e-9f) ? 1.0f / l_row : 0.0f;   // cuda/VedicGEMM.cu:1049
+                    const size_t row = ((size_t)bh * S + i_glob) * kD + half * 32;
+                    if (a.out_is_f32) {
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
-                } else {
-                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
+                        for (int j = 0; j < 8; ++j)
+                            dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        uint32_t w[4];
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
-                        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int e = 0; e < 4; ++e)
+                                w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
+                            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                     }
                 }
             }
