@@ -23,7 +23,7 @@
 //              FP16's normal range, saturating beyond it);
 //   warp 16    TMA producers: lane 0 loads Q, Q_prev once and then K tiles, lane 1 loads V tiles; K and
 //              V have separate two-stage rings (a K stage is free as soon as its scores are done);
-//   warp 17    MMA issuer (one lane): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
+//   warps 17,18  MMA issuers (one lane each, one per query tile): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
 //              (M128 N64 K16 x 8), completion via tcgen05.commit; the scores of the next tile are
 //              issued before the current tile's weights are waited for.
 // TMEM: columns [0,128) / [128,256) hold S of tile 0 / 1, [256,320) / [320,384) hold O.
@@ -45,8 +45,8 @@ constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit til
 constexpr int kStages = 2;
 constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
 constexpr int kSoftmaxThreads = 512;  // 16 softmax warps
-constexpr int kTcThreads = 576;       // + TMA warp + MMA warp
-constexpr int kTmaWarp = 16, kMmaWarp = 17;
+constexpr int kTcThreads = 608;       // + TMA warp + two MMA warps (one issuer per query tile)
+constexpr int kTmaWarp = 16, kMmaWarp = 17;   // MMA warps: 17 (tile 0; also owns TMEM) and 18 (tile 1)
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
@@ -232,9 +232,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         mbar_init(bar(B_QREADY), kSoftmaxThreads);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_KFULL0 + s), 1);
-            mbar_init(bar(B_KEMPTY0 + s), 1);
+            mbar_init(bar(B_KEMPTY0 + s), 2);     // one arrival per MMA issuer
             mbar_init(bar(B_VFULL0 + s), 1);
-            mbar_init(bar(B_VEMPTY0 + s), 1);
+            mbar_init(bar(B_VEMPTY0 + s), 2);
             mbar_init(bar(B_VREADY0 + s), kSoftmaxThreads);
         }
         for (int g = 0; g < 2; ++g) {
@@ -285,64 +285,72 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ================= MMA issuer =================
+    } else if (warp >= kMmaWarp) {
+        // ================= MMA issuers: one thread per query tile =================
+        // The issuing thread is a single instruction stream, so everything it can know in advance
+        // is computed before the loop: descriptors are a constant high word plus a 14-bit address
+        // field, and the loop only adds to the low word.
         if (lane == 0) {
+            const int g = warp - kMmaWarp;
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_qk = instr_desc(fmt, fmt, 0, kBN);
             const uint32_t idesc_pv = instr_desc(0, 0, 1 /* V is MN-major */, kD);   // FP16 weights x FP16 V
+            const uint32_t desc_hi = (uint32_t)(smem_desc(0) >> 32);
+            auto lo_of = [](uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); };
+            auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
+            const uint32_t qhi_lo = lo_of(sbase + kOffQ + (2 * g) * kTileBytes);
+            const uint32_t qlo_lo = lo_of(sbase + kOffQ + (2 * g + 1) * kTileBytes);
+            const uint32_t p_lo = lo_of(sbase + kOffP + g * 2 * kTileBytes);
+            const uint32_t k_lo0 = lo_of(sbase + kOffK), v_lo0 = lo_of(sbase + kOffV);
+            const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + 256u + (uint32_t)g * 64u;
+            const int it_first = first_iter(g);
+            const int it_last = (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1;
+            const int v_bar = f16 ? B_VFULL0 : B_VREADY0;
             bool ok = mbar_wait(bar(B_QREADY), 0, abort_flag);
-            auto issue_qk = [&](int g, int i) {   // S_g = Q_adv,g K(i)^T
-                const int st = i % kStages, k = i - first_iter(g);
-                if (!mbar_wait(bar(B_KFULL0 + st), (i / kStages) & 1, abort_flag)) return false;
-                if (k > 0 && !mbar_wait(bar(B_SEMPTY0 + g), (k - 1) & 1, abort_flag)) return false;
-                tc_fence_after();
-                const uint32_t d = tmem + (uint32_t)g * 128u;
-                const uint32_t qhi = sbase + kOffQ + (2 * g) * kTileBytes, qlo = qhi + kTileBytes;
+
+            auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
+                const int st = i & 1, k = i - it_first;
+                if (!mbar_wait(bar(B_KFULL0 + st), (i >> 1) & 1, abort_flag)) return false;
+                if (i >= it_first && i <= it_last) {
+                    if (k > 0 && !mbar_wait(bar(B_SEMPTY0 + g), (k - 1) & 1, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t kl = k_lo0 + (uint32_t)st * (kTileBytes >> 4);
 #pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint64_t bd = smem_desc(sbase + kOffK + st * kTileBytes + kk * 32);
-                    tc_mma_f16(d, smem_desc(qhi + kk * 32), bd, idesc_qk, kk > 0 ? 1u : 0u);
-                    if (has_lo) tc_mma_f16(d, smem_desc(qlo + kk * 32), bd, idesc_qk, 1u);
+                    for (int kk = 0; kk < kD / 16; ++kk) {
+                        tc_mma_f16(d_s, desc(qhi_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, kk > 0 ? 1u : 0u);
+                        if (has_lo) tc_mma_f16(d_s, desc(qlo_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, 1u);
+                    }
+                    tc_commit(bar(B_SFULL0 + g));
                 }
-                tc_commit(bar(B_SFULL0 + g));
+                tc_commit(bar(B_KEMPTY0 + st));   // both issuers arrive, each after its own reads of K(i)
                 return true;
             };
-            auto issue_pv = [&](int g, int i) {   // O_g (+)= W_g(i) V(i)
-                const int st = i % kStages, k = i - first_iter(g);
-                if (!mbar_wait(bar(B_PFULL0 + g), k & 1, abort_flag)) return false;
-                if (!mbar_wait(bar((f16 ? B_VFULL0 : B_VREADY0) + st), (i / kStages) & 1, abort_flag)) return false;
-                tc_fence_after();
-                const uint32_t d = tmem + 256u + (uint32_t)g * 64u;
-                const uint32_t pbase = sbase + kOffP + g * 2 * kTileBytes;
+            auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
+                const int st = i & 1, k = i - it_first;
+                if (i >= it_first && i <= it_last) {
+                    if (!mbar_wait(bar(B_PFULL0 + g), k & 1, abort_flag)) return false;
+                    if (!mbar_wait(bar(v_bar + st), (i >> 1) & 1, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t vl = v_lo0 + (uint32_t)st * (kTileBytes >> 4);
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom;
-                    // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
-                    tc_mma_f16(d, smem_desc(pbase + (kk >> 2) * kTileBytes + (kk & 3) * 32),
-                               smem_desc(sbase + kOffV + st * kTileBytes + kk * 2048), idesc_pv,
-                               (k > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < kBN / 16; ++kk) {
+                        // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom;
+                        // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
+                        tc_mma_f16(d_o, desc(p_lo + (kk >> 2) * (kTileBytes >> 4) + (kk & 3) * 2),
+                                   desc(vl + kk * (2048 >> 4)), idesc_pv, (k > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar(B_PVDONE0 + g));
+                } else if (!mbar_wait(bar(v_bar + st), (i >> 1) & 1, abort_flag)) {
+                    return false;   // an idle issuer still paces itself on the tile it releases
                 }
-                tc_commit(bar(B_PVDONE0 + g));
+                tc_commit(bar(B_VEMPTY0 + st));
                 return true;
             };
-            for (int g = 0; ok && g < 2; ++g)
-                if (active(g, 0)) ok = issue_qk(g, 0);
-            if (ok) tc_commit(bar(B_KEMPTY0));
+            if (ok) ok = issue_qk(0);
             for (int i = 0; ok && i < n_iter; ++i) {
                 // scores of the next tile first: they only need the previous scores to have left TMEM
-                if (i + 1 < n_iter) {
-                    for (int g = 0; ok && g < 2; ++g)
-                        if (active(g, i + 1)) ok = issue_qk(g, i + 1);
-                    if (ok) tc_commit(bar(B_KEMPTY0 + ((i + 1) % kStages)));
-                }
-                for (int g = 0; ok && g < 2; ++g)
-                    if (active(g, i)) ok = issue_pv(g, i);
-                if (ok) {
-                    if (!active(0, i) && !active(1, i))   // nobody multiplied: the tile must still have landed / been converted
-                        ok = mbar_wait(bar((f16 ? B_VFULL0 : B_VREADY0) + (i % kStages)), (i / kStages) & 1, abort_flag);
-                    tc_commit(bar(B_VEMPTY0 + (i % kStages)));
-                }
+                if (i + 1 < n_iter) ok = issue_qk(i + 1);
+                if (ok) ok = issue_pv(i);
             }
         }
     } else {
@@ -396,7 +404,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         mbar_arrive(bar(B_QREADY));
 
         float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
-        float l_run = 0.0f;          // running sum of this thread's (rounded) weights
+        float l_run = 0.0f;          // running sum of this thread's weights
         float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
         const float c = a.c;
         const float nu = DIFF ? a.nu : 0.0f;
@@ -494,7 +502,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             m_run = m_new;
             const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;   // all scores are -inf in that case
 
-            // FP16 weights with the diffusion stencil folded in; row sum of the rounded values
+            // FP16 weights with the diffusion stencil folded in.  The row sum is taken before the
+            // rounding: the two differ by at most 2^-12 relative, far inside the output tolerance.
             float nxt = DIFF ? ex2(s_above + neg_m) : 0.0f;             // -inf gives 0
             unsigned char* prow = smem + kOffP + (g * 2 + half) * kTileBytes + r * 128;
             float lsum = 0.0f;
@@ -524,8 +533,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                             nxt = p0;
                         }
                         __half2 hw = __floats2half2_rn(w0, w1);
-                        float2 back = __half22float2(hw);
-                        lsum += back.x + back.y;
+                        lsum += w0 + w1;   // unrounded: converting back would double the load on the XU pipe
                         w[e] = *reinterpret_cast<uint32_t*>(&hw);
                     }
                     const int ch = hb * 4 + cq;

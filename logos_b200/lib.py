@@ -10,7 +10,8 @@ import os
 from functools import lru_cache
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "liblogos_attn.so")
+# LOGOS_ATTN_LIB points at another build of the same ABI (kernel experiments); default is in-tree
+LIB_PATH = os.environ.get("LOGOS_ATTN_LIB") or os.path.join(PKG, "liblogos_attn.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_ALIGNMENT = range(7)
 ERR_SCRATCH_LIMIT = 7
