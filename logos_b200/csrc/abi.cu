@@ -127,7 +127,9 @@ int logos_ctx_synchronize(logos_ctx* ctx) {
     LOGOS_CUDA_TRY(ctx, cudaMemcpy(&flag, ctx->tc_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(ctx->tc_status, 0, sizeof(int));
-        return logos::fail(ctx, LOGOS_ERR_KERNEL_TIMEOUT, "a bounded wait inside a kernel ran out; results of that call are invalid");
+        return logos::fail(ctx, LOGOS_ERR_KERNEL_TIMEOUT,
+                           "a bounded wait inside a kernel ran out (barrier %d, thread %d); results of that call are invalid",
+                           (flag & 0xffff) / 8, (flag >> 16) & 0x3fff);
     }
     return LOGOS_OK;
 }

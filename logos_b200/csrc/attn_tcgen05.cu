@@ -102,7 +102,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (ok) return true;
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
-    *abort_flag = 1;
+    // record who gave up first: bits [0,16) = shared-memory address of the barrier, [16,30) = thread id
+    atomicCAS(const_cast<int*>(abort_flag), 0, (int)((bar & 0xffffu) | (threadIdx.x << 16)) | 0x40000000);
     return false;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
@@ -585,7 +586,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // ---- teardown: every role comes here, aborted or not ----
     tc_fence_before();
     __syncthreads();
-    if (*abort_flag && tid == 0) atomicExch(a.status, 1);
+    if (*abort_flag && tid == 0) atomicExch(a.status, *abort_flag - (int)(bar0 & 0xffffu));   // barrier offset + thread
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
