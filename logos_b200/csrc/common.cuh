@@ -114,6 +114,9 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
                    const logos_attn_params*);
+bool attention_window_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
+int attention_window(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
+                     void* O, int B, int H, int S, int DH, const logos_attn_params*);
 int umma_selftest(logos_ctx*, int mode, int dtype, const void* A, const void* B, float* D);
 bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
 int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,

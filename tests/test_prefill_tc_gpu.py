@@ -23,18 +23,19 @@ CASES = [
 
 
 def run(engine, engine_general, B, H, S, dtype, case, seed, outliers=False):
-    w, eta, nu, mode = case
+    w, eta, nu, mode = case[:4]
+    stride = case[4] if len(case) > 4 else 0
     Q, K, V = (syn.normal((B, H, S, 64), seed, t) for t in (1, 2, 3))
     if outliers:
         K[syn.normal((B, H, S, 64), seed, 9) > 2.3] *= 8
     dev = lambda a: torch.from_numpy(a).cuda().to(dtype)
     Qt, Kt, Vt = dev(Q), dev(K), dev(V)
-    p = L.Params.make(0.125, True, w, 0, eta, nu, 1.0, mode)
+    p = L.Params.make(0.125, True, w, stride, eta, nu, 1.0, mode)
     got = engine.attention(Qt, Kt, Vt, p, out_dtype=torch.float32)
     engine.synchronize()
     got = got.cpu().numpy()
     Qr, Kr, Vr = (t.float().cpu().numpy() for t in (Qt, Kt, Vt))
-    op = O.attn_params(0.125, True, w, 0, eta, nu, 1.0, mode)
+    op = O.attn_params(0.125, True, w, stride, eta, nu, 1.0, mode)
     want = O.attention_batched(Qr, Kr, Vr, op)
     assert_close(got, want, f"S={S} {dtype} case={case} vs oracle")
     ref = engine_general.attention(Qt, Kt, Vt, p, out_dtype=torch.float32).cpu().numpy()
@@ -51,6 +52,23 @@ def test_smallest_case_first(engine, engine_general):
 def test_shapes_and_switches(engine, engine_general, S, dtype):
     for n, case in enumerate(CASES):
         run(engine, engine_general, 2, 2, S, dtype, case, 40 + n)
+
+
+# Shunyam with landmarks: (window, eta, nu, mode, stride); 64/16 is the reference's production setting
+LANDMARK_CASES = [
+    (64, 0.1, 0.05, L.DIFFUSE_CAUSAL, 16),
+    (64, 0.0, 0.0, L.DIFFUSE_NONE, 16),
+    (8, 0.1, 0.05, L.DIFFUSE_CAUSAL, 5),      # stride does not divide the tile size
+    (32, 0.0, 0.05, L.DIFFUSE_CAUSAL, 8),
+    (16, 0.1, 0.0, L.DIFFUSE_NONE, 1),        # every key is a landmark: equals full causal attention
+]
+
+
+@pytest.mark.parametrize("S", [65, 127, 200, 513, 1100])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_window_with_landmarks(engine, engine_general, S, dtype):
+    for n, case in enumerate(LANDMARK_CASES):
+        run(engine, engine_general, 1, 2, S, dtype, case, 70 + n, outliers=(n == 0))
 
 
 def test_outlier_keys_long_sequence(engine, engine_general):
