@@ -98,7 +98,7 @@ template <bool F16> __device__ __forceinline__ uint32_t pack2(float x, float y) 
 }
 
 template <bool F16, bool DIFF>
-__global__ void __launch_bounds__(kWThreads)
+__global__ void __launch_bounds__(kWThreads, 4)
 shunyam_window_kernel(const WinArgs a) {
     extern __shared__ __align__(128) unsigned char wsm[];
     const uint32_t sb = (uint32_t)__cvta_generic_to_shared(wsm);
@@ -189,6 +189,8 @@ shunyam_window_kernel(const WinArgs a) {
         const uint32_t ks = sb + stage * kWStage, vs = ks + kWTile, ps = vs + kWTile;
         const bool lm = ti >= n_win;
 
+        const int kbase = lm ? (ti - n_win) * kWN : k_hi - kWN * (ti + 1) + 1;   // landmark index or first key
+
         // ---- S = Q_adv K^T : 16 rows x 64 keys per warp ----
         float s[8][4];
 #pragma unroll
@@ -209,7 +211,6 @@ shunyam_window_kernel(const WinArgs a) {
             }
 
         // ---- mask, scale to the log2 domain, online softmax ----
-        const int kbase = lm ? (ti - n_win) * kWN : k_hi - kWN * (ti + 1) + 1;   // landmark index or first key
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 8; ++n)
@@ -276,9 +277,9 @@ shunyam_window_kernel(const WinArgs a) {
                 o[n][2] = fmaf(h_b, v0, o[n][2]); o[n][3] = fmaf(h_b, v1, o[n][3]);
             }
         }
-        float wp[8][4];   // landmark part only: weights of the V[j-1] rows
         if (DIFF && !lm) {
-            // w_r = (1-nu) p_r + nu p_{r+1}; p_{r+1} of the last column comes from the tile above
+            // in place: w_r = (1-nu) p_r + nu p_{r+1}; p_{r+1} of the last column comes from the tile
+            // above.  Ascending n: everything read from block n+1 is still the original p.
             const float ab_a = (carry_a == -INFINITY) ? 0.0f : ex2f(carry_a - sub_a);
             const float ab_b = (carry_b == -INFINITY) ? 0.0f : ex2f(carry_b - sub_b);
 #pragma unroll
@@ -287,37 +288,30 @@ shunyam_window_kernel(const WinArgs a) {
                 // block's first element of lane 0, or the tile above
                 const float nx_same_a = __shfl_sync(0xffffffffu, s[n][0], (lane & ~3) | ((t + 1) & 3));
                 const float nx_same_b = __shfl_sync(0xffffffffu, s[n][2], (lane & ~3) | ((t + 1) & 3));
-                const float first_next_a = s[n < 7 ? n + 1 : 7][0];
-                const float first_next_b = s[n < 7 ? n + 1 : 7][2];
-                const float nx_blk_a = __shfl_sync(0xffffffffu, first_next_a, lane & ~3);
-                const float nx_blk_b = __shfl_sync(0xffffffffu, first_next_b, lane & ~3);
+                const float nx_blk_a = __shfl_sync(0xffffffffu, s[n < 7 ? n + 1 : 7][0], lane & ~3);
+                const float nx_blk_b = __shfl_sync(0xffffffffu, s[n < 7 ? n + 1 : 7][2], lane & ~3);
                 const float right_a = (t < 3) ? nx_same_a : ((n < 7) ? nx_blk_a : ab_a);
                 const float right_b = (t < 3) ? nx_same_b : ((n < 7) ? nx_blk_b : ab_b);
                 const float p0a = s[n][0], p1a = s[n][1], p0b = s[n][2], p1b = s[n][3];
                 float w0a = one_m_nu * p0a + nu * p1a, w1a = one_m_nu * p1a + nu * right_a;
                 float w0b = one_m_nu * p0b + nu * p1b, w1b = one_m_nu * p1b + nu * right_b;
                 if (kbase + n * 8 + 2 * t == 0) { w0a += nu * p0a; w0b += nu * p0b; }   // V_s[0] = V[0]
-                wp[n][0] = w0a; wp[n][1] = w1a; wp[n][2] = w0b; wp[n][3] = w1b;
+                s[n][0] = w0a; s[n][1] = w1a; s[n][2] = w0b; s[n][3] = w1b;
             }
-#pragma unroll
-            for (int n = 0; n < 8; ++n) { s[n][0] = wp[n][0]; s[n][1] = wp[n][1]; s[n][2] = wp[n][2]; s[n][3] = wp[n][3]; }
             carry_a = col0_a;
             carry_b = col0_b;
-        } else if (DIFF && lm) {
-#pragma unroll
-            for (int n = 0; n < 8; ++n)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { wp[n][e] = nu * s[n][e]; s[n][e] *= one_m_nu; }
         }
+        // landmark part: the gathered rows V[j] take (1-nu) p_j, the rows V[j-1] take nu p_j
+        const float w_main = (DIFF && lm) ? one_m_nu : 1.0f;
 
         // ---- O += W V (weights as hi + lo 16-bit fragments) ----
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
             uint32_t ah[4], al[4];
-            split2<F16>(s[2 * kk][0], s[2 * kk][1], ah[0], al[0]);
-            split2<F16>(s[2 * kk][2], s[2 * kk][3], ah[1], al[1]);
-            split2<F16>(s[2 * kk + 1][0], s[2 * kk + 1][1], ah[2], al[2]);
-            split2<F16>(s[2 * kk + 1][2], s[2 * kk + 1][3], ah[3], al[3]);
+            split2<F16>(w_main * s[2 * kk][0], w_main * s[2 * kk][1], ah[0], al[0]);
+            split2<F16>(w_main * s[2 * kk][2], w_main * s[2 * kk][3], ah[1], al[1]);
+            split2<F16>(w_main * s[2 * kk + 1][0], w_main * s[2 * kk + 1][1], ah[2], al[2]);
+            split2<F16>(w_main * s[2 * kk + 1][2], w_main * s[2 * kk + 1][3], ah[3], al[3]);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 uint32_t b[4];
@@ -329,10 +323,10 @@ shunyam_window_kernel(const WinArgs a) {
                 mma16816<F16>(o[2 * np + 1], al, b[2], b[3]);
             }
             if (DIFF && lm) {
-                split2<F16>(wp[2 * kk][0], wp[2 * kk][1], ah[0], al[0]);
-                split2<F16>(wp[2 * kk][2], wp[2 * kk][3], ah[1], al[1]);
-                split2<F16>(wp[2 * kk + 1][0], wp[2 * kk + 1][1], ah[2], al[2]);
-                split2<F16>(wp[2 * kk + 1][2], wp[2 * kk + 1][3], ah[3], al[3]);
+                split2<F16>(nu * s[2 * kk][0], nu * s[2 * kk][1], ah[0], al[0]);
+                split2<F16>(nu * s[2 * kk][2], nu * s[2 * kk][3], ah[1], al[1]);
+                split2<F16>(nu * s[2 * kk + 1][0], nu * s[2 * kk + 1][1], ah[2], al[2]);
+                split2<F16>(nu * s[2 * kk + 1][2], nu * s[2 * kk + 1][3], ah[3], al[3]);
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {
                     uint32_t b[4];
