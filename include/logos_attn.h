@@ -117,6 +117,8 @@ size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
  * no counterpart in the reference.  dtype: LOGOS_BF16 or LOGOS_F16.
  *   mode 0: D[128][128] = A[128][64] * B[128][64]^T        (the S = Q K^T operand layouts)
  *   mode 1: D[128][64]  = A[128][128] * B[128][64]         (the O = W V operand layouts)
+ *   mode 2: issues no load, so the kernel's bounded wait runs out and it returns: the following
+ *           logos_ctx_synchronize must report LOGOS_ERR_KERNEL_TIMEOUT (D is not written)
  * D is fp32, row-major.  Check the result with logos_ctx_synchronize. */
 int logos_selftest_umma(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D);
 

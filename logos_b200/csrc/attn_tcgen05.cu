@@ -89,8 +89,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -598,6 +599,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 //   mode 0: D[128 x 128] = A[128 x 64] B[128 x 64]^T   A, B by TMA, both K-major (the S = Q K^T shape)
 //   mode 1: D[128 x 64]  = A[128 x 128] B[128 x 64]    A written by the threads into the swizzled
 //           K-major layout, B by TMA and used MN-major (the O = W V shape)
+//   mode 2: no load is issued: every thread's bounded wait runs out, the kernel returns and the
+//           status word is raised (a check of the time-out path that cannot hang)
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      const unsigned short* __restrict__ a_rows, float* __restrict__ D, int mode, int fmt,
@@ -628,7 +631,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (tid == 0) {
+    if (tid == 0 && mode != 2) {   // mode 2: nothing is loaded, so the wait below must run out
         mbar_expect_tx(bar_load, mode == 0 ? 2 * kTileBytes : kTileBytes);
         if (mode == 0) tma_load_3d(sbase + offA, &mapA, 0, 0, 0, bar_load);
         tma_load_3d(sbase + offB, &mapB, 0, 0, 0, bar_load);
@@ -642,7 +645,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         }
         fence_async_smem();
     }
-    bool ok = mbar_wait(bar_load, 0, abort_flag);
+    bool ok = mbar_wait(bar_load, 0, abort_flag, mode == 2 ? (1u << 14) : kSpinLimit);
     __syncthreads();
     if (tid == 0 && ok) {
         tc_fence_after();
@@ -715,7 +718,7 @@ bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
 }  // namespace
 
 int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
-    if (!A || !B || !D || (mode != 0 && mode != 1) || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
+    if (!A || !B || !D || mode < 0 || mode > 2 || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "selftest: bad argument");
     const bool f16 = dtype == LOGOS_F16;
     CUtensorMap ma, mb;
