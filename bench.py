@@ -29,6 +29,10 @@ if ROOT not in sys.path:
 
 B, H, S_MAX, DH = 64, 16, 8192, 64
 ETA, NU = 0.1, 0.05
+# DRAM traffic of decode_dense_kernel per (sequence, head) pair at ctx 8192, from the ncu capture
+# summarised in profiles/decode_dense_kernel_b16_ctx8192.md: 268.60 MB read + 3.69 MB written over
+# 256 pairs.  Pairs are independent, so a launch moves this times its number of pairs.
+DECODE_TRAFFIC_PER_PAIR = (268.60e6 + 3.69e6) / 256
 METRIC = "int8_kv_decode_attention_bandwidth_8k_ctx"
 UNIT = "GB/s"
 
@@ -173,7 +177,11 @@ def run_reference(args) -> None:
 
 
 PREFILL = {"name": "causal_prefill_b4_h16_s4096_dh64_bf16", "B": 4, "S": 4096, "window": 0, "outliers": False}
-WINDOW = {"name": "shunyam_window64_b8_h16_s8192_dh64_bf16", "B": 8, "S": 8192, "window": 64, "outliers": True}
+WINDOW = {"name": "shunyam_window64_b8_h16_s8192_dh64_bf16", "B": 8, "S": 8192, "window": 64, "stride": 0,
+          "outliers": True}
+# the reference's production setting: window 64 plus every 16th key as a landmark (cuda/train_gpu.cu:1172-1173)
+WINDOW_LM = {"name": "shunyam_window64_stride16_b8_h16_s8192_dh64_bf16", "B": 8, "S": 8192, "window": 64,
+             "stride": 16, "outliers": True}
 
 
 def measured_peak_tflops():
@@ -201,7 +209,7 @@ def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_ov
         sets.append(tuple(t.bfloat16() for t in (Q, K, V)))
         del Q, K, V
     O = torch.empty((Bc, Hl, S, DH), dtype=torch.bfloat16, device=dev)
-    p = L.Params.make(1.0 / 8.0, True, cfg["window"], 0, ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
+    p = L.Params.make(1.0 / 8.0, True, cfg["window"], cfg.get("stride", 0), ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
 
     def step(i):
         Q, K, V = sets[i % 2]
@@ -269,8 +277,8 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if args.workload in ("prefill", "window"):
-        cfg = dict(PREFILL if args.workload == "prefill" else WINDOW)
+    if args.workload in ("prefill", "window", "window_lm"):
+        cfg = dict({"prefill": PREFILL, "window": WINDOW, "window_lm": WINDOW_LM}[args.workload])
         if args.batch != 64:   # profiling case: fewer sequences than the configuration
             cfg["B"] = args.batch
             cfg["name"] += f"_batch{args.batch}"
@@ -372,7 +380,7 @@ def run_ours(args) -> None:
         "roofline": {"bound": "hbm", "kernel": "decode_dense_kernel",
                      "achieved": kernel_bytes / (kern_ms * 1e-3) / 1e9, "peak": peak, "peak_kind": peak_kind,
                      "unit": "GB/s", "frac": kernel_bytes / (kern_ms * 1e-3) / 1e9 / peak,
-                     "kernel_ms": kern_ms, "traffic": None},
+                     "kernel_ms": kern_ms, "traffic": DECODE_TRAFFIC_PER_PAIR * B * Hl},
         "clocks": clocks,
     }
     if not args.no_secondary:
@@ -380,7 +388,7 @@ def run_ours(args) -> None:
         del decoders
         torch.cuda.empty_cache()
         line["secondary"] = [measure_attention(eng, dev, world, rank, cfg, max(3, args.steps // 4), 3, barrier,
-                                               max_over_ranks) for cfg in (PREFILL, WINDOW)]
+                                               max_over_ranks) for cfg in (PREFILL, WINDOW, WINDOW_LM)]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_port_baseline()
@@ -397,7 +405,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "window"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "window", "window_lm"],
                     help="decode is the benchmark; prefill / window time the other kernels alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")

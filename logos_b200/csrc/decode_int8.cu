@@ -233,7 +233,7 @@ __device__ __forceinline__ int signed_digit(int v, int which) {
     return which == 0 ? d0 : (which == 1 ? d1 : d2);
 }
 
-constexpr int kDenseWarps = 4;                  // warps per CTA, each with its own key range
+constexpr int kDenseWarps = 2;                  // warps per CTA, each with its own key range (512 keys at most)
 constexpr int kDenseThreads = kDenseWarps * 32;
 constexpr int kSubMax = kMaxChunk / kDenseWarps;  // keys per warp (256)
 constexpr int kDigitPitch = kSubMax / 4 + 4;    // words per digit row (+4: no bank aliasing)
@@ -245,7 +245,7 @@ constexpr float kWGrid = 8388608.0f;            // 2^23 levels per unit weight
 // the passes there is no block-wide barrier, and the next 32-key tile is always in
 // flight while the current one is consumed.
 template <bool BLEND>
-__global__ void __launch_bounds__(kDenseThreads, 4)
+__global__ void __launch_bounds__(kDenseThreads, 10)
 decode_dense_kernel(const DecodeArgs a) {
     constexpr int PATHS = BLEND ? 2 : 1;
     constexpr int ND = 3 * PATHS;                                   // digit rows / columns in use
