@@ -13,16 +13,16 @@
 //     which a softmax thread applies to the row it holds in registers.  KV tiles are
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
-// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 576 threads:
+// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 640 threads:
 //   warps 0-7 / 8-15  softmax of tile 0 / tile 1.  A query row (= TMEM lane) is shared by two
 //              threads in different warps, each owning 64 of the tile's 128 score columns: they
 //              read S with tcgen05.ld, trade the half-row maximum and the stencil's boundary scores
 //              through shared memory, write FP16 weights to shared memory (128B-swizzled, K-major)
-//              and finally O / l to global memory.  The MMA takes one type for both operands, so
-//              for BF16 inputs the same threads first turn the V tile into FP16 in place (exact in
-//              FP16's normal range, saturating beyond it);
+//              and finally O / l to global memory;
 //   warp 16    TMA producers: lane 0 loads Q, Q_prev once and then K tiles, lane 1 loads V tiles; K and
 //              V have separate two-stage rings (a K stage is free as soon as its scores are done);
+//   warp 19    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
+//              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond);
 //   warps 17,18  MMA issuers (one lane each, one per query tile): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
 //              (M128 N64 K16 x 8), completion via tcgen05.commit; the scores of the next tile are
 //              issued before the current tile's weights are waited for.
@@ -45,8 +45,9 @@ constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit til
 constexpr int kStages = 2;
 constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
 constexpr int kSoftmaxThreads = 512;  // 16 softmax warps
-constexpr int kTcThreads = 608;       // + TMA warp + two MMA warps (one issuer per query tile)
+constexpr int kTcThreads = 640;       // + TMA warp + two MMA warps (one issuer per query tile) + V converter warp
 constexpr int kTmaWarp = 16, kMmaWarp = 17;   // MMA warps: 17 (tile 0; also owns TMEM) and 18 (tile 1)
+constexpr int kCvtWarp = 19;
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
@@ -237,7 +238,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mbar_init(bar(B_KEMPTY0 + s), 2);     // one arrival per MMA issuer
             mbar_init(bar(B_VFULL0 + s), 1);
             mbar_init(bar(B_VEMPTY0 + s), 2);
-            mbar_init(bar(B_VREADY0 + s), kSoftmaxThreads);
+            mbar_init(bar(B_VREADY0 + s), 32);    // the converter warp
         }
         for (int g = 0; g < 2; ++g) {
             mbar_init(bar(B_SFULL0 + g), 1);
@@ -285,6 +286,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 if (i >= kStages && !mbar_wait(bar(B_VEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
                 tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
+            }
+        }
+    } else if (warp == kCvtWarp) {
+        // ================= V converter (BF16 inputs only) =================
+        // BF16 V -> FP16 in place (exact for |v| in FP16's normal range, saturating beyond), so that
+        // weights and V share one type; 1024 16-byte chunks per tile over 32 lanes.
+        if (!f16) {
+            bool ok = true;
+            for (int i = 0; ok && i < n_iter; ++i) {
+                const int st = i % kStages;
+                if (!mbar_wait(bar(B_VFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+                unsigned char* vt = smem + kOffV + st * kTileBytes;
+#pragma unroll 4
+                for (int q = 0; q < 32; ++q) {
+                    uint4* pch = reinterpret_cast<uint4*>(vt + (lane + 32 * q) * 16);
+                    uint4 v = *pch;
+                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                    }
+                    *pch = v;
+                }
+                fence_async_smem();
+                mbar_arrive(bar(B_VREADY0 + st));
             }
         }
     } else if (warp >= kMmaWarp) {
@@ -414,27 +441,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         int k_last = -1;
 
         for (int i = 0; ok && i < n_iter; ++i) {
-            const int st = i % kStages;
-            if (!f16) {
-                // BF16 V -> FP16 in place (exact for |v| in FP16's normal range, saturating beyond),
-                // so that weights and V share one type; 1024 16-byte chunks over 512 threads
-                if (!mbar_wait(bar(B_VFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
-                unsigned char* vt = smem + kOffV + st * kTileBytes;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    uint4* pch = reinterpret_cast<uint4*>(vt + (tid + kSoftmaxThreads * q) * 16);
-                    uint4 v = *pch;
-                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
-                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
-                    }
-                    *pch = v;
-                }
-                fence_async_smem();
-                mbar_arrive(bar(B_VREADY0 + st));
-            }
             if (!active(g, i)) continue;
             const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN, kh = k0 + half * kHalf;
             k_last = k;
