@@ -30,9 +30,9 @@ if ROOT not in sys.path:
 B, H, S_MAX, DH = 64, 16, 8192, 64
 ETA, NU = 0.1, 0.05
 # DRAM traffic of decode_dense_kernel per (sequence, head) pair at ctx 8192, from the ncu capture
-# summarised in profiles/decode_dense_kernel_b16_ctx8192.md: 268.60 MB read + 3.69 MB written over
-# 256 pairs.  Pairs are independent, so a launch moves this times its number of pairs.
-DECODE_TRAFFIC_PER_PAIR = (268.60e6 + 3.69e6) / 256
+# summarised in profiles/decode_dense_kernel_b16_ctx8192.md: 268.55 MB read + 4.20 MB written (mean of
+# two launches) over 256 pairs.  Pairs are independent, so a launch moves this times its number of pairs.
+DECODE_TRAFFIC_PER_PAIR = (268.55e6 + 4.20e6) / 256
 METRIC = "int8_kv_decode_attention_bandwidth_8k_ctx"
 UNIT = "GB/s"
 
