@@ -119,6 +119,7 @@ size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
  *   mode 1: D[128][64]  = A[128][128] * B[128][64]         (the O = W V operand layouts)
  *   mode 2: issues no load, so the kernel's bounded wait runs out and it returns: the following
  *           logos_ctx_synchronize must report LOGOS_ERR_KERNEL_TIMEOUT (D is not written)
+ *   mode 3: as mode 1 with A held in tensor memory (the way the prefill kernel passes W)
  * D is fp32, row-major.  Check the result with logos_ctx_synchronize. */
 int logos_selftest_umma(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D);
 

@@ -56,8 +56,7 @@ constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running m
 constexpr int kOffQ = 0;                                       // per query tile: hi, lo (4 tiles)
 constexpr int kOffK = kOffQ + 4 * kTileBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffP = kOffV + kStages * kTileBytes;            // per query tile: 128 x 128 FP16 weights = 32 KiB
-constexpr int kOffXch = kOffP + 4 * kTileBytes;               // row-pair exchange: [2][2][128] float4
+constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [2][2][128] float4
 constexpr int kOffBar = kOffXch + 2 * 2 * kBM * 16;
 constexpr int kNumBars = 32;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
@@ -130,6 +129,24 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same, with the A operand read from tensor memory: lane = row, one 32-bit column = two 16-bit
+// K elements (the lower index in the lower half), 8 columns per k-step of 16.
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
@@ -141,6 +158,20 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+                 ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
     const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
@@ -260,7 +291,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // columns: S of tile 0 [0,128), S of tile 1 [128,256), O of tile 0 [256,320), O of tile 1 [320,384)
+    // columns: S of tile 0 [0,128), S of tile 1 [128,256), O of tile 0 [256,320), O of tile 1 [320,384),
+    // FP16 weights of tile 0 [384,448), of tile 1 [448,512): two keys per column
 
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
@@ -329,7 +361,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
             const uint32_t qhi_lo = lo_of(sbase + kOffQ + (2 * g) * kTileBytes);
             const uint32_t qlo_lo = lo_of(sbase + kOffQ + (2 * g + 1) * kTileBytes);
-            const uint32_t p_lo = lo_of(sbase + kOffP + g * 2 * kTileBytes);
+            const uint32_t a_p = tmem + 384u + (uint32_t)g * 64u;
             const uint32_t k_lo0 = lo_of(sbase + kOffK), v_lo0 = lo_of(sbase + kOffV);
             const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + 256u + (uint32_t)g * 64u;
             const int it_first = first_iter(g);
@@ -363,10 +395,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     const uint32_t vl = v_lo0 + (uint32_t)st * (kTileBytes >> 4);
 #pragma unroll
                     for (int kk = 0; kk < kBN / 16; ++kk) {
-                        // weights: two 64-key swizzle atoms of 16 KiB, 32 bytes per k-step inside an atom;
+                        // weights: from tensor memory, 8 columns per k-step of 16 keys;
                         // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
-                        tc_mma_f16(d_o, desc(p_lo + (kk >> 2) * (kTileBytes >> 4) + (kk & 3) * 2),
-                                   desc(vl + kk * (2048 >> 4)), idesc_pv, (k > 0 || kk > 0) ? 1u : 0u);
+                        tc_mma_f16_ta(d_o, a_p + 8u * (uint32_t)kk, desc(vl + kk * (2048 >> 4)), idesc_pv,
+                                      (k > 0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(bar(B_PVDONE0 + g));
                 } else if (!mbar_wait(bar(v_bar + st), (i >> 1) & 1, abort_flag)) {
@@ -396,6 +428,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
         const uint32_t tmem_S = tmem + (uint32_t)g * 128u + (uint32_t)half * 64u + lane_addr;
         const uint32_t tmem_O = tmem + 256u + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
+        const uint32_t tmem_P = tmem + 384u + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
         const uint32_t pair_bar = bar(B_PAIR0 + g * 4 + quarter);
         float* xch = reinterpret_cast<float*>(smem + kOffXch);   // [parity][g][row][4]: max0, max1, score col 0, score col 64
         int pair_phase = 0;
@@ -436,8 +469,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         float l_run = 0.0f;          // running sum of this thread's weights
         float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
         const float c = a.c;
-        const float nu = DIFF ? a.nu : 0.0f;
-        const float one_m_nu = 1.0f - nu;
+        const float rho = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;   // nu <= 1/2 on this path
         int k_last = -1;
 
         for (int i = 0; ok && i < n_iter; ++i) {
@@ -459,6 +491,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     v[j] = allowed ? v[j] : -INFINITY;
                 }
             };
+            auto mask16 = [&](float (&v)[16], int key0) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int jg = key0 + j;
+                    const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
+                    v[j] = allowed ? v[j] : -INFINITY;
+                }
+            };
             float mxh = -INFINITY, s_first = 0.0f;
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
@@ -466,8 +506,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 tc_ld32(tmem_S + 32 * hb, v);
                 tc_wait_ld();
                 if (edge) mask32(v, kh + 32 * hb);
+                float m0 = fmaxf(v[0], v[1]);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mxh = fmaxf(mxh, v[j]);
+                for (int j = 2; j < 32; j += 2) m0 = fmaxf(fmaxf(m0, v[j]), v[j + 1]);   // three-input maxima
+                mxh = fmaxf(mxh, m0);
                 if (hb == 0) s_first = v[0];
             }
             // trade with the other half of the row
@@ -510,46 +552,59 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             m_run = m_new;
             const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;   // all scores are -inf in that case
 
-            // FP16 weights with the diffusion stencil folded in.  The row sum is taken before the
-            // rounding: the two differ by at most 2^-12 relative, far inside the output tolerance.
+            // FP16 weights with the diffusion stencil folded in, written to tensor memory as the A
+            // operand of O += W V.  The weights carry a common factor 1 / (1 - nu), which the
+            // normalisation by their own sum removes: w'_r = p_r + rho p_{r+1}, rho = nu / (1 - nu).
+            // Arithmetic runs on packed pairs (key k, key k + 8) of a 16-key chunk so that the
+            // neighbour pair of the stencil is again a register pair.  The row sum is taken before
+            // the FP16 rounding: the two differ by at most 2^-12 relative, far inside the tolerance.
             float nxt = DIFF ? ex2(s_above + neg_m) : 0.0f;             // -inf gives 0
-            unsigned char* prow = smem + kOffP + (g * 2 + half) * kTileBytes + r * 128;
-            float lsum = 0.0f;
+            const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m), rho2 = make_float2(rho, rho);
+            float2 lsum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int hb = 1; hb >= 0; --hb) {         // pass 2: upper 32 columns first, the stencil walks downwards
-                float v[32];
-                tc_ld32(tmem_S + 32 * hb, v);
+            for (int cb = 3; cb >= 0; --cb) {         // pass 2: highest 16 columns first, the stencil walks downwards
+                float v[16];
+                tc_ld16(tmem_S + 16 * cb, v);
                 tc_wait_ld();
-                if (hb == 0) {                        // the scores have left TMEM: the next S may be written
+                if (cb == 0) {                        // the scores have left TMEM: the next S may be written
                     tc_fence_before();
                     mbar_arrive(bar(B_SEMPTY0 + g));
                 }
-                if (edge) mask32(v, kh + 32 * hb);
+                if (edge) mask16(v, kh + 16 * cb);
+                float2 P[9];
 #pragma unroll
-                for (int cq = 3; cq >= 0; --cq) {     // 16-byte chunks of 8 keys, highest first
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 3; e >= 0; --e) {
-                        const int j1 = cq * 8 + 2 * e + 1, j0 = j1 - 1;
-                        const float p1 = ex2(fmaf(v[j1], c, neg_m));
-                        const float p0 = ex2(fmaf(v[j0], c, neg_m));
-                        float w1 = p1, w0 = p0;
-                        if (DIFF) {
-                            w1 = fmaf(nu, nxt, one_m_nu * p1);
-                            w0 = fmaf(nu, p1, one_m_nu * p0);
-                            if (hb == 0 && cq == 0 && e == 0 && kh == 0) w0 = fmaf(nu, p0, w0);   // V_s[0] = V[0]
-                            nxt = p0;
-                        }
-                        __half2 hw = __floats2half2_rn(w0, w1);
-                        lsum += w0 + w1;   // unrounded: converting back would double the load on the XU pipe
-                        w[e] = *reinterpret_cast<uint32_t*>(&hw);
-                    }
-                    const int ch = hb * 4 + cq;
-                    *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int e = 0; e < 8; ++e) {
+                    const float2 t = __ffma2_rn(make_float2(v[2 * e], v[2 * e + 1]), c2, nm2);
+                    const float p0 = ex2(t.x), p1 = ex2(t.y);          // keys 2e, 2e+1 of the chunk
+                    if (2 * e < 8) { P[2 * e].x = p0; P[2 * e + 1].x = p1; }
+                    else { P[2 * e - 8].y = p0; P[2 * e - 7].y = p1; }
                 }
+                float2 W[8];
+                if (DIFF) {
+                    P[8] = make_float2(P[0].y, nxt);                   // keys 8 and 16 (= first key of the chunk above)
+                    nxt = P[0].x;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) W[q] = __ffma2_rn(rho2, P[q + 1], P[q]);
+                    if (cb == 0 && kh == 0) W[0].x = fmaf(rho, P[0].x, W[0].x);   // V_s[0] = V[0]
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) W[q] = P[q];
+                }
+                uint32_t pk[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) lsum2 = __fadd2_rn(lsum2, W[q]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {                          // word e: keys 2e, 2e+1; word 4+e: keys 8+2e, 9+2e
+                    __half2 h_lo = __floats2half2_rn(W[2 * e].x, W[2 * e + 1].x);
+                    __half2 h_hi = __floats2half2_rn(W[2 * e].y, W[2 * e + 1].y);
+                    pk[e] = *reinterpret_cast<uint32_t*>(&h_lo);
+                    pk[4 + e] = *reinterpret_cast<uint32_t*>(&h_hi);
+                }
+                tc_st8(tmem_P + 8 * cb, pk);
             }
-            l_run += lsum;
-            fence_async_smem();
+            l_run += lsum2.x + lsum2.y;
+            tc_wait_st();
+            tc_fence_before();
             mbar_arrive(bar(B_PFULL0 + g));
         }
 
@@ -607,6 +662,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 //           K-major layout, B by TMA and used MN-major (the O = W V shape)
 //   mode 2: no load is issued: every thread's bounded wait runs out, the kernel returns and the
 //           status word is raised (a check of the time-out path that cannot hang)
+//   mode 3: as mode 1, but A is written by the threads into tensor memory (lane = row, two K
+//           elements per column) and read from there by the MMA (how the prefill kernel passes W)
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      const unsigned short* __restrict__ a_rows, float* __restrict__ D, int mode, int fmt,
@@ -651,11 +708,28 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
         }
         fence_async_smem();
     }
+    if (mode == 3) {   // row tid of A -> tensor-memory columns [64,128) of lane tid
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(a_rows + (size_t)tid * 128);
+        float w[32];
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w[j] = __uint_as_float(src[c0 + j]);
+            tc_st32(tmem + (((uint32_t)(warp * 32)) << 16) + 64u + (uint32_t)c0, w);
+        }
+        tc_wait_st();
+        tc_fence_before();
+    }
     bool ok = mbar_wait(bar_load, 0, abort_flag, mode == 2 ? (1u << 14) : kSpinLimit);
     __syncthreads();
     if (tid == 0 && ok) {
         tc_fence_after();
-        if (mode == 0) {
+        if (mode == 3) {
+            const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                tc_mma_f16_ta(tmem, tmem + 64u + 8u * (uint32_t)k, smem_desc(sbase + offB + k * 2048), idesc,
+                              k > 0 ? 1u : 0u);
+        } else if (mode == 0) {
             const uint32_t idesc = instr_desc(fmt, fmt, 0, 128);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
@@ -724,11 +798,11 @@ bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
 }  // namespace
 
 int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
-    if (!A || !B || !D || mode < 0 || mode > 2 || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
+    if (!A || !B || !D || mode < 0 || mode > 3 || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "selftest: bad argument");
     const bool f16 = dtype == LOGOS_F16;
     CUtensorMap ma, mb;
-    // mode 1 does not load A by TMA; its map then simply aliases B's
+    // modes 1 and 3 do not load A by TMA; its map then simply aliases B's
     if (!make_map(&ma, mode == 0 ? A : B, 1, kBM, f16) || !make_map(&mb, B, 1, kBM, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "selftest: cuTensorMapEncodeTiled failed");
     const int smem = 3 * kTileBytes + 64 + 1024;
@@ -747,7 +821,8 @@ bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn
     const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
     if (ns_any && p->ns_alpha < 1.0f) return false;                 // blend: two attention passes
     if (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CENTRAL) return false;
-    if (ns_any && (p->ns_nu < 0.0f || p->ns_nu > 1.0f)) return false;
+    // the diffusion weights are carried with a factor 1 / (1 - nu): keep them inside FP16
+    if (ns_any && (p->ns_nu < 0.0f || p->ns_nu > 0.5f)) return false;
     if (shunyam_active(p->window, S) && p->stride > 0) return false;  // landmarks: general kernel
     return true;
 }

@@ -42,3 +42,11 @@ def test_qk_shape_f16(engine):
 
 def test_pv_shape_f16(engine):
     _run(engine, 1, torch.float16)
+
+
+def test_pv_shape_weights_in_tmem_bf16(engine):
+    _run(engine, 3, torch.bfloat16)
+
+
+def test_pv_shape_weights_in_tmem_f16(engine):
+    _run(engine, 3, torch.float16)
