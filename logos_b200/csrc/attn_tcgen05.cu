@@ -38,26 +38,31 @@ namespace logos {
 namespace {
 
 constexpr int kBM = 128;              // rows of one query tile (= TMEM lanes)
-constexpr int kBQ = 256;              // query rows per CTA: two tiles that share every K/V tile
+constexpr int kTiles = 2;             // query tiles per CTA (2: both share every K/V tile, one CTA per SM)
+constexpr int kCtasPerSm = kTiles == 1 ? 2 : 1;   // one tile per CTA: two CTAs share an SM and its 512 TMEM columns
+constexpr int kBQ = kBM * kTiles;     // query rows per CTA
 constexpr int kBN = 128;              // keys per tile
 constexpr int kD = 64;                // head dimension
 constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
 constexpr int kStages = 2;
 constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
-constexpr int kSoftmaxThreads = 512;  // 16 softmax warps
-constexpr int kTcThreads = 640;       // + TMA warp + two MMA warps (one issuer per query tile) + V converter warp
-constexpr int kTmaWarp = 16, kMmaWarp = 17;   // MMA warps: 17 (tile 0; also owns TMEM) and 18 (tile 1)
-constexpr int kCvtWarp = 19;
+constexpr int kSoftmaxWarps = 8 * kTiles;
+constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
+constexpr int kTmaWarp = kSoftmaxWarps;          // then one MMA warp per query tile (the first also owns TMEM)
+constexpr int kMmaWarp = kTmaWarp + 1;
+constexpr int kCvtWarp = kMmaWarp + kTiles;      // V converter warp
+constexpr int kTcThreads = 32 * (kCvtWarp + 1);
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
-constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemCols = 256 * kTiles;
+constexpr uint32_t kColO = 128 * kTiles, kColP = kColO + 64 * kTiles;   // S first, then O, then the weights
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int kOffQ = 0;                                       // per query tile: hi, lo (4 tiles)
-constexpr int kOffK = kOffQ + 4 * kTileBytes;                  // kStages tiles
+constexpr int kOffK = kOffQ + 2 * kTiles * kTileBytes;         // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
 constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [2][2][128] float4
-constexpr int kOffBar = kOffXch + 2 * 2 * kBM * 16;
+constexpr int kOffBar = kOffXch + 2 * kTiles * kBM * 16;
 constexpr int kNumBars = 32;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
@@ -140,13 +145,6 @@ __device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, 
         ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
     uint32_t* r = reinterpret_cast<uint32_t*>(v);
     asm volatile(
@@ -207,24 +205,13 @@ __host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int b_mn
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-__device__ __forceinline__ float lo16_to_f32(uint32_t w, bool f16) {
-    return f16 ? __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)))
-               : __uint_as_float(w << 16);
-}
-__device__ __forceinline__ float hi16_to_f32(uint32_t w, bool f16) {
-    return f16 ? __half2float(__ushort_as_half((unsigned short)(w >> 16))) : __uint_as_float(w & 0xffff0000u);
-}
 __device__ __forceinline__ uint32_t f32_to_16(float x, bool f16) {
     return f16 ? (uint32_t)__half_as_ushort(__float2half_rn(x))
                : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
-__device__ __forceinline__ float from16(uint32_t h, bool f16) {
-    return f16 ? __half2float(__ushort_as_half((unsigned short)h)) : __uint_as_float(h << 16);
-}
-
 // -------------------------------------------------------------------------------------
 template <bool DIFF>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, kCtasPerSm)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const TcArgs a) {
     extern __shared__ unsigned char smem_raw[];
@@ -252,34 +239,57 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     const int jt_top0 = min(q0 / kBN, jt_max), jt_top1 = min((q0 + kBM) / kBN, jt_max);
     const int jt_bot0 = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
     const int jt_bot1 = (a.window > 0) ? max(0, q0 + kBM - a.window - 1) / kBN : 0;
-    const int jt_lo = min(jt_bot0, jt_bot1);
+    const int jt_lo = kTiles == 2 ? min(jt_bot0, jt_bot1) : jt_bot0;
     const int n_iter = jt_hi - jt_lo + 1;
-    const bool tile1_live = (q0 + kBM) < S;                // query tile 1 may lie wholly beyond the sequence
+    const bool tile1_live = kTiles == 2 && (q0 + kBM) < S;                // query tile 1 may lie wholly beyond the sequence
     auto active = [&](int g, int i) {
         const int jt = jt_hi - i;
         return g == 0 ? (jt <= jt_top0 && jt >= jt_bot0) : (tile1_live && jt <= jt_top1 && jt >= jt_bot1);
     };
     auto first_iter = [&](int g) { return jt_hi - (g == 0 ? jt_top0 : jt_top1); };
 
-    if (tid == 0) {
+    if (warp == kTmaWarp && lane == 0) {   // the producer sets the barriers up, so that its first loads can go out at once
         mbar_init(bar(B_QLOAD), 1);
         mbar_init(bar(B_QREADY), kSoftmaxThreads);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_KFULL0 + s), 1);
-            mbar_init(bar(B_KEMPTY0 + s), 2);     // one arrival per MMA issuer
+            mbar_init(bar(B_KEMPTY0 + s), kTiles);   // one arrival per MMA issuer
             mbar_init(bar(B_VFULL0 + s), 1);
-            mbar_init(bar(B_VEMPTY0 + s), 2);
+            mbar_init(bar(B_VEMPTY0 + s), kTiles);
             mbar_init(bar(B_VREADY0 + s), 32);    // the converter warp
         }
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < kTiles; ++g) {
             mbar_init(bar(B_SFULL0 + g), 1);
             mbar_init(bar(B_SEMPTY0 + g), 256);
             mbar_init(bar(B_PFULL0 + g), 256);
             mbar_init(bar(B_PVDONE0 + g), 1);
         }
-        for (int p = 0; p < 8; ++p) mbar_init(bar(B_PAIR0 + p), 64);
+        for (int p = 0; p < 4 * kTiles; ++p) mbar_init(bar(B_PAIR0 + p), 64);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kTmaWarp) {
+        // Q and the first K / V tiles are requested before the rest of the CTA has finished its own
+        // set-up (TMEM allocation, the CTA-wide barrier): their latency is the longest of the prologue
+        __syncwarp();
+        if (lane == 0) {
+            const int nq = (has_lo ? 2 : 1) * (tile1_live ? 2 : 1);
+            mbar_expect_tx(bar(B_QLOAD), nq * kTileBytes);
+            for (int g = 0; g < (tile1_live ? 2 : 1); ++g) {
+                tma_load_3d(sbase + kOffQ + (2 * g) * kTileBytes, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD));
+                if (has_lo)
+                    tma_load_3d(sbase + kOffQ + (2 * g + 1) * kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD));
+            }
+            for (int i = 0; i < min(kStages, n_iter); ++i) {
+                mbar_expect_tx(bar(B_KFULL0 + i), kTileBytes);
+                tma_load_3d(sbase + kOffK + i * kTileBytes, &mapK, 0, (jt_hi - i) * kBN, bh, bar(B_KFULL0 + i));
+            }
+        } else if (lane == 1) {
+            for (int i = 0; i < min(kStages, n_iter); ++i) {
+                mbar_expect_tx(bar(B_VFULL0 + i), kTileBytes);
+                tma_load_3d(sbase + kOffV + i * kTileBytes, &mapV, 0, (jt_hi - i) * kBN, bh, bar(B_VFULL0 + i));
+            }
+        }
     }
     if (warp == kMmaWarp) {   // TMEM allocation is warp-wide; this warp also frees it
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -291,31 +301,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // columns: S of tile 0 [0,128), S of tile 1 [128,256), O of tile 0 [256,320), O of tile 1 [320,384),
-    // FP16 weights of tile 0 [384,448), of tile 1 [448,512): two keys per column
+    // columns per query tile: S 128 (from column 0), O 64 (from kColO), FP16 weights 64 (from kColP, two keys per column)
 
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            const int nq = (has_lo ? 2 : 1) * (tile1_live ? 2 : 1);
-            mbar_expect_tx(bar(B_QLOAD), nq * kTileBytes);
-            for (int g = 0; g < (tile1_live ? 2 : 1); ++g) {
-                tma_load_3d(sbase + kOffQ + (2 * g) * kTileBytes, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD));
-                if (has_lo)
-                    tma_load_3d(sbase + kOffQ + (2 * g + 1) * kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD));
-            }
             // K tiles: a stage is free again as soon as the scores that read it are done
-            for (int i = 0; i < n_iter; ++i) {
+            for (int i = kStages; i < n_iter; ++i) {
                 const int st = i % kStages, jt = jt_hi - i;
-                if (i >= kStages && !mbar_wait(bar(B_KEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
+                if (!mbar_wait(bar(B_KEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
                 tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KFULL0 + st));
             }
         } else if (lane == 1) {
             // V tiles on their own ring: needed later and freed later than K, so they never hold K back
-            for (int i = 0; i < n_iter; ++i) {
+            for (int i = kStages; i < n_iter; ++i) {
                 const int st = i % kStages, jt = jt_hi - i;
-                if (i >= kStages && !mbar_wait(bar(B_VEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
+                if (!mbar_wait(bar(B_VEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
                 tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
             }
@@ -347,11 +349,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             }
         }
     } else if (warp >= kMmaWarp) {
-        // ================= MMA issuers: one thread per query tile =================
-        // The issuing thread is a single instruction stream, so everything it can know in advance
-        // is computed before the loop: descriptors are a constant high word plus a 14-bit address
-        // field, and the loop only adds to the low word.
-        if (lane == 0) {
+        // ================= MMA issuers: one warp per query tile =================
+        // The whole warp runs the loop and the waits, one elected lane issues the MMAs and commits:
+        // with warp-uniform control flow the descriptors stay in uniform registers, which halves the
+        // cost of issuing an MMA compared with a single divergent thread.  Everything that can be
+        // known in advance is computed before the loop: descriptors are a constant high word plus a
+        // 14-bit address field, and the loop only adds to the low word.
+        {
+            uint32_t elected;
+            asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(elected));
+            const bool leader = elected != 0;
+            auto wait_w = [&](uint32_t b, uint32_t parity) {   // warp-uniform verdict
+                return __all_sync(0xffffffffu, mbar_wait(b, parity, abort_flag)) != 0;
+            };
             const int g = warp - kMmaWarp;
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_qk = instr_desc(fmt, fmt, 0, kBN);
@@ -361,50 +371,56 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
             const uint32_t qhi_lo = lo_of(sbase + kOffQ + (2 * g) * kTileBytes);
             const uint32_t qlo_lo = lo_of(sbase + kOffQ + (2 * g + 1) * kTileBytes);
-            const uint32_t a_p = tmem + 384u + (uint32_t)g * 64u;
+            const uint32_t a_p = tmem + kColP + (uint32_t)g * 64u;
             const uint32_t k_lo0 = lo_of(sbase + kOffK), v_lo0 = lo_of(sbase + kOffV);
-            const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + 256u + (uint32_t)g * 64u;
+            const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + kColO + (uint32_t)g * 64u;
             const int it_first = first_iter(g);
             const int it_last = (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1;
             const int v_bar = f16 ? B_VFULL0 : B_VREADY0;
-            bool ok = mbar_wait(bar(B_QREADY), 0, abort_flag);
+            bool ok = wait_w(bar(B_QREADY), 0);
 
             auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
                 const int st = i & 1, k = i - it_first;
-                if (!mbar_wait(bar(B_KFULL0 + st), (i >> 1) & 1, abort_flag)) return false;
+                if (!wait_w(bar(B_KFULL0 + st), (i >> 1) & 1)) return false;
                 if (i >= it_first && i <= it_last) {
-                    if (k > 0 && !mbar_wait(bar(B_SEMPTY0 + g), (k - 1) & 1, abort_flag)) return false;
+                    if (k > 0 && !wait_w(bar(B_SEMPTY0 + g), (k - 1) & 1)) return false;
                     tc_fence_after();
                     const uint32_t kl = k_lo0 + (uint32_t)st * (kTileBytes >> 4);
+                    if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < kD / 16; ++kk) {
-                        tc_mma_f16(d_s, desc(qhi_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, kk > 0 ? 1u : 0u);
-                        if (has_lo) tc_mma_f16(d_s, desc(qlo_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, 1u);
+                        for (int kk = 0; kk < kD / 16; ++kk) {
+                            tc_mma_f16(d_s, desc(qhi_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, kk > 0 ? 1u : 0u);
+                            if (has_lo) tc_mma_f16(d_s, desc(qlo_lo + 2 * kk), desc(kl + 2 * kk), idesc_qk, 1u);
+                        }
+                        tc_commit(bar(B_SFULL0 + g));
                     }
-                    tc_commit(bar(B_SFULL0 + g));
                 }
-                tc_commit(bar(B_KEMPTY0 + st));   // both issuers arrive, each after its own reads of K(i)
+                if (leader) tc_commit(bar(B_KEMPTY0 + st));   // both issuers arrive, each after its own reads of K(i)
+                __syncwarp();
                 return true;
             };
             auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
                 const int st = i & 1, k = i - it_first;
                 if (i >= it_first && i <= it_last) {
-                    if (!mbar_wait(bar(B_PFULL0 + g), k & 1, abort_flag)) return false;
-                    if (!mbar_wait(bar(v_bar + st), (i >> 1) & 1, abort_flag)) return false;
+                    if (!wait_w(bar(B_PFULL0 + g), k & 1)) return false;
+                    if (!wait_w(bar(v_bar + st), (i >> 1) & 1)) return false;
                     tc_fence_after();
                     const uint32_t vl = v_lo0 + (uint32_t)st * (kTileBytes >> 4);
+                    if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk) {
-                        // weights: from tensor memory, 8 columns per k-step of 16 keys;
-                        // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
-                        tc_mma_f16_ta(d_o, a_p + 8u * (uint32_t)kk, desc(vl + kk * (2048 >> 4)), idesc_pv,
-                                      (k > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < kBN / 16; ++kk) {
+                            // weights: from tensor memory, 8 columns per k-step of 16 keys;
+                            // V tile: key-major rows of 128 bytes, 16 keys per k-step = 2048 bytes
+                            tc_mma_f16_ta(d_o, a_p + 8u * (uint32_t)kk, desc(vl + kk * (2048 >> 4)), idesc_pv,
+                                          (k > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit(bar(B_PVDONE0 + g));
                     }
-                    tc_commit(bar(B_PVDONE0 + g));
-                } else if (!mbar_wait(bar(v_bar + st), (i >> 1) & 1, abort_flag)) {
+                } else if (!wait_w(bar(v_bar + st), (i >> 1) & 1)) {
                     return false;   // an idle issuer still paces itself on the tile it releases
                 }
-                tc_commit(bar(B_VEMPTY0 + st));
+                if (leader) tc_commit(bar(B_VEMPTY0 + st));
+                __syncwarp();
                 return true;
             };
             if (ok) ok = issue_qk(0);
@@ -427,8 +443,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const int i_glob = q0 + g * kBM + r;
         const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
         const uint32_t tmem_S = tmem + (uint32_t)g * 128u + (uint32_t)half * 64u + lane_addr;
-        const uint32_t tmem_O = tmem + 256u + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
-        const uint32_t tmem_P = tmem + 384u + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
+        const uint32_t tmem_O = tmem + kColO + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
+        const uint32_t tmem_P = tmem + kColP + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
         const uint32_t pair_bar = bar(B_PAIR0 + g * 4 + quarter);
         float* xch = reinterpret_cast<float*>(smem + kOffXch);   // [parity][g][row][4]: max0, max1, score col 0, score col 64
         int pair_phase = 0;
@@ -448,15 +464,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 uint32_t* pw = reinterpret_cast<uint32_t*>(&prv);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float q_a = lo16_to_f32(cw[e], f16), q_b = hi16_to_f32(cw[e], f16);
-                    float p_a = (i_glob > 0) ? lo16_to_f32(pw[e], f16) : q_a;
-                    float p_b = (i_glob > 0) ? hi16_to_f32(pw[e], f16) : q_b;
-                    float a_a = q_a + a.eta * (q_a - p_a), a_b = q_b + a.eta * (q_b - p_b);
-                    uint32_t h_a = f32_to_16(a_a, f16), h_b = f32_to_16(a_b, f16);
-                    uint32_t l_a = f32_to_16(a_a - from16(h_a, f16), f16);
-                    uint32_t l_b = f32_to_16(a_b - from16(h_b, f16), f16);
-                    cw[e] = h_a | (h_b << 16);
-                    pw[e] = l_a | (l_b << 16);
+                    const uint32_t wq = cw[e], wp = (i_glob > 0) ? pw[e] : cw[e];   // row 0 has no predecessor
+                    float2 q, pq;
+                    if (f16) {
+                        q = __half22float2(*reinterpret_cast<const __half2*>(&wq));
+                        pq = __half22float2(*reinterpret_cast<const __half2*>(&wp));
+                    } else {
+                        q = make_float2(__uint_as_float(wq << 16), __uint_as_float(wq & 0xffff0000u));
+                        pq = make_float2(__uint_as_float(wp << 16), __uint_as_float(wp & 0xffff0000u));
+                    }
+                    const float a_a = fmaf(a.eta, q.x - pq.x, q.x), a_b = fmaf(a.eta, q.y - pq.y, q.y);
+                    uint32_t hi, lo;
+                    if (f16) {
+                        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
+                        const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+                        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - hf.y), "f"(a_a - hf.x));
+                    } else {
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
+                        const float h_a = __uint_as_float(hi << 16), h_b = __uint_as_float(hi & 0xffff0000u);
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - h_b), "f"(a_a - h_a));
+                    }
+                    cw[e] = hi;
+                    pw[e] = lo;
                 }
                 *reinterpret_cast<uint4*>(qh + pc) = cur;
                 *reinterpret_cast<uint4*>(ql + pc) = prv;
@@ -483,21 +512,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const int r_first = q0 + g * kBM;
             const bool edge = (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
                               (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
-            auto mask32 = [&](float (&v)[32], int key0) {   // keys key0 .. key0+31 of this row
+            // visible columns of this thread's 64, relative to its first column: [lo_rel, hi_rel];
+            // the column offsets below are compile-time constants, so a masked element costs two
+            // compares against these bounds and a select
+            const int hi_rel = min(i_glob, S - 1) - kh;
+            const int lo_rel = (a.window > 0) ? i_glob - a.window - kh : -(1 << 30);
+            auto mask32 = [&](float (&v)[32], int off) {   // columns off .. off + 31
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int jg = key0 + j;
-                    const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
-                    v[j] = allowed ? v[j] : -INFINITY;
-                }
+                for (int j = 0; j < 32; ++j) v[j] = (off + j <= hi_rel && off + j >= lo_rel) ? v[j] : -INFINITY;
             };
-            auto mask16 = [&](float (&v)[16], int key0) {
+            auto mask16 = [&](float (&v)[16], int off) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int jg = key0 + j;
-                    const bool allowed = (jg <= i_glob) && (jg < S) && (a.window <= 0 || jg >= i_glob - a.window);
-                    v[j] = allowed ? v[j] : -INFINITY;
-                }
+                for (int j = 0; j < 16; ++j) v[j] = (off + j <= hi_rel && off + j >= lo_rel) ? v[j] : -INFINITY;
             };
             float mxh = -INFINITY, s_first = 0.0f;
 #pragma unroll
@@ -505,7 +531,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 float v[32];
                 tc_ld32(tmem_S + 32 * hb, v);
                 tc_wait_ld();
-                if (edge) mask32(v, kh + 32 * hb);
+                if (edge) mask32(v, 32 * hb);
                 float m0 = fmaxf(v[0], v[1]);
 #pragma unroll
                 for (int j = 2; j < 32; j += 2) m0 = fmaxf(fmaxf(m0, v[j]), v[j + 1]);   // three-input maxima
@@ -513,7 +539,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 if (hb == 0) s_first = v[0];
             }
             // trade with the other half of the row
-            float* x = xch + (((k & 1) * 2 + g) * kBM + r) * 4;
+            float* x = xch + (((k & 1) * kTiles + g) * kBM + r) * 4;
             x[half] = mxh * c;
             x[2 + half] = s_first * c;
             mbar_arrive(pair_bar);
@@ -560,18 +586,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             // the FP16 rounding: the two differ by at most 2^-12 relative, far inside the tolerance.
             float nxt = DIFF ? ex2(s_above + neg_m) : 0.0f;             // -inf gives 0
             const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m), rho2 = make_float2(rho, rho);
-            float2 lsum2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-            for (int cb = 3; cb >= 0; --cb) {         // pass 2: highest 16 columns first, the stencil walks downwards
-                float v[16];
-                tc_ld16(tmem_S + 16 * cb, v);
-                tc_wait_ld();
-                if (cb == 0) {                        // the scores have left TMEM: the next S may be written
-                    tc_fence_before();
-                    mbar_arrive(bar(B_SEMPTY0 + g));
-                }
-                if (edge) mask16(v, kh + 16 * cb);
-                float2 P[9];
+            float2 lsum2 = make_float2(0.0f, 0.0f), lsum2b = make_float2(0.0f, 0.0f);
+            // stage A of a 16-column chunk: p = 2^(c s - m) as pairs (key j, key j + 8)
+            auto expo16 = [&](float (&v)[16], int cb, float2 (&P)[9]) {
+                if (edge) mask16(v, 16 * cb);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float2 t = __ffma2_rn(make_float2(v[2 * e], v[2 * e + 1]), c2, nm2);
@@ -579,6 +597,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     if (2 * e < 8) { P[2 * e].x = p0; P[2 * e + 1].x = p1; }
                     else { P[2 * e - 8].y = p0; P[2 * e - 7].y = p1; }
                 }
+            };
+            // stage B: stencil, row sum, FP16 pack, store to the weight columns
+            auto store16 = [&](float2 (&P)[9], int cb) {
                 float2 W[8];
                 if (DIFF) {
                     P[8] = make_float2(P[0].y, nxt);                   // keys 8 and 16 (= first key of the chunk above)
@@ -592,7 +613,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 }
                 uint32_t pk[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) lsum2 = __fadd2_rn(lsum2, W[q]);
+                for (int q = 0; q < 8; q += 2) {
+                    lsum2 = __fadd2_rn(lsum2, W[q]);
+                    lsum2b = __fadd2_rn(lsum2b, W[q + 1]);
+                }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {                          // word e: keys 2e, 2e+1; word 4+e: keys 8+2e, 9+2e
                     __half2 h_lo = __floats2half2_rn(W[2 * e].x, W[2 * e + 1].x);
@@ -601,7 +625,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     pk[4 + e] = *reinterpret_cast<uint32_t*>(&h_hi);
                 }
                 tc_st8(tmem_P + 8 * cb, pk);
+            };
+            // pass 2, highest columns first (the stencil walks downwards).  The exponentials of a chunk
+            // are issued ahead of the previous chunk's stencil / pack / store, and the chunk after it
+            // is already in flight from TMEM.
+            {
+                float va[16], vb[16];
+                float2 Pa[9], Pb[9];
+                tc_ld16(tmem_S + 48, va);
+                tc_wait_ld();
+                tc_ld16(tmem_S + 32, vb);
+                expo16(va, 3, Pa);
+                tc_wait_ld();
+                tc_ld16(tmem_S + 16, va);
+                expo16(vb, 2, Pb);
+                store16(Pa, 3);
+                tc_wait_ld();
+                tc_ld16(tmem_S, vb);
+                expo16(va, 1, Pa);
+                store16(Pb, 2);
+                tc_wait_ld();
+                tc_fence_before();                    // the scores have left TMEM: the next S may be written
+                mbar_arrive(bar(B_SEMPTY0 + g));
+                expo16(vb, 0, Pb);
+                store16(Pa, 1);
+                store16(Pb, 0);
             }
+            lsum2 = __fadd2_rn(lsum2, lsum2b);
             l_run += lsum2.x + lsum2.y;
             tc_wait_st();
             tc_fence_before();
@@ -610,7 +660,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 
         // ---- epilogue: O / l, 32 channels per thread ----
         if (ok && k_last >= 0) {
-            float* x = xch + ((((k_last + 1) & 1) * 2 + g) * kBM + r) * 4;
+            float* x = xch + ((((k_last + 1) & 1) * kTiles + g) * kBM + r) * 4;
             x[half] = l_run;
             mbar_arrive(pair_bar);
             ok = mbar_wait(pair_bar, pair_phase & 1, abort_flag);
