@@ -44,7 +44,7 @@ constexpr int kBQ = kBM * kTiles;     // query rows per CTA
 constexpr int kBN = 128;              // keys per tile
 constexpr int kD = 64;                // head dimension
 constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
-constexpr int kStages = 2;
+constexpr int kStages = 2;              // depth of the K ring and of the V ring (3 and 4 measured no faster)
 constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
 constexpr int kSoftmaxWarps = 8 * kTiles;
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
@@ -63,13 +63,14 @@ constexpr int kOffK = kOffQ + 2 * kTiles * kTileBytes;         // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
 constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [2][2][128] float4
 constexpr int kOffBar = kOffXch + 2 * kTiles * kBM * 16;
-constexpr int kNumBars = 32;
+constexpr int kNumBars = 2 + 5 * kStages + 8 + 8;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
-enum Bar { B_QLOAD = 0, B_QREADY, B_KFULL0, B_KFULL1, B_KEMPTY0, B_KEMPTY1, B_VFULL0, B_VFULL1, B_VEMPTY0, B_VEMPTY1,
-           B_VREADY0, B_VREADY1,
-           B_SFULL0, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
-           B_PAIR0 /* eight: one per warp pair */ };
+enum Bar { B_QLOAD = 0, B_QREADY,
+           B_KFULL0 = 2, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
+           B_VEMPTY0 = B_VFULL0 + kStages, B_VREADY0 = B_VEMPTY0 + kStages,
+           B_SFULL0 = B_VREADY0 + kStages, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
+           B_PAIR0 /* eight: one per warp pair */, B_NUM = B_PAIR0 + 8 };
 
 struct TcArgs {
     void* O;
@@ -380,8 +381,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             bool ok = wait_w(bar(B_QREADY), 0);
 
             auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
-                const int st = i & 1, k = i - it_first;
-                if (!wait_w(bar(B_KFULL0 + st), (i >> 1) & 1)) return false;
+                const int st = i % kStages, k = i - it_first;
+                if (!wait_w(bar(B_KFULL0 + st), (i / kStages) & 1)) return false;
                 if (i >= it_first && i <= it_last) {
                     if (k > 0 && !wait_w(bar(B_SEMPTY0 + g), (k - 1) & 1)) return false;
                     tc_fence_after();
@@ -400,10 +401,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 return true;
             };
             auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
-                const int st = i & 1, k = i - it_first;
+                const int st = i % kStages, k = i - it_first;
                 if (i >= it_first && i <= it_last) {
                     if (!wait_w(bar(B_PFULL0 + g), k & 1)) return false;
-                    if (!wait_w(bar(v_bar + st), (i >> 1) & 1)) return false;
+                    if (!wait_w(bar(v_bar + st), (i / kStages) & 1)) return false;
                     tc_fence_after();
                     const uint32_t vl = v_lo0 + (uint32_t)st * (kTileBytes >> 4);
                     if (leader) {
@@ -416,7 +417,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                         }
                         tc_commit(bar(B_PVDONE0 + g));
                     }
-                } else if (!wait_w(bar(v_bar + st), (i >> 1) & 1)) {
+                } else if (!wait_w(bar(v_bar + st), (i / kStages) & 1)) {
                     return false;   // an idle issuer still paces itself on the tile it releases
                 }
                 if (leader) tc_commit(bar(B_VEMPTY0 + st));
