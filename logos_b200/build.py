@@ -2,7 +2,8 @@
 
     python -m logos_b200.build [--force] [--verbose]
 
-Output: logos_b200/liblogos_attn.so (C ABI of include/logos_attn.h).
+Outputs: logos_b200/liblogos_attn.so (C ABI of include/logos_attn.h) and
+logos_b200/liblogos_attn_shim.so (the reference's C++ symbol cuda_flash_attention_fwd on top of it).
 """
 from __future__ import annotations
 
@@ -14,6 +15,8 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "liblogos_attn.so")
+SHIM = os.path.join(PKG, "liblogos_attn_shim.so")
+SHIM_SRC = os.path.join(PKG, "shim", "logos_attn_shim.cu")
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -26,10 +29,10 @@ def sources() -> list[str]:
 
 
 def stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(SHIM):
         return True
-    t = os.path.getmtime(LIB)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + \
+    t = min(os.path.getmtime(LIB), os.path.getmtime(SHIM))
+    deps = sources() + [SHIM_SRC] + glob.glob(os.path.join(CSRC, "*.cuh")) + \
         glob.glob(os.path.join(PKG, "..", "include", "*.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -59,6 +62,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     subprocess.check_call(["nvcc", "-shared", "--cudart", "static", "-gencode",
                            "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-lcuda"])
+    # the drop-in C++ symbol; finds liblogos_attn.so beside itself
+    subprocess.check_call(["nvcc", "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "--cudart", "static",
+                           "-gencode", "arch=compute_100a,code=sm_100a", "-o", SHIM, SHIM_SRC, "-L" + PKG, "-llogos_attn", "-Xlinker", "-rpath=$ORIGIN"])
     return LIB
 
 

@@ -59,3 +59,14 @@ def test_null_context_is_rejected_without_touching_a_device():
     assert lib.logos_kv_quantize(None, 0, None, 0, None, 0, None, 1, 16) == L.ERR_INVALID_ARG
     assert lib.logos_ctx_destroy(None) == L.OK
     assert lib.logos_decode_workspace_bytes(64, 16, 8192, 64) > 64 * 1024
+
+
+def test_shim_exports_the_reference_symbol():
+    """liblogos_attn_shim.so defines cuda_flash_attention_fwd with the C++ signature the reference
+    declares (cuda/VedicGEMM.cuh:236-243): (const float*, const float*, const float*, float*, float*,
+    int, int, float, bool, bool, int, int)."""
+    import subprocess
+    from logos_b200.build import SHIM, build
+    build()
+    out = subprocess.run(["nm", "-D", "--defined-only", SHIM], capture_output=True, text=True, check=True).stdout
+    assert "_Z24cuda_flash_attention_fwdPKfS0_S0_PfS1_iifbbii" in out
