@@ -58,16 +58,19 @@ constexpr uint32_t kColO = 128 * kTiles, kColP = kColO + 64 * kTiles;   // S fir
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr int kOffQ = 0;                                       // per query tile: hi, lo (4 tiles)
-constexpr int kOffK = kOffQ + 2 * kTiles * kTileBytes;         // kStages tiles
+constexpr int kOffQ = 0;                                       // two buffers (work items alternate), each: per query tile hi, lo
+constexpr int kQBufBytes = 2 * kTiles * kTileBytes;
+constexpr int kOffK = kOffQ + 2 * kQBufBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [2][2][128] float4
-constexpr int kOffBar = kOffXch + 2 * kTiles * kBM * 16;
-constexpr int kNumBars = 2 + 5 * kStages + 8 + 8;
+constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [3][tiles][128] float4 (two step slots, one for the epilogue)
+constexpr int kOffBar = kOffXch + 3 * kTiles * kBM * 16;
+constexpr int kNumBars = 8 + 5 * kStages + 8 + 8;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
-enum Bar { B_QLOAD = 0, B_QREADY,
-           B_KFULL0 = 2, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
+enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buffer
+           B_QREADY0 = 2,                                  // four: Q buffer * 2 + query tile
+           B_QFREE0 = 6,                                   // two: one per Q buffer
+           B_KFULL0 = 8, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
            B_VEMPTY0 = B_VFULL0 + kStages, B_VREADY0 = B_VEMPTY0 + kStages,
            B_SFULL0 = B_VREADY0 + kStages, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
            B_PAIR0 /* eight: one per warp pair */, B_NUM = B_PAIR0 + 8 };
@@ -79,6 +82,7 @@ struct TcArgs {
     float eta, nu;
     int diffuse;        // 0 none, 1 causal
     int window;         // > 0: sliding window active (pure window, no landmarks)
+    int n_qb, BH, n_items;   // query blocks per head, heads, work items = n_qb * BH
     int* status;        // device word: non-zero = a wait ran out
 };
 
@@ -224,34 +228,65 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBar + kNumBars * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // long (late) query blocks first
-    const int bh = blockIdx.y;
-    const int q0 = qb * kBQ;                               // first row of query tile 0; tile 1 starts 128 later
     const int S = a.S;
     const bool f16 = a.in_is_f16 != 0;
     const bool has_lo = a.eta != 0.0f;
-
-    // Global iteration i visits KV tile jt_hi - i.  Query tile g (rows q0 + 128 g ...) takes part in
-    // iterations [i_first[g], i_last[g]]: above its diagonal and below its window it has nothing to do.
     const int jt_max = (S - 1) / kBN;
-    const int jt_hi = min((q0 + kBQ - 1) / kBN, jt_max);
-    // diagonal tile of each query tile, and the lowest tile its window reaches (one key below the
-    // window still feeds the diffusion stencil)
-    const int jt_top0 = min(q0 / kBN, jt_max), jt_top1 = min((q0 + kBM) / kBN, jt_max);
-    const int jt_bot0 = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
-    const int jt_bot1 = (a.window > 0) ? max(0, q0 + kBM - a.window - 1) / kBN : 0;
-    const int jt_lo = kTiles == 2 ? min(jt_bot0, jt_bot1) : jt_bot0;
-    const int n_iter = jt_hi - jt_lo + 1;
-    const bool tile1_live = kTiles == 2 && (q0 + kBM) < S;                // query tile 1 may lie wholly beyond the sequence
+
+    // The CTA is persistent: it works through the items blockIdx.x, blockIdx.x + gridDim.x, ... of the
+    // list of (head, block of 256 query rows), long blocks (late rows) first.  Every role walks the
+    // same list, barriers and rings run on across items (phases come from running counters), and
+    // Q has two buffers, so the loads of the next item and the epilogue of one query tile overlap
+    // the other tile's work instead of standing alone at a CTA's start and end.
+    // Within an item, iteration i visits KV tile jt_hi - i.  Query tile g (rows q0 + 128 g ...) takes
+    // part in iterations [first_iter(g), last_iter(g)]: above its diagonal and below its window it has
+    // nothing to do.
+    int qb = 0, bh = 0, q0 = 0, jt_hi = 0, jt_top0 = 0, jt_top1 = 0, jt_bot0 = 0, jt_bot1 = 0, n_iter = 0;
+    bool tile1_live = false;
+    auto set_item = [&](int t) {
+        qb = a.n_qb - 1 - t / a.BH;
+        bh = t % a.BH;
+        q0 = qb * kBQ;                        // first row of query tile 0; tile 1 starts 128 later
+        jt_hi = min((q0 + kBQ - 1) / kBN, jt_max);
+        // diagonal tile of each query tile, and the lowest tile its window reaches (one key below the
+        // window still feeds the diffusion stencil)
+        jt_top0 = min(q0 / kBN, jt_max);
+        jt_top1 = min((q0 + kBM) / kBN, jt_max);
+        jt_bot0 = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
+        jt_bot1 = (a.window > 0) ? max(0, q0 + kBM - a.window - 1) / kBN : 0;
+        const int jt_lo = kTiles == 2 ? min(jt_bot0, jt_bot1) : jt_bot0;
+        n_iter = jt_hi - jt_lo + 1;
+        tile1_live = kTiles == 2 && (q0 + kBM) < S;   // query tile 1 may lie wholly beyond the sequence
+    };
     auto active = [&](int g, int i) {
         const int jt = jt_hi - i;
         return g == 0 ? (jt <= jt_top0 && jt >= jt_bot0) : (tile1_live && jt <= jt_top1 && jt >= jt_bot1);
     };
     auto first_iter = [&](int g) { return jt_hi - (g == 0 ? jt_top0 : jt_top1); };
+    auto last_iter = [&](int g) { return (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1; };
+    // Items are sorted by length, so the CTAs take them in snake order: round r hands items r G ...
+    // r G + G - 1 to CTAs 0 ... G - 1 in even rounds and G - 1 ... 0 in odd ones.  For the causal
+    // shapes the longest CTA is then within 2 % of the mean (plain round-robin: 14 %).
+    auto item_at = [&](int it) {
+        const int G = (int)gridDim.x, cta = (int)blockIdx.x;
+        return it * G + ((it & 1) ? G - 1 - cta : cta);
+    };
+    auto load_q = [&](int qsel) {     // the item's Q tiles (and the same tiles one row up) into buffer qsel
+        const int nq = (has_lo ? 2 : 1) * (tile1_live ? 2 : 1);
+        mbar_expect_tx(bar(B_QLOAD0 + qsel), nq * kTileBytes);
+        for (int g = 0; g < (tile1_live ? 2 : 1); ++g) {
+            const uint32_t dst = sbase + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes;
+            tma_load_3d(dst, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD0 + qsel));
+            if (has_lo) tma_load_3d(dst + kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD0 + qsel));
+        }
+    };
 
     if (warp == kTmaWarp && lane == 0) {   // the producer sets the barriers up, so that its first loads can go out at once
-        mbar_init(bar(B_QLOAD), 1);
-        mbar_init(bar(B_QREADY), kSoftmaxThreads);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(B_QLOAD0 + b), 1);
+            mbar_init(bar(B_QFREE0 + b), kTiles);     // one commit per MMA issuer
+            for (int g = 0; g < kTiles; ++g) mbar_init(bar(B_QREADY0 + 2 * b + g), kSoftmaxThreads / kTiles);
+        }
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar(B_KFULL0 + s), 1);
             mbar_init(bar(B_KEMPTY0 + s), kTiles);   // one arrival per MMA issuer
@@ -273,14 +308,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         // Q and the first K / V tiles are requested before the rest of the CTA has finished its own
         // set-up (TMEM allocation, the CTA-wide barrier): their latency is the longest of the prologue
         __syncwarp();
+        set_item(item_at(0));
         if (lane == 0) {
-            const int nq = (has_lo ? 2 : 1) * (tile1_live ? 2 : 1);
-            mbar_expect_tx(bar(B_QLOAD), nq * kTileBytes);
-            for (int g = 0; g < (tile1_live ? 2 : 1); ++g) {
-                tma_load_3d(sbase + kOffQ + (2 * g) * kTileBytes, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD));
-                if (has_lo)
-                    tma_load_3d(sbase + kOffQ + (2 * g + 1) * kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD));
-            }
+            load_q(0);
             for (int i = 0; i < min(kStages, n_iter); ++i) {
                 mbar_expect_tx(bar(B_KFULL0 + i), kTileBytes);
                 tma_load_3d(sbase + kOffK + i * kTileBytes, &mapK, 0, (jt_hi - i) * kBN, bh, bar(B_KFULL0 + i));
@@ -307,20 +337,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            // K tiles: a stage is free again as soon as the scores that read it are done
-            for (int i = kStages; i < n_iter; ++i) {
-                const int st = i % kStages, jt = jt_hi - i;
-                if (!mbar_wait(bar(B_KEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
-                tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KFULL0 + st));
+            // Q of the item, then its K tiles: a stage is free again as soon as the scores that read it
+            // are done.  The first item's Q and first tiles are already on their way.
+            int nk = 0;
+            bool ok = true;
+            for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
+                set_item(t);
+                if (it > 0) {
+                    const int qsel = it & 1;
+                    if (it >= 2 && !mbar_wait(bar(B_QFREE0 + qsel), ((it >> 1) - 1) & 1, abort_flag)) break;
+                    load_q(qsel);
+                }
+                for (int i = 0; i < n_iter; ++i, ++nk) {
+                    if (it == 0 && i < kStages) continue;
+                    const int st = nk % kStages, jt = jt_hi - i;
+                    if (nk >= kStages && !mbar_wait(bar(B_KEMPTY0 + st), ((nk / kStages) - 1) & 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
+                    tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KFULL0 + st));
+                }
             }
         } else if (lane == 1) {
             // V tiles on their own ring: needed later and freed later than K, so they never hold K back
-            for (int i = kStages; i < n_iter; ++i) {
-                const int st = i % kStages, jt = jt_hi - i;
-                if (!mbar_wait(bar(B_VEMPTY0 + st), ((i / kStages) - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
-                tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
+            int nv = 0;
+            bool ok = true;
+            for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
+                set_item(t);
+                for (int i = 0; i < n_iter; ++i, ++nv) {
+                    if (it == 0 && i < kStages) continue;
+                    const int st = nv % kStages, jt = jt_hi - i;
+                    if (nv >= kStages && !mbar_wait(bar(B_VEMPTY0 + st), ((nv / kStages) - 1) & 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
+                    tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
+                }
             }
         }
     } else if (warp == kCvtWarp) {
@@ -329,9 +377,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         // weights and V share one type; 1024 16-byte chunks per tile over 32 lanes.
         if (!f16) {
             bool ok = true;
-            for (int i = 0; ok && i < n_iter; ++i) {
-                const int st = i % kStages;
-                if (!mbar_wait(bar(B_VFULL0 + st), (i / kStages) & 1, abort_flag)) { ok = false; break; }
+            int n_total = 0;
+            for (int it = 0, t = item_at(0); t < a.n_items; ++it, t = item_at(it)) {
+                set_item(t);
+                n_total += n_iter;
+            }
+            for (int nv = 0; ok && nv < n_total; ++nv) {
+                const int st = nv % kStages;
+                if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) { ok = false; break; }
                 unsigned char* vt = smem + kOffV + st * kTileBytes;
 #pragma unroll 4
                 for (int q = 0; q < 32; ++q) {
@@ -370,21 +423,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const uint32_t desc_hi = (uint32_t)(smem_desc(0) >> 32);
             auto lo_of = [](uint32_t addr) { return ((addr >> 4) & 0x3FFFu) | (1u << 16); };
             auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
-            const uint32_t qhi_lo = lo_of(sbase + kOffQ + (2 * g) * kTileBytes);
-            const uint32_t qlo_lo = lo_of(sbase + kOffQ + (2 * g + 1) * kTileBytes);
             const uint32_t a_p = tmem + kColP + (uint32_t)g * 64u;
             const uint32_t k_lo0 = lo_of(sbase + kOffK), v_lo0 = lo_of(sbase + kOffV);
             const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + kColO + (uint32_t)g * 64u;
-            const int it_first = first_iter(g);
-            const int it_last = (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1;
             const int v_bar = f16 ? B_VFULL0 : B_VREADY0;
-            bool ok = wait_w(bar(B_QREADY), 0);
+            // running counters: K / V tiles taken from the rings, score tiles and products issued
+            int nt_qk = 0, nt_pv = 0, s_qk = 0, s_pv = 0;
+            int it_first = 0, it_last = -1;
+            uint32_t qhi_lo = 0, qlo_lo = 0;
 
             auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
-                const int st = i % kStages, k = i - it_first;
-                if (!wait_w(bar(B_KFULL0 + st), (i / kStages) & 1)) return false;
+                const int st = nt_qk % kStages;
+                if (!wait_w(bar(B_KFULL0 + st), (nt_qk / kStages) & 1)) return false;
                 if (i >= it_first && i <= it_last) {
-                    if (k > 0 && !wait_w(bar(B_SEMPTY0 + g), (k - 1) & 1)) return false;
+                    // the previous scores of this tile (of this item or the one before) must have left TMEM
+                    if (s_qk > 0 && !wait_w(bar(B_SEMPTY0 + g), (s_qk - 1) & 1)) return false;
                     tc_fence_after();
                     const uint32_t kl = k_lo0 + (uint32_t)st * (kTileBytes >> 4);
                     if (leader) {
@@ -395,16 +448,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                         }
                         tc_commit(bar(B_SFULL0 + g));
                     }
+                    ++s_qk;
                 }
                 if (leader) tc_commit(bar(B_KEMPTY0 + st));   // both issuers arrive, each after its own reads of K(i)
+                ++nt_qk;
                 __syncwarp();
                 return true;
             };
             auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
-                const int st = i % kStages, k = i - it_first;
+                const int st = nt_pv % kStages, k = i - it_first;
                 if (i >= it_first && i <= it_last) {
-                    if (!wait_w(bar(B_PFULL0 + g), k & 1)) return false;
-                    if (!wait_w(bar(v_bar + st), (i / kStages) & 1)) return false;
+                    if (!wait_w(bar(B_PFULL0 + g), s_pv & 1)) return false;
+                    if (!wait_w(bar(v_bar + st), (nt_pv / kStages) & 1)) return false;
                     tc_fence_after();
                     const uint32_t vl = v_lo0 + (uint32_t)st * (kTileBytes >> 4);
                     if (leader) {
@@ -417,18 +472,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                         }
                         tc_commit(bar(B_PVDONE0 + g));
                     }
-                } else if (!wait_w(bar(v_bar + st), (i / kStages) & 1)) {
+                    ++s_pv;
+                } else if (!wait_w(bar(v_bar + st), (nt_pv / kStages) & 1)) {
                     return false;   // an idle issuer still paces itself on the tile it releases
                 }
                 if (leader) tc_commit(bar(B_VEMPTY0 + st));
+                ++nt_pv;
                 __syncwarp();
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (int i = 0; ok && i < n_iter; ++i) {
-                // scores of the next tile first: they only need the previous scores to have left TMEM
-                if (i + 1 < n_iter) ok = issue_qk(i + 1);
-                if (ok) ok = issue_pv(i);
+            bool ok = true;
+            for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
+                set_item(t);
+                const int qsel = it & 1;
+                it_first = first_iter(g);
+                it_last = last_iter(g);
+                qhi_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes);
+                qlo_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g + 1) * kTileBytes);
+                ok = wait_w(bar(B_QREADY0 + 2 * qsel + g), (it >> 1) & 1);   // this tile's Q_adv is in place
+                if (ok) ok = issue_qk(0);
+                for (int i = 0; ok && i < n_iter; ++i) {
+                    // scores of the next tile first: they only need the previous scores to have left TMEM
+                    if (i + 1 < n_iter) ok = issue_qk(i + 1);
+                    if (ok) ok = issue_pv(i);
+                }
+                if (ok && leader) tc_commit(bar(B_QFREE0 + qsel));   // this item's reads of Q are all issued
+                __syncwarp();
             }
         }
     } else {
@@ -441,7 +510,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const int half = (warp >> 2) & 1;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;         // row in tile = TMEM lane
-        const int i_glob = q0 + g * kBM + r;
         const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
         const uint32_t tmem_S = tmem + (uint32_t)g * 128u + (uint32_t)half * 64u + lane_addr;
         const uint32_t tmem_O = tmem + kColO + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
@@ -449,11 +517,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const uint32_t pair_bar = bar(B_PAIR0 + g * 4 + quarter);
         float* xch = reinterpret_cast<float*>(smem + kOffXch);   // [parity][g][row][4]: max0, max1, score col 0, score col 64
         int pair_phase = 0;
-        bool ok = mbar_wait(bar(B_QLOAD), 0, abort_flag);
+        int s_run = 0;               // score tiles of this query tile taken so far, over all items
+        bool ok = true;
+        const float c = a.c;
+        const float rho = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;   // nu <= 1/2 on this path
+
+        for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
+        set_item(t);
+        const int qsel = it & 1;
+        const int i_glob = q0 + g * kBM + r;
+        ok = mbar_wait(bar(B_QLOAD0 + qsel), (it >> 1) & 1, abort_flag);
 
         // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (4 chunks per thread) ----
         if (ok && has_lo && (g == 0 || tile1_live)) {
-            unsigned char* qh = smem + kOffQ + (2 * g) * kTileBytes + r * 128;
+            unsigned char* qh = smem + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes + r * 128;
             unsigned char* ql = qh + kTileBytes;
 #pragma unroll
             for (int cq = 0; cq < 4; ++cq) {
@@ -493,20 +570,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             }
             fence_async_smem();
         }
-        mbar_arrive(bar(B_QREADY));
+        mbar_arrive(bar(B_QREADY0 + 2 * qsel + g));
 
         float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
         float l_run = 0.0f;          // running sum of this thread's weights
         float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
-        const float c = a.c;
-        const float rho = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;   // nu <= 1/2 on this path
         int k_last = -1;
 
         for (int i = 0; ok && i < n_iter; ++i) {
             if (!active(g, i)) continue;
             const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN, kh = k0 + half * kHalf;
             k_last = k;
-            if (!mbar_wait(bar(B_SFULL0 + g), k & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar(B_SFULL0 + g), s_run & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             // pass 1 over this thread's 64 score columns: maximum of the raw scores (c > 0); the scores
             // are read again from TMEM in pass 2 instead of being held in 64 registers
@@ -540,7 +615,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 if (hb == 0) s_first = v[0];
             }
             // trade with the other half of the row
-            float* x = xch + (((k & 1) * kTiles + g) * kBM + r) * 4;
+            float* x = xch + (((s_run & 1) * kTiles + g) * kBM + r) * 4;
             x[half] = mxh * c;
             x[2 + half] = s_first * c;
             mbar_arrive(pair_bar);
@@ -562,7 +637,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             float m_new = want ? mx : m_run;
             if (any && m_new < mx) m_new = mx;       // correcting anyway: take the exact maximum
             // before touching O or the weight buffer the previous O += W V must be complete
-            if (k > 0 && !mbar_wait(bar(B_PVDONE0 + g), (k - 1) & 1, abort_flag)) { ok = false; break; }
+            if (k > 0 && !mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) { ok = false; break; }
             if (any) {
                 tc_fence_after();
                 const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
@@ -657,16 +732,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(B_PFULL0 + g));
+            ++s_run;
         }
 
         // ---- epilogue: O / l, 32 channels per thread ----
         if (ok && k_last >= 0) {
-            float* x = xch + ((((k_last + 1) & 1) * kTiles + g) * kBM + r) * 4;
+            float* x = xch + ((2 * kTiles + g) * kBM + r) * 4;      // the epilogue's own slot
             x[half] = l_run;
             mbar_arrive(pair_bar);
             ok = mbar_wait(pair_bar, pair_phase & 1, abort_flag);
+            ++pair_phase;
             const float l_row = x[0] + x[1];
-            if (ok && mbar_wait(bar(B_PVDONE0 + g), k_last & 1, abort_flag)) {
+            if (ok && mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) {
                 tc_fence_after();
                 float o[32];
                 tc_ld32(tmem_O, o);
@@ -694,6 +771,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 }
             }
         }
+        }   // next work item
     }
 
     // ---- teardown: every role comes here, aborted or not ----
@@ -882,7 +960,6 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
                  void* O, int B, int H, int S, int DH, const logos_attn_params* p) {
     (void)DH;
     const int BH = B * H;
-    if (BH > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention: B*H > 65535");
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O))
         return fail(ctx, LOGOS_ERR_ALIGNMENT, "attention: tensors must be 16-byte aligned");
     if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "attention: status word missing");
@@ -901,7 +978,10 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     a.diffuse = (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CAUSAL) ? 1 : 0;
     a.window = shunyam_active(p->window, S) ? p->window : 0;
     a.status = ctx->tc_status;
-    dim3 grid((S + kBQ - 1) / kBQ, BH);
+    a.n_qb = (S + kBQ - 1) / kBQ;
+    a.BH = BH;
+    a.n_items = a.n_qb * BH;
+    dim3 grid(a.n_items < ctx->sm_count ? a.n_items : ctx->sm_count);   // persistent: one CTA per SM
     if (a.diffuse) {
         LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         prefill_tc_kernel<true><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
