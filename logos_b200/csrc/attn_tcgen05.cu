@@ -13,13 +13,16 @@
 //     which a softmax thread applies to the row it holds in registers.  KV tiles are
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
-// CTA = 256 query rows of one head as two 128-row tiles that share every K/V tile, 640 threads:
+// A work item = 256 query rows of one head as two 128-row tiles that share every K/V tile.  The CTA
+// (640 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
+// rings run on across items, so one item's epilogue overlaps the other tile's work and the next
+// item's loads.  Roles:
 //   warps 0-7 / 8-15  softmax of tile 0 / tile 1.  A query row (= TMEM lane) is shared by two
 //              threads in different warps, each owning 64 of the tile's 128 score columns: they
 //              read S with tcgen05.ld, trade the half-row maximum and the stencil's boundary scores
 //              through shared memory, write FP16 weights to shared memory (128B-swizzled, K-major)
 //              and finally O / l to global memory;
-//   warp 16    TMA producers: lane 0 loads Q, Q_prev once and then K tiles, lane 1 loads V tiles; K and
+//   warp 16    TMA producers: lane 0 loads Q, Q_prev per item (two buffers) and the K tiles, lane 1 the V tiles; K and
 //              V have separate two-stage rings (a K stage is free as soon as its scores are done);
 //   warp 19    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
 //              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond);
