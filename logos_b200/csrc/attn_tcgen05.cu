@@ -19,17 +19,23 @@
 // item's loads.  Roles:
 //   warps 0-7 / 8-15  softmax of tile 0 / tile 1.  A query row (= TMEM lane) is shared by two
 //              threads in different warps, each owning 64 of the tile's 128 score columns: they
-//              read S with tcgen05.ld, trade the half-row maximum and the stencil's boundary scores
-//              through shared memory, write FP16 weights to shared memory (128B-swizzled, K-major)
-//              and finally O / l to global memory;
-//   warp 16    TMA producers: lane 0 loads Q, Q_prev per item (two buffers) and the K tiles, lane 1 the V tiles; K and
-//              V have separate two-stage rings (a K stage is free as soon as its scores are done);
+//              read S with tcgen05.ld (twice: once for the maximum, once for the weights, instead
+//              of holding 64 scores in registers), trade the half-row maximum and the stencil's
+//              boundary scores through shared memory, write FP16 weights back to tensor memory
+//              with tcgen05.st and finally O / l to global memory;
+//   warp 16    TMA producers: lane 0 loads Q, Q_prev per item (two buffers) and the K tiles, lane 1 the
+//              V tiles; K and V have separate two-stage rings (a K stage is free as soon as its scores
+//              are done).  This warp also initialises the barriers, so its first loads leave before
+//              the CTA's set-up (TMEM allocation, first CTA-wide barrier) has finished;
+//   warps 17,18  MMA issuers, one per query tile: S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}) from
+//              shared-memory descriptors, O_g += W_g V (M128 N64 K16 x 8) with W read from tensor
+//              memory; completion via tcgen05.commit; the scores of the next tile are issued before
+//              the current tile's weights are waited for.  The whole warp runs the loop, one elected
+//              lane issues;
 //   warp 19    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
-//              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond);
-//   warps 17,18  MMA issuers (one lane each, one per query tile): S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}), O_g += W_g V
-//              (M128 N64 K16 x 8), completion via tcgen05.commit; the scores of the next tile are
-//              issued before the current tile's weights are waited for.
-// TMEM: columns [0,128) / [128,256) hold S of tile 0 / 1, [256,320) / [320,384) hold O.
+//              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond).
+// TMEM (512 columns): S of tile 0 / 1 at [0,128) / [128,256), O at [256,320) / [320,384), FP16
+// weights (two keys per column) at [384,448) / [448,512).
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA raises an abort
 // flag, all roles leave their loops, TMEM is freed and the status word tells the host.
