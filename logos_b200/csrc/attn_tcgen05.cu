@@ -531,55 +531,66 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         const float c = a.c;
         const float rho = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;   // nu <= 1/2 on this path
 
+        // The set-up of an item's Q (wait for its tiles, form Q_adv in place, tell the issuer) is done for
+        // the first item here and for every later item before the epilogue of the item before it, so that
+        // the next item's first scores are being computed while this item's output is written.
+        // Expects set_item() of that item to be in force.
+        auto prep_q = [&](int it_of) -> bool {
+            const int qsel = it_of & 1;
+            const int i_glob = q0 + g * kBM + r;
+            const bool fine = mbar_wait(bar(B_QLOAD0 + qsel), (it_of >> 1) & 1, abort_flag);
+            // Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (4 chunks per thread)
+            if (fine && has_lo && (g == 0 || tile1_live)) {
+                unsigned char* qh = smem + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes + r * 128;
+                unsigned char* ql = qh + kTileBytes;
+#pragma unroll
+                for (int cq = 0; cq < 4; ++cq) {
+                    const int cidx = half * 4 + cq;
+                    const int pc = (cidx ^ (r & 7)) * 16;
+                    uint4 cur = *reinterpret_cast<uint4*>(qh + pc);
+                    uint4 prv = *reinterpret_cast<uint4*>(ql + pc);
+                    uint32_t* cw = reinterpret_cast<uint32_t*>(&cur);
+                    uint32_t* pw = reinterpret_cast<uint32_t*>(&prv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t wq = cw[e], wp = (i_glob > 0) ? pw[e] : cw[e];   // row 0 has no predecessor
+                        float2 q, pq;
+                        if (f16) {
+                            q = __half22float2(*reinterpret_cast<const __half2*>(&wq));
+                            pq = __half22float2(*reinterpret_cast<const __half2*>(&wp));
+                        } else {
+                            q = make_float2(__uint_as_float(wq << 16), __uint_as_float(wq & 0xffff0000u));
+                            pq = make_float2(__uint_as_float(wp << 16), __uint_as_float(wp & 0xffff0000u));
+                        }
+                        const float a_a = fmaf(a.eta, q.x - pq.x, q.x), a_b = fmaf(a.eta, q.y - pq.y, q.y);
+                        uint32_t hi, lo;
+                        if (f16) {
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
+                            const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - hf.y), "f"(a_a - hf.x));
+                        } else {
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
+                            const float h_a = __uint_as_float(hi << 16), h_b = __uint_as_float(hi & 0xffff0000u);
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - h_b), "f"(a_a - h_a));
+                        }
+                        cw[e] = hi;
+                        pw[e] = lo;
+                    }
+                    *reinterpret_cast<uint4*>(qh + pc) = cur;
+                    *reinterpret_cast<uint4*>(ql + pc) = prv;
+                }
+                fence_async_smem();
+            }
+            mbar_arrive(bar(B_QREADY0 + 2 * qsel + g));
+            return fine;
+        };
+        set_item(item_at(0));
+        if (item_at(0) < a.n_items) ok = prep_q(0);
+
         for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
         set_item(t);
-        const int qsel = it & 1;
         const int i_glob = q0 + g * kBM + r;
-        ok = mbar_wait(bar(B_QLOAD0 + qsel), (it >> 1) & 1, abort_flag);
 
-        // ---- Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (4 chunks per thread) ----
-        if (ok && has_lo && (g == 0 || tile1_live)) {
-            unsigned char* qh = smem + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes + r * 128;
-            unsigned char* ql = qh + kTileBytes;
-#pragma unroll
-            for (int cq = 0; cq < 4; ++cq) {
-                const int cidx = half * 4 + cq;
-                const int pc = (cidx ^ (r & 7)) * 16;
-                uint4 cur = *reinterpret_cast<uint4*>(qh + pc);
-                uint4 prv = *reinterpret_cast<uint4*>(ql + pc);
-                uint32_t* cw = reinterpret_cast<uint32_t*>(&cur);
-                uint32_t* pw = reinterpret_cast<uint32_t*>(&prv);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t wq = cw[e], wp = (i_glob > 0) ? pw[e] : cw[e];   // row 0 has no predecessor
-                    float2 q, pq;
-                    if (f16) {
-                        q = __half22float2(*reinterpret_cast<const __half2*>(&wq));
-                        pq = __half22float2(*reinterpret_cast<const __half2*>(&wp));
-                    } else {
-                        q = make_float2(__uint_as_float(wq << 16), __uint_as_float(wq & 0xffff0000u));
-                        pq = make_float2(__uint_as_float(wp << 16), __uint_as_float(wp & 0xffff0000u));
-                    }
-                    const float a_a = fmaf(a.eta, q.x - pq.x, q.x), a_b = fmaf(a.eta, q.y - pq.y, q.y);
-                    uint32_t hi, lo;
-                    if (f16) {
-                        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
-                        const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-                        asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - hf.y), "f"(a_a - hf.x));
-                    } else {
-                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(a_b), "f"(a_a));
-                        const float h_a = __uint_as_float(hi << 16), h_b = __uint_as_float(hi & 0xffff0000u);
-                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(a_b - h_b), "f"(a_a - h_a));
-                    }
-                    cw[e] = hi;
-                    pw[e] = lo;
-                }
-                *reinterpret_cast<uint4*>(qh + pc) = cur;
-                *reinterpret_cast<uint4*>(ql + pc) = prv;
-            }
-            fence_async_smem();
-        }
-        mbar_arrive(bar(B_QREADY0 + 2 * qsel + g));
 
         float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
         float l_run = 0.0f;          // running sum of this thread's weights
@@ -744,7 +755,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             ++s_run;
         }
 
-        // ---- epilogue: O / l, 32 channels per thread ----
+        // ---- the next item's Q, then this item's epilogue: O / l, 32 channels per thread ----
+        {
+            const int t_next = item_at(it + 1);
+            if (ok && t_next < a.n_items) {
+                set_item(t_next);
+                ok = prep_q(it + 1);
+                set_item(t);
+            }
+        }
         if (ok && k_last >= 0) {
             float* x = xch + ((2 * kTiles + g) * kBM + r) * 4;      // the epilogue's own slot
             x[half] = l_run;

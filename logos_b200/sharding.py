@@ -71,6 +71,35 @@ class ShardedDecoder:
         self.eng.decode_int8(q, q_prev, self.kc, self.vc, self.ks, self.vs, lens, self.params, out=self.out_local)
         return all_gather_heads(self.out_local, self.world, self.group)
 
+    def capture(self, q, q_prev, k_new, v_new, lens):
+        """Record one step over these tensors (append, decode, all-gather) into a CUDA graph.
+
+        A decode step is a handful of short launches; at several GPUs per job each rank's share
+        of the work takes less time than the host needs to issue it, so the step is replayed as
+        one graph launch.  The tensors are the graph's inputs: refill them in place between
+        replays.  Returns the gathered output tensor that every replay writes."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        self.eng.use_stream(side)
+        try:
+            with torch.cuda.stream(side):
+                for _ in range(3):                      # warm-up on the side stream before the capture
+                    self.step(q, q_prev, k_new, v_new, lens)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    gathered = self.step(q, q_prev, k_new, v_new, lens)
+        finally:
+            self.eng.use_stream(torch.cuda.current_stream())
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph, self.graph_out = graph, gathered
+        return gathered
+
+    def replay(self):
+        """Launch the captured step on the current stream; returns the gathered output tensor."""
+        self.graph.replay()
+        return self.graph_out
+
     def step_host(self, q, q_prev, k_new, v_new, lens, out):
         """Pinned HOST tensors in (this rank's heads) and out ([B, H, DH] fp32, pinned host)."""
         if self.world == 1:

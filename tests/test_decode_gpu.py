@@ -167,3 +167,31 @@ def test_argument_errors(engine):
     with pytest.raises(L.LogosError) as e:
         engine.decode_int8(q, q, z8_32, z8_32, one, one, lens, p)
     assert e.value.status == L.ERR_UNSUPPORTED
+
+
+def test_decode_step_replayed_as_cuda_graph(engine):
+    """ShardedDecoder.capture / replay: the graph's inputs are refilled in place between replays and
+    every replay gives bit for bit what the eager step gives on the same inputs."""
+    from logos_b200.sharding import ShardedDecoder
+    B, H, S_max, DH = 3, 4, 600, 64
+    g = torch.Generator(device="cuda").manual_seed(77)
+    kc = torch.randint(-127, 128, (B, H, S_max, DH), generator=g, device="cuda", dtype=torch.int8)
+    vc = torch.randint(-127, 128, (B, H, S_max, DH), generator=g, device="cuda", dtype=torch.int8)
+    ks = torch.rand((B, H), generator=g, device="cuda") * 0.05 + 0.01
+    vs = torch.rand((B, H), generator=g, device="cuda") * 0.05 + 0.01
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    dec = ShardedDecoder(engine, kc.clone(), vc.clone(), ks, vs, p)
+    ref = ShardedDecoder(engine, kc.clone(), vc.clone(), ks, vs, p)
+    q, qp, kn, vn = (torch.randn((B, H, DH), generator=g, device="cuda").half() for _ in range(4))
+    lens = torch.tensor([600, 333, 17], dtype=torch.int32, device="cuda")
+    out = dec.capture(q, qp, kn, vn, lens)
+    for rnd in range(3):
+        for t in (q, qp, kn, vn):
+            t.copy_(torch.randn((B, H, DH), generator=g, device="cuda").half())
+        lens.copy_(torch.tensor([600 - rnd, 333 + rnd, 17 + 5 * rnd], dtype=torch.int32, device="cuda"))
+        got = dec.replay().clone()
+        want = ref.step(q, qp, kn, vn, lens).clone()
+        torch.cuda.synchronize()
+        assert got.data_ptr() != want.data_ptr() and out is dec.graph_out
+        assert torch.equal(got, want), f"round {rnd}"
+        assert torch.equal(dec.kc, ref.kc) and torch.equal(dec.vc, ref.vc)

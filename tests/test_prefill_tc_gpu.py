@@ -106,3 +106,23 @@ def test_full_size_sampled(engine):
         for (r0, r1) in [(0, 130), (2040, 2060), (4090, 4096)]:
             want = O.attention_rows(q, k, v, op, r0, r1)
             assert_close(out[b, h, r0:r1].cpu().numpy(), want, f"head {(b, h)} rows {r0}:{r1}")
+
+
+@pytest.mark.parametrize("case", [CASES[1], CASES[3]])
+def test_many_ragged_items_per_cta(engine, engine_general, case):
+    """600 work items of five different lengths on the persistent CTAs, the last block of every
+    head with its second query tile beyond the sequence: the whole output against the engine's fp32
+    kernel, sampled heads against the oracle."""
+    B, H, S = 3, 40, 1100
+    w, eta, nu, mode = case
+    g = torch.Generator(device="cuda").manual_seed(61)
+    Q, K, V = (torch.randn((B, H, S, 64), device="cuda", generator=g).bfloat16() for _ in range(3))
+    p = L.Params.make(0.125, True, w, 0, eta, nu, 1.0, mode)
+    got = engine.attention(Q, K, V, p, out_dtype=torch.float32)
+    engine.synchronize()
+    ref = engine_general.attention(Q, K, V, p, out_dtype=torch.float32)
+    assert_close(got.cpu().numpy(), ref.cpu().numpy(), f"case={case} vs fp32 kernel")
+    op = O.attn_params(0.125, True, w, 0, eta, nu, 1.0, mode)
+    for (b, h) in [(0, 0), (1, 17), (2, 39)]:
+        q, k, v = (t[b, h].float().cpu().numpy() for t in (Q, K, V))
+        assert_close(got[b, h].cpu().numpy(), O.attention_rows(q, k, v, op), f"case={case} head {(b, h)} vs oracle")
