@@ -16,6 +16,7 @@ the same step through the host-buffer entry point with the copies inside the tim
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -260,7 +261,8 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that falls out must end the others with an error, not leave them waiting
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     eng = Engine(local_rank)
     lo, hi = head_range(H, rank, world)
     Hl = hi - lo
