@@ -591,7 +591,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         set_item(t);
         const int i_glob = q0 + g * kBM + r;
 
-
         float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
         float l_run = 0.0f;          // running sum of this thread's weights
         float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
@@ -650,7 +649,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 s_carry = x[2];
             }
             // move the reference maximum only when it would grow by more than the threshold (weights
-            // stay below 2^8, well inside FP16); the decision is warp-wide because the O correction is
+            // stay below 2^9, well inside FP16); the decision is warp-wide because the O correction is
             // a warp-collective TMEM access, and identical in both warps of a pair (same rows, same data)
             const bool want = (mx > m_run + kRescaleThreshold) || (m_run == -INFINITY && mx > -INFINITY);
             const bool any = __any_sync(0xffffffffu, want && k > 0 && m_run > -INFINITY);
