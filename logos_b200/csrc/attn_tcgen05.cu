@@ -620,18 +620,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = (off + j <= hi_rel && off + j >= lo_rel) ? v[j] : -INFINITY;
             };
-            float mxh = -INFINITY, s_first = 0.0f;
-#pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                float v[32];
-                tc_ld32(tmem_S + 32 * hb, v);
+            float mxh, s_first;
+            {
+                float v0[32], v1[32];                 // both loads in flight before the first use
+                tc_ld32(tmem_S, v0);
+                tc_ld32(tmem_S + 32, v1);
                 tc_wait_ld();
-                if (edge) mask32(v, 32 * hb);
-                float m0 = fmaxf(v[0], v[1]);
+                if (edge) {
+                    mask32(v0, 0);
+                    mask32(v1, 32);
+                }
+                float m0 = fmaxf(v0[0], v0[1]), m1 = fmaxf(v1[0], v1[1]);
 #pragma unroll
-                for (int j = 2; j < 32; j += 2) m0 = fmaxf(fmaxf(m0, v[j]), v[j + 1]);   // three-input maxima
-                mxh = fmaxf(mxh, m0);
-                if (hb == 0) s_first = v[0];
+                for (int j = 2; j < 32; j += 2) {     // three-input maxima, two chains
+                    m0 = fmaxf(fmaxf(m0, v0[j]), v0[j + 1]);
+                    m1 = fmaxf(fmaxf(m1, v1[j]), v1[j + 1]);
+                }
+                mxh = fmaxf(m0, m1);
+                s_first = v0[0];
             }
             // trade with the other half of the row
             float* x = xch + (((s_run & 1) * kTiles + g) * kBM + r) * 4;
