@@ -112,6 +112,18 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
                         const logos_attn_params* params);
 size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
 
+/* Prefill of one layer in one call: logos_attention_fwd, and before it -- when k_cache is non-NULL --
+ * the layer's INT8 cache filled from the raw K and V.  This is the order of ModelGPU::forward, which
+ * quantises a head's K and V (cuda/ModelGPU.cu:908) before the Navier-Stokes prologue and the attention
+ * (cuda/ModelGPU.cu:915-968), done here for all heads at once.
+ * k_cache, v_cache: int8 [B][H][S_max][DH], rows [0, S) of every (b, h) tensor are written;
+ * k_scale, v_scale: float [B][H].  The four are given together or all NULL; S <= S_max.
+ * Bytes and scales are those of logos_kv_quantize, the output that of logos_attention_fwd. */
+int logos_prefill_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                      const void* V, void* O, int B, int H, int S, int DH,
+                      const logos_attn_params* params, int8_t* k_cache, int8_t* v_cache,
+                      float* k_scale, float* v_scale, int S_max);
+
 /* Hardware bring-up check of the tensor-core building blocks (TMA tile load with 128-byte
  * swizzle, tcgen05.mma from shared-memory descriptors, TMEM read-back) on one 128-row tile;
  * no counterpart in the reference.  dtype: LOGOS_BF16 or LOGOS_F16.

@@ -192,6 +192,34 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
     return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
 }
 
+int logos_prefill_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                      const void* V, void* O, int B, int H, int S, int DH,
+                      const logos_attn_params* params, int8_t* k_cache, int8_t* v_cache,
+                      float* k_scale, float* v_scale, int S_max) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    const int given = (k_cache != nullptr) + (v_cache != nullptr) + (k_scale != nullptr) + (v_scale != nullptr);
+    if (given != 0 && given != 4)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "prefill_fwd: caches and scales are given together or not at all");
+    if (given == 4) {
+        if (!K || !V || B <= 0 || H <= 0 || S <= 0 || DH <= 0 || S > S_max)
+            return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "prefill_fwd: bad pointer or extent (S=%d, S_max=%d)", S, S_max);
+        // the raw K and V, before diffusion; at most 65535 tensors per quantise call
+        const int64_t elems = (int64_t)S * DH, dst_stride = (int64_t)S_max * DH;
+        const size_t esz = in_dtype == LOGOS_F32 ? 4 : 2;
+        const int n = B * H;
+        for (int t0 = 0; t0 < n; t0 += 32768) {
+            const int nt = n - t0 < 32768 ? n - t0 : 32768;
+            int rc = logos::kv_quantize(ctx, in_dtype, (const char*)K + (size_t)t0 * elems * esz, elems,
+                                        k_cache + (size_t)t0 * dst_stride, dst_stride, k_scale + t0, nt, elems);
+            if (rc != LOGOS_OK) return rc;
+            rc = logos::kv_quantize(ctx, in_dtype, (const char*)V + (size_t)t0 * elems * esz, elems,
+                                    v_cache + (size_t)t0 * dst_stride, dst_stride, v_scale + t0, nt, elems);
+            if (rc != LOGOS_OK) return rc;
+        }
+    }
+    return logos_attention_fwd(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+}
+
 int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,
                       int8_t* dst, int64_t dst_stride, float* scales, int n_tensors,
                       int64_t elems) {

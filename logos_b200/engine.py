@@ -83,6 +83,20 @@ class Engine:
         return out
 
     # ---- Nikhilam INT8 KV ----------------------------------------------------
+    def prefill(self, Q, K, V, params: L.Params, k_cache, v_cache, k_scale, v_scale, out_dtype=None, out=None):
+        """One layer's prefill in one call: the raw K, V ([B,H,S,DH]) quantised into rows [0, S) of the
+        INT8 caches ([B,H,S_max,DH]) with their scales ([B,H]), then the attention -> O [B,H,S,DH]."""
+        B, H, S, DH = Q.shape
+        assert Q.is_contiguous() and K.is_contiguous() and V.is_contiguous()
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[:2]) == (B, H)
+        out_dtype = out_dtype or Q.dtype
+        if out is None:
+            out = torch.empty((B, H, S, DH), dtype=out_dtype, device=Q.device)
+        self._check(self.lib.logos_prefill_fwd(self.h, _DT[Q.dtype], _DT[out.dtype], _ptr(Q), _ptr(K), _ptr(V),
+                                              _ptr(out), B, H, S, DH, C.byref(params), _ptr(k_cache), _ptr(v_cache),
+                                              _ptr(k_scale), _ptr(v_scale), k_cache.shape[2]))
+        return out
+
     def nikhilam_compress(self, x, cache=None, rows=None):
         """x: [..., S, DH] (any leading dims = independent tensors) -> (int8 like x, scales[...]).
 

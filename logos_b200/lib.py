@@ -54,6 +54,7 @@ SIGNATURES = {
     "logos_last_error": (C.c_char_p, [_vp]),
     "logos_flash_attention_fwd_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),
     "logos_attention_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
+    "logos_prefill_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp, _vp, _vp, _vp, _i]),
     "logos_selftest_umma": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "logos_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_kv_quantize": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i, _i64]),

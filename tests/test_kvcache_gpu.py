@@ -71,3 +71,33 @@ def test_two_layer_generation_over_the_arena(engine, tmp_path):
     for l in range(LAYERS):
         kc, vc, _, _ = cache.layer(l)
         assert np.array_equal(kc.cpu().numpy(), ref[l][0]) and np.array_equal(vc.cpu().numpy(), ref[l][1])
+
+
+def test_prefill_in_one_call_fills_the_cache(engine):
+    """logos_prefill_fwd = logos_kv_quantize of the raw K and V + logos_attention_fwd, bit for bit."""
+    B, H, S, S_max, DH = 2, 3, 200, 256, 64
+    dev = lambda a: torch.from_numpy(a).cuda().bfloat16()
+    Q, K, V = (dev(syn.normal_with_outliers((B, H, S, DH), 97, t)) for t in (1, 2, 3))
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    kc = torch.zeros((B, H, S_max, DH), dtype=torch.int8, device="cuda")
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros((B, H), dtype=torch.float32, device="cuda")
+    vs = torch.zeros_like(ks)
+    out = engine.prefill(Q, K, V, p, kc, vc, ks, vs, out_dtype=torch.float32)
+    engine.synchronize()
+    kq, ks2 = engine.nikhilam_compress(K)
+    vq, vs2 = engine.nikhilam_compress(V)
+    want = engine.attention(Q, K, V, p, out_dtype=torch.float32)
+    engine.synchronize()
+    assert torch.equal(kc[:, :, :S], kq) and torch.equal(vc[:, :, :S], vq)
+    assert int(kc[:, :, S:].abs().sum()) == 0 and int(vc[:, :, S:].abs().sum()) == 0
+    assert torch.equal(ks, ks2) and torch.equal(vs, vs2)
+    assert torch.equal(out, want)
+    # the cache bytes against the oracle as well, for one head
+    q_o, s_o = O.nikhilam_compress(K[1, 2].float().cpu().numpy())
+    assert np.array_equal(kc[1, 2, :S].cpu().numpy(), q_o) and np.float32(ks[1, 2].item()) == s_o
+    # caches and scales travel together
+    rc = engine.lib.logos_prefill_fwd(engine.h, L.BF16, L.F32, Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(),
+                                      B, H, S, DH, __import__("ctypes").byref(p), kc.data_ptr(), None, ks.data_ptr(),
+                                      vs.data_ptr(), S_max)
+    assert rc == L.ERR_INVALID_ARG
