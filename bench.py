@@ -349,7 +349,6 @@ def run_ours(args) -> None:
             all_gather_heads(d.out_local, world)
     ev[1].record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     step_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / args.steps)
     kern_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in kev) / args.steps)
 
@@ -370,6 +369,7 @@ def run_ours(args) -> None:
         ev[1].record()
         barrier()
         graph_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / args.steps)
+    clocks = sampler.stop() if rank == 0 else None      # sampled over the eager and the replayed loop
     eager_ms = step_ms
     if graph_ms is not None:      # `value` is the replayed step whenever it was measured
         step_ms = graph_ms
