@@ -127,20 +127,23 @@ def test_full_size_benchmark_shape(engine):
     assert np.abs(a - b_).max() < 1e-5
 
 
-def test_host_step_entry_point(engine):
-    """logos_decode_step_int8_host == append + decode on device tensors."""
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_step_entry_point(engine, pinned):
+    """logos_decode_step_int8_host == append + decode on device tensors, with page-locked host
+    buffers (new K/V rows and the output are not staged) and with pageable ones (everything is)."""
     B, H, S_max, DH = 4, 4, 512, 64
     lens0 = np.array([10, 100, 300, 511], np.int32)
     kq, vq, ks, vs = make_cache(B, H, S_max, lens0, 21)
     dev = lambda a: torch.from_numpy(a).cuda()
     kc, vc, ksd, vsd = dev(kq), dev(vq), dev(ks), dev(vs)
     kc2, vc2 = kc.clone(), vc.clone()
-    q = torch.randn(B, H, DH).half().pin_memory()
-    qp = torch.randn(B, H, DH).half().pin_memory()
-    kn = torch.randn(B, H, DH).half().pin_memory()
-    vn = torch.randn(B, H, DH).half().pin_memory()
-    lens = torch.from_numpy(lens0 + 1).pin_memory()
-    out = torch.empty(B, H, DH).pin_memory()
+    host = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    q = host(torch.randn(B, H, DH).half())
+    qp = host(torch.randn(B, H, DH).half())
+    kn = host(torch.randn(B, H, DH).half())
+    vn = host(torch.randn(B, H, DH).half())
+    lens = host(torch.from_numpy(lens0 + 1))
+    out = host(torch.full((B, H, DH), float("nan")))
     p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
     engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
     engine.decode_step_host(q, qp, kn, vn, kc, vc, ksd, vsd, lens, p, out)
