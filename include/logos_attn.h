@@ -79,7 +79,8 @@ int logos_ctx_destroy(logos_ctx* ctx);
 /* cudaStream_t as void*; NULL selects the legacy default stream (reference behaviour:
  * every launch in cuda/ModelGPU.cu and cuda/VedicGEMM.cu is on stream 0). */
 int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream);
-/* Grows the context-owned workspace to at least `bytes` (cudaMalloc; not a hot call). */
+/* Grows the context-owned workspace to at least `bytes` (cudaMalloc; not a hot call).  Growing frees
+ * the old block: see LOGOS_OPT_WORKSPACE_LOCK when captured graphs use it. */
 int logos_ctx_reserve(logos_ctx* ctx, size_t bytes);
 /* Uses caller memory as workspace instead (256-byte aligned device memory). */
 int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes);
@@ -89,6 +90,23 @@ int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes);
 int logos_ctx_synchronize(logos_ctx* ctx);
 /* Text of the last failure on this context (owned by the context). */
 const char* logos_last_error(const logos_ctx* ctx);
+
+/* Switches of a context; they replace what the reference reads from GPUPhysicsConfig at build time
+ * (cuda/ModelGPU.cuh:67-82) and are never read from the environment.
+ *   LOGOS_OPT_FORCE_GENERAL  1: every attention call takes the exact fp32 kernel (tests compare the
+ *                            tensor-core kernels with it); 0 (default): normal dispatch.
+ *   LOGOS_OPT_DECODE_CHUNK   keys per split of the dense decode kernel: 128, 256, 512 or 1024;
+ *                            0 (default) = chosen from the problem size.  Results of two calls are
+ *                            bit-identical only when they use the same chunk.
+ *   LOGOS_OPT_PEER_WAIT_MS   longest time a kernel waits for the other GPUs of a logos_comm before it
+ *                            gives up and raises LOGOS_ERR_KERNEL_TIMEOUT (default 2000).
+ *   LOGOS_OPT_WORKSPACE_LOCK 1: logos_ctx_reserve / logos_ctx_set_workspace calls that would replace
+ *                            the workspace fail with LOGOS_ERR_WORKSPACE.  A CUDA graph captured from
+ *                            decode calls holds the workspace's address: lock it for as long as such
+ *                            a graph can still be launched. */
+typedef enum { LOGOS_OPT_FORCE_GENERAL = 0, LOGOS_OPT_DECODE_CHUNK = 1, LOGOS_OPT_PEER_WAIT_MS = 2,
+               LOGOS_OPT_WORKSPACE_LOCK = 3 } logos_option;
+int logos_ctx_set_option(logos_ctx* ctx, int option, int value);
 
 /* ---- attention ---------------------------------------------------------- */
 
@@ -209,6 +227,51 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
                               const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                               const float* v_scale, const int32_t* len, int B, int H, int S_max,
                               int DH, const logos_attn_params* params, float* out);
+
+/* ---- heads over several GPUs -------------------------------------------- */
+
+/* The path shards by (sequence, head): GPU r of N owns heads [r H/N, (r+1) H/N) and their cache, and
+ * the only exchange is the all-gather of the per-head outputs along the head axis.  The reference has
+ * no counterpart (its head loop is serial on one GPU, cuda/ModelGPU.cu:892-988).  A logos_comm is one
+ * rank's end of that exchange: a block of device memory that the other ranks map and write with
+ * ordinary peer stores (no TMA, no multicast), two staging slots of `gathered_bytes` each plus flags.
+ *   set-up, once:  logos_comm_create on every rank; then either
+ *                    logos_comm_handle -> exchange the 64-byte handles by any means -> logos_comm_connect
+ *                    (one process per GPU: the blocks are shared through CUDA IPC), or
+ *                    logos_comm_connect_local (all ranks are contexts of one process).
+ *   per step:      a producing call (logos_decode_int8_push, logos_comm_push) stores this rank's rows
+ *                  into every rank's staging slot and raises this rank's flag; logos_comm_wait queues a
+ *                  kernel that waits for all ranks' flags of the step -- at most LOGOS_OPT_PEER_WAIT_MS,
+ *                  then logos_ctx_synchronize reports LOGOS_ERR_KERNEL_TIMEOUT -- and copies the slot to
+ *                  `gathered`.  Exactly one producing call per wait, in the same order on every rank.
+ * The step counter is device memory, so a CUDA graph that holds a step replays unchanged.  Nothing here
+ * allocates after logos_comm_create; destroy the comm after its last kernel has finished. */
+typedef struct logos_comm logos_comm;
+#define LOGOS_COMM_HANDLE_BYTES 64
+int logos_comm_create(logos_ctx* ctx, int rank, int world, size_t gathered_bytes, logos_comm** out);
+int logos_comm_handle(logos_comm* comm, void* handle_out /* LOGOS_COMM_HANDLE_BYTES */);
+int logos_comm_connect(logos_comm* comm, const void* handles /* world x LOGOS_COMM_HANDLE_BYTES, rank order */);
+int logos_comm_connect_local(logos_comm* const* comms /* [world], rank order */, int world);
+int logos_comm_destroy(logos_comm* comm);
+
+/* logos_decode_int8 over this rank's H_local heads whose merged rows go straight from the kernel's
+ * epilogue into every rank's staging slot at head offset rank * H_local (the gathered tensor is
+ * float [B][H_local * world][DH]); no separate gather pass and no library collective. */
+int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                           const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
+                           const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
+                           const logos_attn_params* params);
+/* logos_decode_int8_push followed by logos_comm_wait into `gathered` (float [B][H_local * world][DH]). */
+int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                             const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
+                             const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
+                             const logos_attn_params* params, float* gathered);
+/* The same exchange for any per-head tensor this rank has already computed (the prefill output):
+ * local is [B][H_local][row_bytes], gathered [B][H_local * world][row_bytes]; row_bytes a multiple of 16. */
+int logos_comm_push(logos_ctx* ctx, logos_comm* comm, const void* local, int B, int H_local, size_t row_bytes);
+int logos_comm_wait(logos_ctx* ctx, logos_comm* comm, void* gathered, size_t bytes);
+int logos_comm_all_gather_heads(logos_ctx* ctx, logos_comm* comm, const void* local, void* gathered, int B,
+                                int H_local, size_t row_bytes);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,5 @@
 // abi.cu -- the extern "C" surface declared in include/logos_attn.h: context
 // management, argument checks and dispatch to the kernels.
-#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -64,8 +63,6 @@ int logos_ctx_create(int device, logos_ctx** out) {
         delete ctx;
         return LOGOS_ERR_CUDA;
     }
-    const char* force = getenv("LOGOS_ATTN_FORCE_GENERAL");
-    ctx->force_general = force && force[0] == '1';
     *out = ctx;
     return LOGOS_OK;
 }
@@ -89,6 +86,9 @@ int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream) {
 int logos_ctx_reserve(logos_ctx* ctx, size_t bytes) {
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
     if (ctx->workspace && ctx->workspace_bytes >= bytes) return LOGOS_OK;
+    if (ctx->workspace_locked)
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "reserve: the workspace is locked (a captured graph uses it) and holds "
+                           "%zu bytes, %zu wanted; reserve the largest size before capturing", ctx->workspace_bytes, bytes);
     LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     // Work queued on the stream may still use the old block.
     LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -110,6 +110,8 @@ int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes) {
     if (!ctx || (!device_ptr && bytes)) return LOGOS_ERR_INVALID_ARG;
     if (reinterpret_cast<uintptr_t>(device_ptr) & 255u)
         return logos::fail(ctx, LOGOS_ERR_ALIGNMENT, "workspace must be 256-byte aligned");
+    if (ctx->workspace_locked)
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "set_workspace: the workspace is locked (a captured graph uses it)");
     LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
@@ -127,6 +129,10 @@ int logos_ctx_synchronize(logos_ctx* ctx) {
     LOGOS_CUDA_TRY(ctx, cudaMemcpy(&flag, ctx->tc_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(ctx->tc_status, 0, sizeof(int));
+        if (flag & 0x20000000)
+            return logos::fail(ctx, LOGOS_ERR_KERNEL_TIMEOUT,
+                               "rank %d of the comm did not deliver its rows within %d ms; the gathered output is invalid",
+                               (flag >> 16) & 0xff, ctx->peer_wait_ms);
         return logos::fail(ctx, LOGOS_ERR_KERNEL_TIMEOUT,
                            "a bounded wait inside a kernel ran out (barrier %d, thread %d); results of that call are invalid",
                            (flag & 0xffff) / 8, (flag >> 16) & 0x3fff);
@@ -135,6 +141,29 @@ int logos_ctx_synchronize(logos_ctx* ctx) {
 }
 
 const char* logos_last_error(const logos_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    switch (option) {
+        case LOGOS_OPT_FORCE_GENERAL:
+            ctx->force_general = value != 0;
+            return LOGOS_OK;
+        case LOGOS_OPT_DECODE_CHUNK:
+            if (value != 0 && value != 128 && value != 256 && value != 512 && value != 1024)
+                return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: decode chunk must be 0, 128, 256, 512 or 1024");
+            ctx->decode_chunk = value;
+            return LOGOS_OK;
+        case LOGOS_OPT_PEER_WAIT_MS:
+            if (value < 1 || value > 60000)
+                return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: peer wait must be 1..60000 ms");
+            ctx->peer_wait_ms = value;
+            return LOGOS_OK;
+        case LOGOS_OPT_WORKSPACE_LOCK:
+            ctx->workspace_locked = value != 0;
+            return LOGOS_OK;
+    }
+    return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: unknown option %d", option);
+}
 
 int logos_flash_attention_fwd_f32(logos_ctx* ctx, const float* Q, const float* K, const float* V,
                                   float* out, float* attn_ptr, int seq, int DH, float scale,
@@ -257,6 +286,34 @@ int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const i
     return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
 }
 
+int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                           const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
+                           const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
+                           const logos_attn_params* params) {
+    if (!ctx || !comm) return LOGOS_ERR_INVALID_ARG;
+    if (comm->ctx != ctx || !comm->connected)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: comm is not connected or belongs to another context");
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: bad parameter block");
+    if (B <= 0 || H_local <= 0 || DH <= 0 || (size_t)B * H_local * comm->world * DH * sizeof(float) > comm->slot_bytes)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: gathered output exceeds the comm's slot of %zu bytes",
+                           comm->slot_bytes);
+    PeerEpilogue pe;
+    logos::comm_peer_epilogue(comm, H_local, &pe);
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
+                              nullptr, &pe);
+}
+
+int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                             const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
+                             const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
+                             const logos_attn_params* params, float* gathered) {
+    const int rc = logos_decode_int8_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local,
+                                          S_max, DH, params);
+    if (rc != LOGOS_OK) return rc;
+    return logos::comm_wait(ctx, comm, gathered, (size_t)B * H_local * comm->world * DH * sizeof(float));
+}
+
 int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* q_prev_host,
                                 const void* k_new_host, const void* v_new_host,
                                 int8_t* k_cache, int8_t* v_cache, const float* k_scale,
@@ -274,6 +331,7 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
     if (!ctx->workspace || ctx->workspace_bytes < need)
         return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "decode_step_host: workspace of %zu bytes needed, %zu reserved",
                            need, ctx->workspace_bytes);
+    if (B > 4096) return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_step_host: B > 4096");
     for (int b = 0; b < B; ++b)
         if (len_host[b] < 1 || len_host[b] > S_max)
             return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: len[%d]=%d outside [1,%d]", b,
@@ -296,7 +354,6 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, v_new_host, hb, cudaMemcpyHostToDevice, st));
     // len and pos = len - 1 travel as one small copy
     int32_t small[2 * 4096];
-    if (B > 4096) return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_step_host: B > 4096");
     for (int b = 0; b < B; ++b) { small[b] = len_host[b]; small[B + b] = len_host[b] - 1; }
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_len, small, sizeof(int32_t) * 2 * B, cudaMemcpyHostToDevice, st));
     int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_pos, B, H, S_max, DH);

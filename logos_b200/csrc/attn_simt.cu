@@ -227,14 +227,17 @@ int launch(logos_ctx* ctx, const SimtArgs& a, int BH, bool blend) {
     size_t floats = (size_t)BM * DH * (blend ? 2 : 1) + (size_t)BN * (DH + 1) +
                     (size_t)BN * DH * (blend ? 2 : 1) + (size_t)BM * BN * (blend ? 2 : 1);
     size_t smem = floats * sizeof(float);
+    // the limit is raised once, to what the largest head dimension needs
+    const int smem_max = (int)(sizeof(float) * ((size_t)BM * kMaxDH * (blend ? 2 : 1) + (size_t)BN * (kMaxDH + 1) +
+                                                (size_t)BN * kMaxDH * (blend ? 2 : 1) + (size_t)BM * BN * (blend ? 2 : 1)));
     dim3 grid((a.S + BM - 1) / BM, BH);
     if (blend) {
-        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_simt_kernel<TIn, TOut, true>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int rc = ensure_smem_limit(ctx, attention_simt_kernel<TIn, TOut, true>, smem_max);
+        if (rc != LOGOS_OK) return rc;
         attention_simt_kernel<TIn, TOut, true><<<grid, kThreads, smem, ctx->stream>>>(a);
     } else {
-        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(attention_simt_kernel<TIn, TOut, false>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int rc = ensure_smem_limit(ctx, attention_simt_kernel<TIn, TOut, false>, smem_max);
+        if (rc != LOGOS_OK) return rc;
         attention_simt_kernel<TIn, TOut, false><<<grid, kThreads, smem, ctx->stream>>>(a);
     }
     LOGOS_LAUNCH_CHECK(ctx, "attention_simt_kernel");

@@ -123,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
     // record who gave up first: bits [0,16) = shared-memory address of the barrier, [16,30) = thread id
-    atomicCAS(const_cast<int*>(abort_flag), 0, (int)((bar & 0xffffu) | (threadIdx.x << 16)) | 0x40000000);
+    atomicCAS(const_cast<int*>(abort_flag), 0, (int)((bar & 0xffffu) | (threadIdx.x << 16)) | 0x40000000);   // the kernel's teardown turns the address into an offset
     return false;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
@@ -810,7 +810,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // ---- teardown: every role comes here, aborted or not ----
     tc_fence_before();
     __syncthreads();
-    if (*abort_flag && tid == 0) atomicExch(a.status, *abort_flag - (int)(bar0 & 0xffffu));   // barrier offset + thread
+    if (*abort_flag && tid == 0) {   // low half: the barrier's offset from the first one (mod 64 KiB); the rest stays as recorded
+        const int f = *abort_flag;
+        atomicExch(a.status, (f & ~0xffff) | ((f - (int)(bar0 & 0xffffu)) & 0xffff));
+    }
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -968,7 +971,7 @@ int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void
     if (!make_map(&ma, mode == 0 ? A : B, 1, kBM, f16) || !make_map(&mb, B, 1, kBM, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "selftest: cuTensorMapEncodeTiled failed");
     const int smem = 3 * kTileBytes + 64 + 1024;
-    LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (int rc = ensure_smem_limit(ctx, umma_selftest_kernel, smem)) return rc;
     umma_selftest_kernel<<<1, 128, smem, ctx->stream>>>(ma, mb, (const unsigned short*)A, D, mode, f16 ? 0 : 1,
                                                         ctx->tc_status);
     LOGOS_LAUNCH_CHECK(ctx, "umma_selftest_kernel");
@@ -1016,10 +1019,10 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     a.n_items = a.n_qb * BH;
     dim3 grid(a.n_items < ctx->sm_count ? a.n_items : ctx->sm_count);   // persistent: one CTA per SM
     if (a.diffuse) {
-        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<true>, kSmemBytes)) return rc;
         prefill_tc_kernel<true><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
     } else {
-        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<false>, kSmemBytes)) return rc;
         prefill_tc_kernel<false><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
     }
     LOGOS_LAUNCH_CHECK(ctx, "prefill_tc_kernel");

@@ -400,8 +400,8 @@ int attention_window(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q,
     const bool f16 = a.in_is_f16, diff = a.diffuse != 0;
 #define LOGOS_LAUNCH_WIN(F, D)                                                                              \
     do {                                                                                                    \
-        LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(shunyam_window_kernel<F, D>,                               \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kWSmem));     \
+        const int rc__ = ensure_smem_limit(ctx, shunyam_window_kernel<F, D>, kWSmem);                       \
+        if (rc__ != LOGOS_OK) return rc__;                                                                  \
         shunyam_window_kernel<F, D><<<grid, kWThreads, kWSmem, ctx->stream>>>(a);                           \
     } while (0)
     if (f16 && diff) LOGOS_LAUNCH_WIN(true, true);

@@ -22,11 +22,47 @@ struct logos_ctx {
     float* absmax_scratch = nullptr;  // per-tensor absmax words for kv_quantize
     int absmax_slots = 0;
     int* tc_status = nullptr;         // device word raised by a kernel whose bounded wait ran out
-    bool force_general = false;       // LOGOS_ATTN_FORCE_GENERAL=1: never use the tensor-core prefill kernel
+    bool force_general = false;       // LOGOS_OPT_FORCE_GENERAL: never use the tensor-core kernels
+    int decode_chunk = 0;             // LOGOS_OPT_DECODE_CHUNK: 0 = chosen from the problem size
+    int peer_wait_ms = 2000;          // LOGOS_OPT_PEER_WAIT_MS
+    bool workspace_locked = false;    // LOGOS_OPT_WORKSPACE_LOCK
+    const void* smem_set[48] = {};    // kernels whose dynamic shared-memory limit this context has raised
+    int smem_set_n = 0;
     char err[512] = {0};
 };
 
+// Heads spread over several GPUs: where a finished decode row goes.  Every rank owns one block of
+// device memory that its peers can write (logos_comm); a row is stored into the staging slot of
+// EVERY rank, and when all rows of this rank are out the rank raises its flag in every block.
+constexpr int kMaxPeers = 8;
+struct PeerEpilogue {
+    float* stage[kMaxPeers];      // staging area of each rank: two slots of slot_floats floats (step parity)
+    unsigned* flag[kMaxPeers];    // in rank r's block: the word THIS rank sets to step + 1
+    const unsigned* step;         // this rank's step counter (advanced by the wait kernel)
+    unsigned* done;               // rows of this launch already stored; zero between launches
+    size_t slot_floats;
+    int world;                    // 0: no peers, rows go to DecodeArgs::out
+    int H_total, head0;           // heads of the whole model, first head of this rank
+};
+
+struct logos_comm {
+    logos_ctx* ctx = nullptr;
+    int rank = 0, world = 1;
+    size_t slot_bytes = 0;                 // bytes of one gathered tensor, rounded up to 256
+    unsigned char* block = nullptr;        // this rank's block (cudaMalloc)
+    unsigned char* peer[kMaxPeers] = {};   // every rank's block as seen from this device (peer[rank] == block)
+    bool opened[kMaxPeers] = {};           // mapped with cudaIpcOpenMemHandle (to be closed)
+    bool connected = false;
+};
+
 namespace logos {
+
+// layout of a logos_comm block
+constexpr size_t kCommFlagStride = 128;    // one flag word per source rank, a cache line apart
+constexpr size_t kCommStepOff = 1024;      // step counter, then the two completion counters
+constexpr size_t kCommDoneOff = 1028;
+constexpr size_t kCommCopyDoneOff = 1032;
+constexpr size_t kCommStageOff = 4096;
 
 inline int fail(logos_ctx* ctx, int status, const char* fmt, ...) {
     if (ctx) {
@@ -53,6 +89,20 @@ inline int fail(logos_ctx* ctx, int status, const char* fmt, ...) {
             return ::logos::fail((ctx), LOGOS_ERR_CUDA, "launch of %s failed: %s", what,  \
                                  cudaGetErrorString(e__));                                \
     } while (0)
+
+// Raises a kernel's dynamic shared-memory limit once per context (not before every launch: the
+// attribute call costs more than a short kernel).  `bytes` must be the most the kernel is ever given.
+template <typename Fn>
+inline int ensure_smem_limit(logos_ctx* ctx, Fn* kernel, int bytes) {
+    const void* key = reinterpret_cast<const void*>(kernel);
+    for (int i = 0; i < ctx->smem_set_n; ++i)
+        if (ctx->smem_set[i] == key) return LOGOS_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess)
+        return fail(ctx, LOGOS_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", bytes, cudaGetErrorString(e));
+    if (ctx->smem_set_n < 48) ctx->smem_set[ctx->smem_set_n++] = key;
+    return LOGOS_OK;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -109,7 +159,7 @@ int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const
               const float*, const int32_t*, int, int, int, int);
 int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
                 const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
-                float*);
+                float*, const PeerEpilogue* peer = nullptr);
 size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
@@ -121,4 +171,7 @@ int umma_selftest(logos_ctx*, int mode, int dtype, const void* A, const void* B,
 bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
 int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
                  void* O, int B, int H, int S, int DH, const logos_attn_params*);
+void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out);
+int comm_wait(logos_ctx*, logos_comm*, void* gathered, size_t bytes);
+int comm_push(logos_ctx*, logos_comm*, const void* local, int B, int H_local, size_t row_bytes);
 }  // namespace logos

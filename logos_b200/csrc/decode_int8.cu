@@ -55,7 +55,42 @@ struct DecodeArgs {
     int H, S_max, chunk;
     float scale, eta, nu, alpha;
     int diffuse_mode, window, stride;
+    PeerEpilogue peer;     // world == 0: rows go to `out`
 };
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// The finished row of pair bh (thread d < 64 holds channel d); called by every thread of the CTA.
+// Without peers the row goes to `out`.  With peers it goes into the current staging slot of every
+// rank at this rank's head offset, with plain stores over NVLink; the CTA that stores the rank's last
+// row of the launch then raises this rank's flag in every block (release at system scope, after
+// fences that order all rows before it).  Nobody waits here: the receiving side has its own kernel.
+__device__ __forceinline__ void emit_row(const DecodeArgs& a, int bh, int tid, float value, int n_pairs) {
+    if (a.peer.world == 0) {
+        if (tid < kDH) a.out[(int64_t)bh * kDH + tid] = value;
+        return;
+    }
+    const unsigned step = *a.peer.step;
+    const int b = bh / a.H, h = bh - b * a.H;
+    const size_t idx = (size_t)(step & 1u) * a.peer.slot_floats +
+                       ((size_t)b * a.peer.H_total + a.peer.head0 + h) * kDH + tid;
+    if (tid < kDH) {
+        for (int r = 0; r < a.peer.world; ++r) a.peer.stage[r][idx] = value;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence_system();
+        const unsigned prev = atomicAdd(a.peer.done, 1u);
+        if (prev == (unsigned)(n_pairs - 1)) {
+            *a.peer.done = 0;             // ready for the next launch
+            __threadfence_system();
+            for (int r = 0; r < a.peer.world; ++r) st_release_sys(a.peer.flag[r], step + 1u);
+        }
+    }
+}
 
 // Four int8 lanes of a 32-bit word -> four floats.  x ^ 0x80 is the value biased
 // by 128 as an unsigned byte; dropping that byte into the mantissa of 2^23 gives
@@ -235,7 +270,7 @@ __device__ __forceinline__ int signed_digit(int v, int which) {
 
 constexpr int kDenseWarps = 2;                  // warps per CTA, each with its own key range (512 keys at most)
 constexpr int kDenseThreads = kDenseWarps * 32;
-constexpr int kSubMax = kMaxChunk / kDenseWarps;  // keys per warp (256)
+constexpr int kSubMax = kMaxChunk / kDenseWarps;  // keys per warp (512)
 constexpr int kDigitPitch = kSubMax / 4 + 4;    // words per digit row (+4: no bank aliasing)
 constexpr float kQGrid = 4194303.0f;            // 2^22 - 1 levels for the largest |q| channel
 constexpr float kWGrid = 8388608.0f;            // 2^23 levels per unit weight
@@ -522,17 +557,18 @@ decode_dense_kernel(const DecodeArgs a) {
     }
 
     const float vs = a.v_scale[bh];
-    float* outp = a.out + (int64_t)bh * kDH;
+    const int n_pairs = gridDim.y;
 
     if (n_splits == 1) {
+        float r = 0.0f;
         if (tid < kDH) {
-            float r = (l_c[0] > 0.0f) ? o_c[0] / l_c[0] : 0.0f;
+            r = (l_c[0] > 0.0f) ? o_c[0] / l_c[0] : 0.0f;
             if (BLEND) {
                 float r_std = (l_c[PATHS - 1] > 0.0f) ? o_c[PATHS - 1] / l_c[PATHS - 1] : 0.0f;
                 r = (1.0f - a.alpha) * r_std + a.alpha * r;
             }
-            outp[tid] = r * vs;
         }
+        emit_row(a, bh, tid, r * vs, n_pairs);
         return;
     }
 
@@ -555,6 +591,7 @@ decode_dense_kernel(const DecodeArgs a) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    float r_out = 0.0f;
     if (tid < kDH) {
         const float* all = a.partials + (int64_t)bh * n_splits * PATHS * kPartial;
         float r_path[PATHS];
@@ -575,8 +612,9 @@ decode_dense_kernel(const DecodeArgs a) {
         }
         float r = r_path[0];
         if (BLEND) r = (1.0f - a.alpha) * r_path[PATHS - 1] + a.alpha * r_path[0];
-        outp[tid] = r * vs;
+        r_out = r * vs;
     }
+    emit_row(a, bh, tid, r_out, n_pairs);
 }
 
 // ---------------------------------------------------------------------------
@@ -599,9 +637,8 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     const int pos = len - 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row_in_warp = lane >> 2, part = lane & 3;
-    float* outp = a.out + (int64_t)bh * kDH;
     if (len == 0) {
-        if (tid < kDH) outp[tid] = 0.0f;
+        emit_row(a, bh, tid, 0.0f, gridDim.x);
         return;
     }
     // enumeration of visible keys: landmarks before the window, then the window
@@ -698,24 +735,35 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     }
     float o_ns = block_reduce_acc(acc, red_acc);
     float o_std = BLEND ? block_reduce_acc(acc2, red_acc) : 0.0f;
+    float r = 0.0f;
     if (tid < kDH) {
-        float r = (l_ns > 0.0f) ? o_ns / l_ns : 0.0f;
+        r = (l_ns > 0.0f) ? o_ns / l_ns : 0.0f;
         if (BLEND) {
             float r_std = (l_std > 0.0f) ? o_std / l_std : 0.0f;
             r = (1.0f - a.alpha) * r_std + a.alpha * r;
         }
-        outp[tid] = r * a.v_scale[bh];
+        r *= a.v_scale[bh];
     }
+    emit_row(a, bh, tid, r, gridDim.x);
 }
 
-int pick_chunk(const logos_ctx* ctx, int BH, int S_max) {
-    // Largest chunk that still gives every SM about four CTAs.  Measured at 8192 keys with 128 to 1024
-    // (sequence, head) pairs: the largest chunk is the fastest or within 3 % of it at every size (fewer
-    // partial records to merge outweighs a ragged last wave), so the chunk only shrinks for very few pairs.
+// Keys per split of the dense kernel, the one rule of both entry points: the largest chunk that
+// still gives the device kWavesWanted full waves of CTAs (a CTA is two warps, kCtasPerSm fit an SM);
+// `forced` != 0 (LOGOS_OPT_DECODE_CHUNK) overrides it.
+constexpr int kCtasPerSm = 10, kWavesWanted = 2;
+int pick_chunk(int sm_count, int forced, int64_t BH, int S_max) {
+    if (forced) return forced;
     int chunk = kMaxChunk;
-    while (chunk > 128 && (int64_t)BH * ((S_max + chunk - 1) / chunk) < (int64_t)ctx->sm_count * 4)
+    while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)sm_count * kCtasPerSm * kWavesWanted)
         chunk >>= 1;
     return chunk;
+}
+
+// The diffusion-folded weights travel as unsigned fixed-point digits, so every stencil coefficient
+// must be non-negative: nu in [0, 1].  (The reference's ns_diffuse_kernel takes any float.)
+bool dense_nu_ok(const logos_attn_params* p) {
+    const bool diffusing = p->ns_alpha > 0.0f && p->diffuse_mode != LOGOS_DIFFUSE_NONE;
+    return !diffusing || (p->ns_nu >= 0.0f && p->ns_nu <= 1.0f);
 }
 
 }  // namespace
@@ -730,8 +778,8 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH) {
 int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
                 const int8_t* v_cache, const float* k_scale, const float* v_scale,
                 const int32_t* len, int B, int H, int S_max, int DH,
-                const logos_attn_params* p, float* out) {
-    if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || !out || !p || B <= 0 ||
+                const logos_attn_params* p, float* out, const PeerEpilogue* peer) {
+    if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || (!out && !peer) || !p || B <= 0 ||
         H <= 0 || S_max <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad pointer or extent");
     if (DH != kDH) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: DH must be 64, got %d", DH);
@@ -762,6 +810,8 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
     a.diffuse_mode = ns_any ? p->diffuse_mode : LOGOS_DIFFUSE_NONE;
     a.alpha = p->ns_alpha;
     const bool blend = ns_any && p->ns_alpha < 1.0f;
+    if (peer) a.peer = *peer;
+    else a.peer.world = 0;
 
     if (p->window > 0) {
         int t_max = p->window + 1 + (p->stride > 0 ? (S_max + p->stride - 1) / p->stride : 0);
@@ -771,20 +821,23 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
         if (smem > 160 * 1024)
             return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: %d visible keys exceed the sparse kernel", t_max);
         a.partials = nullptr; a.counters = nullptr; a.chunk = 0;
-        if (blend) {
-            LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(decode_sparse_kernel<true>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            decode_sparse_kernel<true><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
-        } else {
-            LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(decode_sparse_kernel<false>,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            decode_sparse_kernel<false><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
+        // more than the default 48 KB of dynamic shared memory needs the attribute (not a hot call: a
+        // window with that many visible keys is not a decode shape of the model)
+        if (smem > 48 * 1024) {
+            if (blend) LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(decode_sparse_kernel<true>,
+                                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            else LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(decode_sparse_kernel<false>,
+                                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         }
+        if (blend) decode_sparse_kernel<true><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
+        else       decode_sparse_kernel<false><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
         LOGOS_LAUNCH_CHECK(ctx, "decode_sparse_kernel");
         return LOGOS_OK;
     }
 
-    a.chunk = pick_chunk(ctx, BH, S_max);
+    if (!dense_nu_ok(p))
+        return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: dense contexts need ns_nu in [0, 1], got %g", (double)p->ns_nu);
+    a.chunk = pick_chunk(ctx->sm_count, ctx->decode_chunk, BH, S_max);
     const int n_splits = (S_max + a.chunk - 1) / a.chunk;
     if (BH > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: B*H > 65535");
     if (n_splits > 1) {
@@ -892,8 +945,8 @@ extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const
     const bool blend = ns_any && p->ns_alpha < 1.0f;
     const int64_t BH = (int64_t)B * H;
     if (BH > kNoAllocMaxPairs) return LOGOS_ERR_SCRATCH_LIMIT;
-    int chunk = kMaxChunk;   // same rule as the context entry point: about eight CTAs per SM
-    while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)nd.sm_count * 8) chunk >>= 1;
+    if (!dense_nu_ok(p)) return LOGOS_ERR_UNSUPPORTED;
+    const int chunk = pick_chunk(nd.sm_count, 0, BH, S_max);   // the rule of the context entry point
     const int n_splits = (S_max + chunk - 1) / chunk;
     if (BH * n_splits * (blend ? 2 : 1) > kNoAllocMaxPartials) return LOGOS_ERR_SCRATCH_LIMIT;
 
@@ -908,6 +961,7 @@ extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const
     a.nu = ns_any ? p->ns_nu : 0.0f;
     a.diffuse_mode = ns_any ? p->diffuse_mode : LOGOS_DIFFUSE_NONE;
     a.alpha = p->ns_alpha;
+    a.peer.world = 0;
     a.counters = (unsigned int*)nd.scratch;
     a.partials = (float*)((char*)nd.scratch + kNoAllocCounterBytes);
     cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);

@@ -61,6 +61,14 @@ class Engine:
     def reserve(self, nbytes: int):
         self._check(self.lib.logos_ctx_reserve(self.h, int(nbytes)))
 
+    def set_workspace(self, buf: torch.Tensor):
+        """Caller-owned scratch (a uint8 tensor the caller keeps alive) instead of the context's own block:
+        what a captured CUDA graph must use, because logos_ctx_reserve may free and replace its block."""
+        self._check(self.lib.logos_ctx_set_workspace(self.h, _ptr(buf), buf.numel() * buf.element_size()))
+
+    def set_option(self, option: int, value: int):
+        self._check(self.lib.logos_ctx_set_option(self.h, int(option), int(value)))
+
     # ---- attention ---------------------------------------------------------
     def flash_attention_fwd_f32(self, Q, K, V, scale, causal=True, shunyam=False, window=0, stride=0):
         """cuda_flash_attention_fwd: one head, fp32 [seq, DH]."""
@@ -143,6 +151,13 @@ class Engine:
                                               C.byref(params), _ptr(out)))
         return out
 
+    def decode_int8_push(self, comm: "Comm", q, q_prev, k_cache, v_cache, k_scale, v_scale, lens, params: L.Params):
+        """Decode over this rank's heads; the rows go into every rank's staging slot (see Comm)."""
+        B, H, S_max, DH = k_cache.shape
+        self._check(self.lib.logos_decode_int8_push(self.h, comm.h, _ptr(q), _ptr(q_prev), _ptr(k_cache),
+                                                   _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H,
+                                                   S_max, DH, C.byref(params)))
+
     def decode_step_host(self, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, lens, params,
                          out):
         """All of q, q_prev, k_new, v_new, lens, out are HOST (ideally pinned) tensors."""
@@ -151,3 +166,51 @@ class Engine:
             self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache),
             _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
         return out
+
+
+class Comm:
+    """One rank's end of the head all-gather over peer-mapped memory (logos_comm)."""
+
+    def __init__(self, engine: Engine, rank: int, world: int, gathered_bytes: int):
+        self.eng, self.rank, self.world = engine, rank, world
+        h = C.c_void_p()
+        engine._check(engine.lib.logos_comm_create(engine.h, rank, world, int(gathered_bytes), C.byref(h)))
+        self.h = h
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(L.COMM_HANDLE_BYTES)
+        self.eng._check(self.eng.lib.logos_comm_handle(self.h, buf))
+        return buf.raw
+
+    def connect(self, handles: list[bytes]):
+        """handles[r] = rank r's handle() (one process per GPU; the entry of this rank is ignored)."""
+        blob = b"".join(handles)
+        assert len(blob) == self.world * L.COMM_HANDLE_BYTES
+        self.eng._check(self.eng.lib.logos_comm_connect(self.h, blob))
+
+    @staticmethod
+    def connect_local(comms: list["Comm"]):
+        """All ranks live in this process (several contexts, on one or on several GPUs)."""
+        arr = (C.c_void_p * len(comms))(*[c.h for c in comms])
+        rc = comms[0].eng.lib.logos_comm_connect_local(arr, len(comms))
+        comms[0].eng._check(rc)
+
+    def push(self, local: torch.Tensor):
+        """local: [B, H_local, ...] contiguous, bytes per (b, h) row a multiple of 16."""
+        B, Hl = local.shape[:2]
+        row = local[0, 0].numel() * local.element_size()
+        self.eng._check(self.eng.lib.logos_comm_push(self.eng.h, self.h, _ptr(local), B, Hl, row))
+
+    def wait(self, gathered: torch.Tensor):
+        self.eng._check(self.eng.lib.logos_comm_wait(self.eng.h, self.h, _ptr(gathered),
+                                                     gathered.numel() * gathered.element_size()))
+
+    def all_gather_heads(self, local: torch.Tensor, gathered: torch.Tensor):
+        self.push(local)
+        self.wait(gathered)
+        return gathered
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.eng.lib.logos_comm_destroy(self.h)
+            self.h = None

@@ -10,14 +10,15 @@ import os
 from functools import lru_cache
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-# LOGOS_ATTN_LIB points at another build of the same ABI (kernel experiments); default is in-tree
-LIB_PATH = os.environ.get("LOGOS_ATTN_LIB") or os.path.join(PKG, "liblogos_attn.so")
+LIB_PATH = os.path.join(PKG, "liblogos_attn.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_NO_DEVICE, ERR_ALIGNMENT = range(7)
 ERR_SCRATCH_LIMIT = 7
 ERR_KERNEL_TIMEOUT = 8
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
+OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK = 0, 1, 2, 3
+COMM_HANDLE_BYTES = 64
 
 
 class LogosError(RuntimeError):
@@ -52,6 +53,17 @@ SIGNATURES = {
     "logos_ctx_set_workspace": (_i, [_vp, _vp, _sz]),
     "logos_ctx_synchronize": (_i, [_vp]),
     "logos_last_error": (C.c_char_p, [_vp]),
+    "logos_ctx_set_option": (_i, [_vp, _i, _i]),
+    "logos_comm_create": (_i, [_vp, _i, _i, _sz, C.POINTER(_vp)]),
+    "logos_comm_handle": (_i, [_vp, _vp]),
+    "logos_comm_connect": (_i, [_vp, _vp]),
+    "logos_comm_connect_local": (_i, [C.POINTER(_vp), _i]),
+    "logos_comm_destroy": (_i, [_vp]),
+    "logos_decode_int8_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
+    "logos_decode_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
+    "logos_comm_push": (_i, [_vp, _vp, _vp, _i, _i, _sz]),
+    "logos_comm_wait": (_i, [_vp, _vp, _vp, _sz]),
+    "logos_comm_all_gather_heads": (_i, [_vp, _vp, _vp, _vp, _i, _i, _sz]),
     "logos_flash_attention_fwd_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i]),
     "logos_attention_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_prefill_fwd": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp, _vp, _vp, _vp, _i]),

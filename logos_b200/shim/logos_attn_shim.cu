@@ -8,9 +8,10 @@
 // the same C++ symbol on top of the C ABI, so a LOGOS build that leaves the original definition out
 // and links liblogos_attn_shim.so + liblogos_attn.so needs no other change.  Conventions kept:
 // the caller owns every buffer, work goes to the default stream of the current device without a
-// synchronisation, and failures surface as C++ exceptions (std::invalid_argument for arguments the
-// reference rejects, cuda/VedicGEMM.cu:1074-1079, std::runtime_error otherwise, like CUDA_CHECK,
-// cuda/VedicGEMM.cuh:111-133).
+// synchronisation, and every failure surfaces as std::runtime_error: the reference throws that type
+// both for the argument it rejects (DH > 128, cuda/VedicGEMM.cu:1074-1079) and for a failed launch
+// (cuda/VedicGEMM.cu:1094-1102, CUDA_CHECK at cuda/VedicGEMM.cuh:111-133), so a caller's
+// catch (const std::runtime_error&) keeps working.
 #include <cuda_runtime.h>
 
 #include <map>
@@ -46,7 +47,5 @@ void cuda_flash_attention_fwd(const float* Q, const float* K, const float* V, fl
     const int rc = logos_flash_attention_fwd_f32(ctx, Q, K, V, out, attn_ptr, seq, DH, scale, causal ? 1 : 0,
                                                  shunyam ? 1 : 0, window, stride);
     if (rc == LOGOS_OK) return;
-    const std::string what = std::string("cuda_flash_attention_fwd: ") + logos_last_error(ctx);
-    if (rc == LOGOS_ERR_INVALID_ARG || rc == LOGOS_ERR_UNSUPPORTED) throw std::invalid_argument(what);
-    throw std::runtime_error(what);
+    throw std::runtime_error(std::string("cuda_flash_attention_fwd: ") + logos_last_error(ctx));
 }

@@ -34,11 +34,9 @@ def engine_general():
     """A context that never takes the tensor-core prefill kernel (exact fp32 arithmetic path)."""
     import torch
     from logos_b200.engine import Engine
+    from logos_b200 import lib as L
     assert torch.cuda.is_available(), "gpu tests need a CUDA device"
-    os.environ["LOGOS_ATTN_FORCE_GENERAL"] = "1"
-    try:
-        eng = Engine(0)
-    finally:
-        del os.environ["LOGOS_ATTN_FORCE_GENERAL"]
+    eng = Engine(0)
+    eng.set_option(L.OPT_FORCE_GENERAL, 1)
     yield eng
     eng.close()
