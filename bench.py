@@ -8,10 +8,17 @@ Workload (one "step" = one decode step over the whole batch): 64 sequences, 16 h
 DH 64, 8191 cached tokens + the new token; K/V pre-quantization values ~ N(0,1) with 1 %
 outliers x8, quantized with one scale per (sequence, head, K|V) tensor; Q in FP16; the new
 token is quantized on append, then attention streams the INT8 cache.  Heads are sharded
-over the GPUs (total work fixed: strong scaling) and the outputs are all-gathered.
+over the GPUs (total work fixed: strong scaling) and every rank ends the step with the
+gathered [B][H][DH] output (the engine's peer-memory exchange; no library collective).
 
-Prints ONE JSON line.  `value` times the device-resident step with CUDA events; `e2e` is
-the same step through the host-buffer entry point with the copies inside the timed region.
+Prints ONE JSON line.  At every N the step is replayed as one CUDA graph per step; the
+`steps` loop is repeated several times and the median repeat is reported.
+  value      device-resident step, CUDA events around the loop, max over ranks
+  roofline   decode_dense_kernel alone, replayed the same way over the same rotating caches
+  e2e        the step through host buffers: copies in and out and a synchronisation per step
+  secondary  the prefill and Shunyam-window kernels, each checked against the CPU oracle on sampled rows
+  baselines  (one GPU only) the reference's CPU forward of configuration 1 and the reference's own
+             CUDA kernels timed on this GPU beside the engine's on the same inputs
 """
 from __future__ import annotations
 
@@ -30,12 +37,19 @@ if ROOT not in sys.path:
 
 B, H, S_MAX, DH = 64, 16, 8192, 64
 ETA, NU = 0.1, 0.05
-# DRAM traffic of decode_dense_kernel per (sequence, head) pair at ctx 8192, from the ncu capture
-# summarised in profiles/decode_dense_kernel_b16_ctx8192.md: 268.55 MB read + 4.20 MB written (mean of
-# two launches) over 256 pairs.  Pairs are independent, so a launch moves this times its number of pairs.
+REPEATS = 7      # the `steps` loop is timed this many times; the median is reported
+# DRAM bytes that one (sequence, head) pair of decode_dense_kernel moves at 8192 cached tokens,
+# from a hardware-counter capture of a 256-pair launch (268.55 MB read + 4.20 MB written).  Pairs are
+# independent, so a launch moves this times its number of pairs.
 DECODE_TRAFFIC_PER_PAIR = (268.55e6 + 4.20e6) / 256
 METRIC = "int8_kv_decode_attention_bandwidth_8k_ctx"
 UNIT = "GB/s"
+
+
+def workload_config(world: int) -> dict:
+    """What is computed -- the same dictionary in both arms."""
+    return {"workload": f"int8_kv_decode_b{B}_h{H}_ctx{S_MAX}_dh{DH}", "batch": B, "heads": H, "ctx": S_MAX, "dh": DH,
+            "ns_eta": ETA, "ns_nu": NU, "diffusion": "causal", "parallelism": f"heads/{world}"}
 
 
 def algorithmic_bytes(b: int, h: int, s: int, dh: int) -> int:
@@ -43,13 +57,18 @@ def algorithmic_bytes(b: int, h: int, s: int, dh: int) -> int:
     return 2 * b * h * s * dh + 2 * b * h * 4 + 2 * b * h * dh * 2 + b * h * dh * 4 + 2 * b * h * dh
 
 
-def measured_peak_gbs():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peaks() -> dict:
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+        return {"hbm": float(j["hbm_gbs"]), "tensor": float(j["bf16_tflops"]), "kind": "measured"}
     except Exception:
-        return 6650.0, "fallback"
+        return {"hbm": 6650.0, "tensor": 1590.0, "kind": "fallback"}
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
 
 
 class ClockSampler:
@@ -66,7 +85,7 @@ class ClockSampler:
     def start(self):
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "50", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
 
@@ -100,6 +119,9 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# ---------------------------------------------------------------------------------------------
+# CPU legs (test infrastructure under oracle/ is executed only here)
+
 def cpu_port_baseline(sample_pairs: int = 128) -> dict:
     """The CPU oracle's decode (same arithmetic, row-only, OpenMP over pairs) on a bounded
     sample of the workload: `sample_pairs` of the 1024 (sequence, head) pairs at full context."""
@@ -130,11 +152,46 @@ def cpu_port_baseline(sample_pairs: int = 128) -> dict:
                       "CPU oracle reading only the decode row"}
 
 
+def configuration1_cpu_baseline() -> dict:
+    """The reference's MultiHeadAttention::forward (include/Attention.hpp:290-300) at benchmark
+    configuration 1 (seq 512, d_model 1024, 16 heads, causal, Navier-Stokes on), compiled unmodified
+    with the reference's flags (-O3 -march=x86-64, CMakeLists.txt:39) and with -march=x86-64-v3, on
+    one thread (as the reference runs) and with the heads farmed over all host threads."""
+    import ctypes as C
+    import numpy as np
+    import oracle as O
+    from logos_b200 import synthetic as syn
+    seq, d, heads = 512, 1024, 16
+    dk = d // heads
+    X = syn.normal((seq, d), 1, 1)
+    W = [syn.normal(s, 1, t, std=0.02) for t, s in enumerate(
+        [(heads, d, dk), (heads, d, dk), (heads, d, dk), (heads, dk, d), (d, d)], start=2)]
+    out = np.empty((seq, d), np.float32)
+    res = {"config": "seq 512, d_model 1024, H 16, DH 64, fp32, causal, NS alpha 1 eta 0.1 nu 0.05",
+           "gflop": 2 * 512 * 1024 * 64 * 3 * 16 / 1e9 + 4 * 512 * 512 * 64 * 16 * 2 / 1e9 +
+                    2 * 512 * 64 * 1024 * 16 / 1e9 + 2 * 512 * 1024 * 1024 / 1e9, "runs": []}
+    for flags, R in (("-O3 -march=x86-64", O.ref()), ("-O3 -march=x86-64-v3", O.ref_v3())):
+        if R is None:
+            res["runs"].append({"flags": flags, "unavailable": "not built, or this host lacks the instruction set"})
+            continue
+        nthreads = max(1, min(R.ref_hardware_threads(), heads))
+        for threads in (1, nthreads):
+            cfg = O.HeadCfg(0, 8, 4, 1, 1.0, ETA, NU, 0, threads)
+            R.ref_mha_forward(X, *W, seq, d, heads, C.byref(cfg), out)       # warms the mask cache
+            t0 = time.perf_counter()
+            R.ref_mha_forward(X, *W, seq, d, heads, C.byref(cfg), out)
+            res["runs"].append({"flags": flags, "threads": threads, "ms_per_forward": (time.perf_counter() - t0) * 1e3})
+    res["nproc"] = os.cpu_count()
+    return res
+
+
 def run_reference(args) -> None:
     """The reference's own CPU attention (include/Attention.hpp, compiled unmodified) doing what
     a decode step costs in the reference today: a full re-forward of every (sequence, head)
     over its whole context (cuda/train_gpu.cu:2037-2046), heads farmed over all host threads.
-    Each step is a bounded sample: one pair per thread at the full 8192-token context."""
+    Each step is a bounded sample: one pair per thread at the full 8192-token context.  This is
+    the reference's real cost per token, not a kernel comparison: the algorithmically equal CPU
+    number is `cpu_baseline` of the other arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -142,7 +199,8 @@ def run_reference(args) -> None:
     import numpy as np
     import oracle as O
     R = O.ref()
-    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    world = args.gpus
+    base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "higher_is_better": True}
     if R is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built (reference tree absent at build time)"}))
@@ -167,17 +225,20 @@ def run_reference(args) -> None:
     dt = (time.perf_counter() - t0) / max(args.steps, 1)
     gbs = algorithmic_bytes(1, n, S_MAX, DH) / dt / 1e9
     sample = (f"{n} of {B * H} (sequence, head) pairs per step at ctx {S_MAX}, one per thread; "
-              "navier_stokes_attention over the whole context, last row is the decode output")
+              "navier_stokes_attention over the whole context (what a generated token costs the reference today), "
+              "last row is the decode output")
     base.update({"value": gbs, "ms_per_step": dt * 1e3, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                 "data": "synthetic",
-                 "config": {"workload": "int8_kv_decode_b64_h16_ctx8192_dh64", "batch": B, "heads": H,
-                            "ctx": S_MAX, "dh": DH},
+                 "data": "synthetic", "config": workload_config(world),
                  "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample},
                  "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     print(json.dumps(base))
 
 
+# ---------------------------------------------------------------------------------------------
+# the other kernels of the path
+
 PREFILL = {"name": "causal_prefill_b4_h16_s4096_dh64_bf16", "B": 4, "S": 4096, "window": 0, "outliers": False}
+PREFILL_8K = {"name": "causal_prefill_b4_h16_s8192_dh64_bf16", "B": 4, "S": 8192, "window": 0, "outliers": False}
 WINDOW = {"name": "shunyam_window64_b8_h16_s8192_dh64_bf16", "B": 8, "S": 8192, "window": 64, "stride": 0,
           "outliers": True}
 # the reference's production setting: window 64 plus every 16th key as a landmark (cuda/train_gpu.cu:1172-1173)
@@ -185,20 +246,30 @@ WINDOW_LM = {"name": "shunyam_window64_stride16_b8_h16_s8192_dh64_bf16", "B": 8,
              "stride": 16, "outliers": True}
 
 
-def measured_peak_tflops():
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            return float(json.load(f)["bf16_tflops"]), "measured burst"
-    except Exception:
-        return 1590.0, "fallback"
+def check_against_oracle(Q, K, V, out, cfg) -> float:
+    """Sampled heads and row ranges of a device result against the CPU oracle; max-abs error."""
+    import numpy as np
+    import oracle as O
+    S = cfg["S"]
+    op = O.attn_params(0.125, True, cfg["window"], cfg.get("stride", 0), ETA, NU, 1.0, O.DIFFUSE_CAUSAL)
+    worst = 0.0
+    heads = [(0, 0), (Q.shape[0] - 1, Q.shape[1] - 1)]
+    for (b, h) in heads:
+        q, k, v = (t[b, h].float().cpu().numpy() for t in (Q, K, V))
+        for (r0, r1) in [(0, 66), (250, 262), (S // 2 - 3, S // 2 + 3), (S - 8, S)]:
+            want = O.attention_rows(q, k, v, op, r0, r1)
+            got = out[b, h, r0:r1].float().cpu().numpy()
+            worst = max(worst, float(np.abs(got - want).max()))
+    return worst
 
 
-def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_over_ranks) -> dict:
+def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_over_ranks, comm=None) -> dict:
     """Device-resident prefill / window attention over this rank's heads (BF16 in, BF16 out,
-    Navier-Stokes prologue fused: eta 0.1, causal diffusion nu 0.05), outputs all-gathered."""
+    Navier-Stokes prologue fused: eta 0.1, causal diffusion nu 0.05); with several GPUs the outputs
+    are gathered through the engine's peer-memory exchange."""
     import torch
     from logos_b200 import lib as L
-    from logos_b200.sharding import all_gather_heads, head_range
+    from logos_b200.sharding import head_range
     lo, hi = head_range(H, rank, world)
     Hl, Bc, S = hi - lo, cfg["B"], cfg["S"]
     g = torch.Generator(device=dev).manual_seed(2000 + rank)
@@ -210,46 +281,111 @@ def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_ov
         sets.append(tuple(t.bfloat16() for t in (Q, K, V)))
         del Q, K, V
     O = torch.empty((Bc, Hl, S, DH), dtype=torch.bfloat16, device=dev)
+    gathered = torch.empty((Bc, H, S, DH), dtype=torch.bfloat16, device=dev) if world > 1 else None
     p = L.Params.make(1.0 / 8.0, True, cfg["window"], cfg.get("stride", 0), ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
 
     def step(i):
         Q, K, V = sets[i % 2]
         eng.attention(Q, K, V, p, out=O)
         if world > 1:
-            all_gather_heads(O, world)
+            comm.all_gather_heads(O, gathered)
 
     for i in range(warmup):
         step(i)
-    barrier()
+    times = []
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record()
-    for i in range(steps):
-        step(warmup + i)
-    ev[1].record()
-    barrier()
+    for _ in range(3):
+        barrier()
+        ev[0].record()
+        for i in range(steps):
+            step(warmup + i)
+        ev[1].record()
+        barrier()
+        times.append(ev[0].elapsed_time(ev[1]) / steps)
     eng.synchronize()
-    ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / steps)
-    out = {"workload": cfg["name"], "ms_per_step": ms, "n_gpus": world}
+    ms = max_over_ranks(median(times))
+    # correctness of what was just timed, outside the timed region: the last step's output
+    Q, K, V = sets[(warmup + steps - 1) % 2]
+    err = max_over_ranks(check_against_oracle(Q, K, V, O, cfg))
+    out = {"workload": cfg["name"], "ms_per_step": ms, "n_gpus": world, "max_abs_err_vs_oracle": err,
+           "checked": "two heads x four row ranges of the last timed step's output, tolerance 2e-3 + BF16 rounding of O"}
+    peaks = measured_peaks()
     if cfg["window"]:
         nbytes = 4 * Bc * H * S * DH * 2                       # Q, K, V read once, O written once
-        peak, kind = measured_peak_gbs()
-        out.update({"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "bound": "hbm", "peak": peak,
-                    "peak_kind": kind, "frac": nbytes / (ms * 1e-3) / 1e9 / (peak * world)})
+        out.update({"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "bound": "hbm", "peak": peaks["hbm"],
+                    "peak_kind": peaks["kind"], "frac": nbytes / (ms * 1e-3) / 1e9 / (peaks["hbm"] * world)})
     else:
         flops = 4.0 * Bc * H * S * S * DH / 2                  # causal-halved convention
-        peak, kind = measured_peak_tflops()
         out.update({"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (causal-halved)", "bound": "tensor",
-                    "peak": peak, "peak_kind": kind, "frac": flops / (ms * 1e-3) / 1e12 / (peak * world)})
+                    "peak": peaks["tensor"], "peak_kind": peaks["kind"] + " burst",
+                    "frac": flops / (ms * 1e-3) / 1e12 / (peaks["tensor"] * world)})
     return out
 
+
+def reference_gpu_kernels(eng, dev) -> list:
+    """One head of the prefill and of the window configuration through the reference's own CUDA path
+    (ns_advect_kernel + ns_diffuse_kernel + cuda_flash_attention_fwd, compiled unmodified for sm_100a)
+    and through the engine on the same fp32 inputs: the fp32 drop-in entry point (exact arithmetic,
+    no Navier-Stokes terms: the reference applies those in separate kernels) and the BF16 tensor-core path."""
+    import torch
+    import oracle as O
+    from logos_b200 import lib as L
+    G = O.refgpu()
+    if G is None:
+        return [{"unavailable": "oracle/_ref/liblogos_refgpu.so was not built"}]
+    out = []
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(n):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / n
+
+    for name, S, window, stride in (("one head of causal_prefill s4096", 4096, 0, 0),
+                                    ("one head of shunyam_window64_stride16 s8192", 8192, 64, 16)):
+        g = torch.Generator(device=dev).manual_seed(3000 + S)
+        Q, K, V = (torch.randn((S, DH), device=dev, generator=g) for _ in range(3))
+        Qa, Vs, Oref, Oours = (torch.empty_like(Q) for _ in range(4))
+        ptr = lambda t: t.data_ptr()
+
+        def ref_path():
+            G.refgpu_ns_advect(ptr(Q), ptr(Qa), S, DH, ETA)
+            G.refgpu_ns_diffuse(ptr(V), ptr(Vs), S, DH, NU)
+            G.refgpu_flash_attention_fwd(ptr(Qa), ptr(K), ptr(Vs), ptr(Oref), S, DH, 0.125, 1, int(window > 0), window, stride)
+
+        def ref_kernel_only():
+            G.refgpu_flash_attention_fwd(ptr(Qa), ptr(K), ptr(Vs), ptr(Oref), S, DH, 0.125, 1, int(window > 0), window, stride)
+
+        t_ref = timed(ref_path, 3)
+        t_ref_k = timed(ref_kernel_only, 3)
+        t_f32 = timed(lambda: eng.flash_attention_fwd_f32(Qa, K, Vs, 0.125, True, window > 0, window, stride), 5)
+        o32 = eng.flash_attention_fwd_f32(Qa, K, Vs, 0.125, True, window > 0, window, stride)
+        p = L.Params.make(0.125, True, window, stride, ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
+        Qb, Kb, Vb = (t.bfloat16()[None, None].contiguous() for t in (Q, K, V))
+        Ob = torch.empty_like(Qb)
+        t_tc = timed(lambda: eng.attention(Qb, Kb, Vb, p, out=Ob), 10)
+        eng.synchronize()
+        out.append({"case": name, "reference_ns_plus_flash_kernel_ms": t_ref, "reference_flash_kernel_ms": t_ref_k,
+                    "engine_f32_drop_in_ms": t_f32, "engine_bf16_fused_ms": t_tc,
+                    "max_abs_f32_drop_in_vs_reference_kernel": float((o32 - Oref).abs().max()),
+                    "max_abs_bf16_fused_vs_reference_path": float((Ob[0, 0].float() - Oref).abs().max())})
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
 
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
 
     from logos_b200 import lib as L
-    from logos_b200.engine import Engine
-    from logos_b200.sharding import ShardedDecoder, head_range
+    from logos_b200.engine import Comm, Engine
+    from logos_b200.sharding import ShardedDecoder, connect_comm, head_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -279,22 +415,40 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    if args.workload in ("prefill", "window", "window_lm"):
-        cfg = dict({"prefill": PREFILL, "window": WINDOW, "window_lm": WINDOW_LM}[args.workload])
+    # one exchange block per rank, large enough for the biggest gathered tensor of the run
+    comm = None
+    if world > 1:
+        biggest = B * H * DH * 4
+        if args.workload != "decode" or not args.no_secondary:
+            biggest = max(biggest, 8 * H * 8192 * DH * 2)
+        comm = Comm(eng, rank, world, biggest)
+        connect_comm(comm)
+
+    def finish():
+        torch.cuda.synchronize()
+        if comm is not None:
+            barrier()
+            comm.close()
+        eng.close()
+        if world > 1:
+            dist.destroy_process_group()
+
+    if args.workload in ("prefill", "prefill8k", "window", "window_lm"):
+        cfg = dict({"prefill": PREFILL, "prefill8k": PREFILL_8K, "window": WINDOW, "window_lm": WINDOW_LM}[args.workload])
         if args.batch != 64:   # profiling case: fewer sequences than the configuration
             cfg["B"] = args.batch
             cfg["name"] += f"_batch{args.batch}"
-        r = measure_attention(eng, dev, world, rank, cfg, args.steps, args.warmup, barrier, max_over_ranks)
+        r = measure_attention(eng, dev, world, rank, cfg, args.steps, args.warmup, barrier, max_over_ranks, comm)
         if rank == 0:
             print(json.dumps({"metric": cfg["name"], "value": r["value"], "unit": r["unit"], "n_gpus": world,
                               "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
                               "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
                               "data": "synthetic", "config": {"workload": cfg["name"]},
+                              "max_abs_err_vs_oracle": r["max_abs_err_vs_oracle"],
                               "roofline": {"bound": r["bound"], "achieved": r["value"], "peak": r["peak"],
                                            "peak_kind": r["peak_kind"], "frac": r["frac"], "traffic": None},
                               "gpu_launches": args.steps}))
-        if world > 1:
-            dist.destroy_process_group()
+        finish()
         return
 
     # ---- caches: enough independent sets that a pass never finds its bytes in L2 ----
@@ -302,6 +456,7 @@ def run_ours(args) -> None:
     n_sets = max(1, -(-(512 << 20) // per_set))
     g = torch.Generator(device=dev).manual_seed(1000 * 4 + rank)
     params = L.Params.make(1.0 / 8.0, True, 0, 0, ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
+    eng.reserve(eng.decode_workspace_bytes(B, Hl, S_MAX, DH))
     decoders = []
     for _ in range(n_sets):
         kc = torch.empty((B, Hl, S_MAX, DH), dtype=torch.int8, device=dev)
@@ -315,111 +470,131 @@ def run_ours(args) -> None:
                 _, s = eng.nikhilam_compress(x, cache=cache[b0:b0 + 8])
                 sc[b0:b0 + 8] = s
                 del x
-        decoders.append(ShardedDecoder(eng, kc, vc, ks, vs, params, rank, world))
+        decoders.append(ShardedDecoder(eng, kc, vc, ks, vs, params, rank, world, gather="peer", comm=comm))
     torch.cuda.synchronize()
 
-    def new_tokens():
-        return [torch.randn((B, Hl, DH), device=dev, generator=g).half() for _ in range(4)]
-
-    q, qp, kn, vn = new_tokens()
+    q, qp, kn, vn = (torch.randn((B, Hl, DH), device=dev, generator=g).half() for _ in range(4))
     lens = torch.full((B,), S_MAX, dtype=torch.int32, device=dev)
     hq, hqp, hkn, hvn = (t.cpu().pin_memory() for t in (q, qp, kn, vn))
     hlens = lens.cpu().pin_memory()
     hout = torch.empty((B, H, DH), dtype=torch.float32).pin_memory()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
 
-    # ---- device-resident step: `value` ----
-    for i in range(args.warmup):
-        decoders[i % n_sets].step(q, qp, kn, vn, lens)
-    barrier()
+    def timed_loop(fn) -> float:
+        """`steps` calls of fn(i) between two events, REPEATS times; the median repeat, max over ranks."""
+        for i in range(args.warmup):
+            fn(i)
+        per = []
+        for _ in range(REPEATS):
+            barrier()
+            ev[0].record()
+            for i in range(args.steps):
+                fn(args.warmup + i)
+            ev[1].record()
+            barrier()
+            per.append(ev[0].elapsed_time(ev[1]) / args.steps)
+        return max_over_ranks(median(per))
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    ev[0].record()
-    for i in range(args.steps):
-        d = decoders[(args.warmup + i) % n_sets]
-        torch.sub(lens, 1, out=d.pos)
-        eng.kv_append(kn, vn, d.kc, d.vc, d.ks, d.vs, d.pos)
-        kev[i][0].record()
-        eng.decode_int8(q, qp, d.kc, d.vc, d.ks, d.vs, lens, params, out=d.out_local)
-        kev[i][1].record()
-        if world > 1:
-            from logos_b200.sharding import all_gather_heads
-            all_gather_heads(d.out_local, world)
-    ev[1].record()
-    barrier()
-    step_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / args.steps)
-    kern_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in kev) / args.steps)
 
-    # ---- the same step replayed as one CUDA graph launch per step ----
-    # (the eager loop above stays: it carries the per-kernel events behind `roofline`)
-    graph_ms = None
-    # One GPU only for now: with two and four ranks the replayed step measured 120 / 90 us against 150 / 126 us
-    # eager, but the eight-rank run of the same code did not finish within its time limit.
-    if not args.no_graph and world == 1:
+    # ---- eager launches (reported for comparison) ----
+    eager_ms = timed_loop(lambda i: decoders[i % n_sets].step(q, qp, kn, vn, lens))
+
+    # ---- the decode kernel alone and the whole step, each as one CUDA graph per cache set ----
+    kernel_graphs = []
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        eng.use_stream(side)
+        with torch.cuda.stream(side):
+            for d in decoders:
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph, stream=side, capture_error_mode="thread_local"):
+                    eng.decode_int8(q, qp, d.kc, d.vc, d.ks, d.vs, lens, params, out=d.out_local)
+                kernel_graphs.append(gph)
+        eng.use_stream(torch.cuda.current_stream())
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
         for d in decoders:
             d.capture(q, qp, kn, vn, lens)
-        for i in range(args.warmup):
-            decoders[i % n_sets].replay()
-        barrier()
-        ev[0].record()
+            barrier()
+        kern_ms = timed_loop(lambda i: kernel_graphs[i % n_sets].replay())
+        step_ms = timed_loop(lambda i: decoders[i % n_sets].replay())
+        launch = "one CUDA graph per step"
+    else:
+        kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
         for i in range(args.steps):
-            decoders[(args.warmup + i) % n_sets].replay()
-        ev[1].record()
-        barrier()
-        graph_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / args.steps)
-    clocks = sampler.stop() if rank == 0 else None      # sampled over the eager and the replayed loop
-    eager_ms = step_ms
-    if graph_ms is not None:      # `value` is the replayed step whenever it was measured
-        step_ms = graph_ms
+            d = decoders[i % n_sets]
+            kev[i][0].record()
+            eng.decode_int8(q, qp, d.kc, d.vc, d.ks, d.vs, lens, params, out=d.out_local)
+            kev[i][1].record()
+        torch.cuda.synchronize()
+        kern_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in kev) / args.steps)
+        step_ms, launch = eager_ms, "eager"
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- host-buffer step: `e2e` ----
-    for i in range(args.warmup):
-        decoders[i % n_sets].step_host(hq, hqp, hkn, hvn, hlens, hout)
-    barrier()
-    ev[0].record()
-    for i in range(args.steps):
-        decoders[(args.warmup + i) % n_sets].step_host(hq, hqp, hkn, hvn, hlens, hout)
-    ev[1].record()
-    barrier()
-    e2e_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / args.steps)
+    if world == 1:
+        e2e_fn = lambda i: decoders[i % n_sets].step_host(hq, hqp, hkn, hvn, hlens, hout)
+        e2e_how = "logos_decode_step_int8_host: copies, append, decode, copy back, synchronise"
+    elif not args.no_graph:
+        def e2e_fn(i):
+            for dst, src in zip((q, qp, kn, vn, lens), (hq, hqp, hkn, hvn, hlens)):
+                dst.copy_(src, non_blocking=True)
+            hout.copy_(decoders[i % n_sets].replay(), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        e2e_how = "pinned-host copies in, the step's graph, copy of the gathered rows back, synchronise"
+    else:
+        e2e_fn = lambda i: decoders[i % n_sets].step_host(hq, hqp, hkn, hvn, hlens, hout)
+        e2e_how = "copies in, eager step, copy back, synchronise"
+    e2e_ms = timed_loop(e2e_fn)
 
     total_bytes = algorithmic_bytes(B, H, S_MAX, DH)
     kernel_bytes = algorithmic_bytes(B, Hl, S_MAX, DH)
-    peak, peak_kind = measured_peak_gbs()
+    peaks = measured_peaks()
     line = {
         "metric": METRIC, "value": total_bytes / (step_ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 KV, fp16 Q, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"int8_kv_decode_b{B}_h16_ctx8192_dh64", "batch": B, "heads": H, "ctx": S_MAX, "dh": DH,
-                   "ns_eta": ETA, "ns_nu": NU, "diffusion": "causal", "parallelism": f"heads/{world}",
-                   "launch": ("one CUDA graph per step" if graph_ms is not None else "eager"),
-                   "ms_per_step_eager": eager_ms, "ms_per_step_graph": graph_ms,
+        "config": workload_config(world),
+        "timing": {"launch": launch, "repeats": REPEATS, "statistic": "median over repeats of the mean step, max over ranks",
+                   "ms_per_step_eager": eager_ms, "ms_per_step_graph": step_ms if launch != "eager" else None,
+                   "gather": "peer-memory stores from the decode kernel + wait/copy kernel" if world > 1 else "none",
                    "l2": (f"inputs larger than L2: {per_set >> 20} MiB of cache per GPU per pass, "
                           f"{n_sets} cache set(s) visited in rotation")},
         "e2e": {"value": total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": 4 * B * Hl * DH * 2 + B * 4, "d2h_bytes_per_step": B * H * DH * 4,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": 2 * args.steps,
+                "ms_per_step": e2e_ms, "how": e2e_how},
+        "gpu_launches": (2 if world == 1 else 3) * args.steps * REPEATS,
         "roofline": {"bound": "hbm", "kernel": "decode_dense_kernel",
-                     "achieved": kernel_bytes / (kern_ms * 1e-3) / 1e9, "peak": peak, "peak_kind": peak_kind,
-                     "unit": "GB/s", "frac": kernel_bytes / (kern_ms * 1e-3) / 1e9 / peak,
-                     "kernel_ms": kern_ms, "traffic": DECODE_TRAFFIC_PER_PAIR * B * Hl},
+                     "achieved": kernel_bytes / (kern_ms * 1e-3) / 1e9, "peak": peaks["hbm"], "peak_kind": peaks["kind"],
+                     "unit": "GB/s", "frac": kernel_bytes / (kern_ms * 1e-3) / 1e9 / peaks["hbm"],
+                     "kernel_ms": kern_ms, "traffic": DECODE_TRAFFIC_PER_PAIR * B * Hl,
+                     "how": "the kernel alone, replayed as a graph over the same rotating caches, same loop and statistic as value"},
         "clocks": clocks,
     }
+    for d in decoders:
+        d.release()
+    for gph in kernel_graphs:
+        gph.reset()
+    kernel_graphs.clear()
     if not args.no_secondary:
-        # the other two kernels of the path, device-resident, a few steps each
-        del decoders
+        # the other kernels of the path, device-resident, a few steps each
+        decoders.clear()
         torch.cuda.empty_cache()
         line["secondary"] = [measure_attention(eng, dev, world, rank, cfg, max(3, args.steps // 4), 3, barrier,
-                                               max_over_ranks) for cfg in (PREFILL, WINDOW, WINDOW_LM)]
+                                               max_over_ranks, comm)
+                             for cfg in (PREFILL, PREFILL_8K, WINDOW, WINDOW_LM)]
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["baselines"] = {"reference_gpu_kernels_on_this_gpu": reference_gpu_kernels(eng, dev),
+                             "configuration_1_reference_cpu_forward": configuration1_cpu_baseline()}
+        line["cpu_baseline"] = cpu_port_baseline()
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_port_baseline()
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    decoders.clear()
+    finish()
 
 
 def main() -> None:
@@ -428,11 +603,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU legs and the reference's GPU kernels")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
-    ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay of the decode step")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "window", "window_lm"],
-                    help="decode is the benchmark; prefill / window time the other kernels alone (profiling)")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm"],
+                    help="decode is the benchmark; the others time one attention kernel alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")
     args = ap.parse_args()

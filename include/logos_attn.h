@@ -193,6 +193,16 @@ int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const i
                       const logos_attn_params* params, float* out);
 size_t logos_decode_workspace_bytes(int B, int H, int S_max, int DH);
 
+/* One whole decode step on device buffers: the new token's K and V rows (FP16 [B][H][DH]) are
+ * quantised into row len[b]-1 of the caches (logos_kv_append with pos = len - 1), then
+ * logos_decode_int8 runs over rows [0, len[b]).  len is the length AFTER the append.  Two
+ * launches, nothing else; this is the per-layer body of an incremental generate loop, which the
+ * reference does not have (cuda/train_gpu.cu:2037-2046 re-runs the whole forward per token). */
+int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new,
+                           const void* v_new, int8_t* k_cache, int8_t* v_cache, const float* k_scale,
+                           const float* v_scale, const int32_t* len, int B, int H, int S_max, int DH,
+                           const logos_attn_params* params, float* out);
+
 /* One whole decode step with HOST buffers for the per-step data: copies q, q_prev,
  * k_new, v_new (FP16 [B][H][DH]) and len (int32 [B], the length AFTER the append)
  * to the device, appends at row len[b]-1, runs logos_decode_int8 and copies the
@@ -220,7 +230,12 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
  * LOGOS_ERR_SCRATCH_LIMIT, window > 0 returns LOGOS_ERR_UNSUPPORTED.  The call makes no
  * cudaMalloc / cudaFree and uses no allocating library routine.  The first call on a
  * device looks up the array's device address; make that first call before any stream
- * capture.  All calls share the one array and it keeps the previous call's contents
+ * capture.  That first call is also where the CUDA runtime may load this library's
+ * device code into the device (kernel images and the array itself, if nothing of the
+ * library ran there before): the runtime takes device memory for it at that moment,
+ * and fails if none is left.  A caller whose pool will own the whole device therefore
+ * makes one warm-up call at start-up, before the pool takes the device; from the
+ * second call on no device memory moves.  All calls share the one array and it keeps the previous call's contents
  * (the call clears the counters it needs on its stream), so calls that overlap on a
  * GPU -- two streams, two threads -- race: issue them on one stream, one at a time. */
 int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_prev,
@@ -266,6 +281,13 @@ int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, co
                              const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                              const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
                              const logos_attn_params* params, float* gathered);
+/* logos_decode_step_int8 over this rank's heads with the gathered result on every rank: append,
+ * decode with the peer epilogue, wait-and-copy (three launches). */
+int logos_decode_step_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                                  const void* k_new, const void* v_new, int8_t* k_cache, int8_t* v_cache,
+                                  const float* k_scale, const float* v_scale, const int32_t* len, int B,
+                                  int H_local, int S_max, int DH, const logos_attn_params* params,
+                                  float* gathered);
 /* The same exchange for any per-head tensor this rank has already computed (the prefill output):
  * local is [B][H_local][row_bytes], gathered [B][H_local * world][row_bytes]; row_bytes a multiple of 16. */
 int logos_comm_push(logos_ctx* ctx, logos_comm* comm, const void* local, int B, int H_local, size_t row_bytes);

@@ -286,6 +286,30 @@ int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const i
     return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
 }
 
+int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new, const void* v_new,
+                           int8_t* k_cache, int8_t* v_cache, const float* k_scale, const float* v_scale,
+                           const int32_t* len, int B, int H, int S_max, int DH, const logos_attn_params* params,
+                           float* out) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step: bad parameter block");
+    int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, -1);
+    if (rc != LOGOS_OK) return rc;
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
+}
+
+int logos_decode_step_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
+                                  const void* k_new, const void* v_new, int8_t* k_cache, int8_t* v_cache,
+                                  const float* k_scale, const float* v_scale, const int32_t* len, int B,
+                                  int H_local, int S_max, int DH, const logos_attn_params* params, float* gathered) {
+    if (!ctx || !comm) return LOGOS_ERR_INVALID_ARG;
+    int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max,
+                              DH, -1);
+    if (rc != LOGOS_OK) return rc;
+    return logos_decode_int8_gather(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max,
+                                    DH, params, gathered);
+}
+
 int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
                            const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                            const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
@@ -336,8 +360,7 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
         if (len_host[b] < 1 || len_host[b] > S_max)
             return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: len[%d]=%d outside [1,%d]", b,
                                len_host[b], S_max);
-    // staging layout behind the kernel workspace: q | q_prev | k_new | v_new (fp16), out (fp32),
-    // len | pos (int32)
+    // staging layout behind the kernel workspace: q | q_prev | k_new | v_new (fp16), out (fp32), len (int32)
     char* base = (char*)ctx->workspace + ((kernel_ws + 255) & ~(size_t)255);
     __half* d_q = (__half*)base;
     __half* d_qp = d_q + vec;
@@ -345,18 +368,14 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
     __half* d_v = d_k + vec;
     float* d_out = (float*)(d_v + vec);
     int32_t* d_len = (int32_t*)(d_out + vec);
-    int32_t* d_pos = d_len + B;
     cudaStream_t st = ctx->stream;
     const size_t hb = vec * sizeof(__half);
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_q, q_host, hb, cudaMemcpyHostToDevice, st));
     if (q_prev_host) LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_qp, q_prev_host, hb, cudaMemcpyHostToDevice, st));
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_k, k_new_host, hb, cudaMemcpyHostToDevice, st));
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_v, v_new_host, hb, cudaMemcpyHostToDevice, st));
-    // len and pos = len - 1 travel as one small copy
-    int32_t small[2 * 4096];
-    for (int b = 0; b < B; ++b) { small[b] = len_host[b]; small[B + b] = len_host[b] - 1; }
-    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_len, small, sizeof(int32_t) * 2 * B, cudaMemcpyHostToDevice, st));
-    int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_pos, B, H, S_max, DH);
+    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_len, len_host, sizeof(int32_t) * B, cudaMemcpyHostToDevice, st));
+    int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_len, B, H, S_max, DH, -1);
     if (rc != LOGOS_OK) return rc;
     rc = logos::decode_int8(ctx, d_q, q_prev_host ? d_qp : nullptr, k_cache, v_cache, k_scale, v_scale, d_len, B,
                             H, S_max, DH, params, d_out);

@@ -155,8 +155,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 namespace logos {
 int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*, int, int64_t);
 int kv_dequantize(logos_ctx*, const int8_t*, int64_t, const float*, float*, int64_t, int, int64_t);
+// pos_bias is added to every pos[b]: -1 appends at len - 1 when `pos` is the length after the append
 int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const float*,
-              const float*, const int32_t*, int, int, int, int);
+              const float*, const int32_t* pos, int, int, int, int, int pos_bias = 0);
 int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
                 const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
                 float*, const PeerEpilogue* peer = nullptr);

@@ -151,10 +151,10 @@ template <typename T>
 __global__ void append_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new,
                               int8_t* __restrict__ k_cache, int8_t* __restrict__ v_cache,
                               const float* __restrict__ k_scale, const float* __restrict__ v_scale,
-                              const int32_t* __restrict__ pos, int H, int S_max, int DH) {
+                              const int32_t* __restrict__ pos, int pos_bias, int H, int S_max, int DH) {
     int bh = blockIdx.x;
     int b = bh / H;
-    int row = pos[b];
+    int row = pos[b] + pos_bias;
     if (row < 0 || row >= S_max) return;  // out-of-range rows are rejected, not written
     int d = threadIdx.x;
     if (d >= DH) return;
@@ -245,7 +245,7 @@ int kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const f
 
 int kv_append(logos_ctx* ctx, int dtype, const void* k_new, const void* v_new, int8_t* k_cache,
               int8_t* v_cache, const float* k_scale, const float* v_scale, const int32_t* pos,
-              int B, int H, int S_max, int DH) {
+              int B, int H, int S_max, int DH, int pos_bias) {
     if (!k_new || !v_new || !k_cache || !v_cache || !k_scale || !v_scale || !pos || B <= 0 ||
         H <= 0 || S_max <= 0 || DH <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_append: bad pointer or extent");
@@ -255,18 +255,18 @@ int kv_append(logos_ctx* ctx, int dtype, const void* k_new, const void* v_new, i
     switch (dtype) {
         case LOGOS_F32:
             append_kernel<float><<<grid, threads, 0, ctx->stream>>>(
-                (const float*)k_new, (const float*)v_new, k_cache, v_cache, k_scale, v_scale, pos,
+                (const float*)k_new, (const float*)v_new, k_cache, v_cache, k_scale, v_scale, pos, pos_bias,
                 H, S_max, DH);
             break;
         case LOGOS_BF16:
             append_kernel<__nv_bfloat16><<<grid, threads, 0, ctx->stream>>>(
                 (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, k_cache, v_cache,
-                k_scale, v_scale, pos, H, S_max, DH);
+                k_scale, v_scale, pos, pos_bias, H, S_max, DH);
             break;
         case LOGOS_F16:
             append_kernel<__half><<<grid, threads, 0, ctx->stream>>>(
                 (const __half*)k_new, (const __half*)v_new, k_cache, v_cache, k_scale, v_scale,
-                pos, H, S_max, DH);
+                pos, pos_bias, H, S_max, DH);
             break;
         default:
             return fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_append: unknown dtype %d", dtype);

@@ -151,6 +151,25 @@ class Engine:
                                               C.byref(params), _ptr(out)))
         return out
 
+    def decode_step(self, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, lens, params: L.Params,
+                    out=None, comm: "Comm | None" = None):
+        """Append the new token at row lens-1 and decode, device tensors throughout.  With `comm` the
+        heads are this rank's share and `out` is the gathered [B, H_local * world, DH] tensor."""
+        B, H, S_max, DH = k_cache.shape
+        if comm is None:
+            if out is None:
+                out = torch.empty((B, H, DH), dtype=torch.float32, device=q.device)
+            self._check(self.lib.logos_decode_step_int8(
+                self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale),
+                _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
+        else:
+            if out is None:
+                out = torch.empty((B, H * comm.world, DH), dtype=torch.float32, device=q.device)
+            self._check(self.lib.logos_decode_step_int8_gather(
+                self.h, comm.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache),
+                _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
+        return out
+
     def decode_int8_push(self, comm: "Comm", q, q_prev, k_cache, v_cache, k_scale, v_scale, lens, params: L.Params):
         """Decode over this rank's heads; the rows go into every rank's staging slot (see Comm)."""
         B, H, S_max, DH = k_cache.shape

@@ -61,6 +61,9 @@ SIGNATURES = {
     "logos_comm_destroy": (_i, [_vp]),
     "logos_decode_int8_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_decode_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
+    "logos_decode_step_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
+    "logos_decode_step_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                          _PP, _vp]),
     "logos_comm_push": (_i, [_vp, _vp, _vp, _i, _i, _sz]),
     "logos_comm_wait": (_i, [_vp, _vp, _vp, _sz]),
     "logos_comm_all_gather_heads": (_i, [_vp, _vp, _vp, _vp, _i, _i, _sz]),

@@ -99,7 +99,6 @@ class ShardedDecoder:
         engine.reserve(engine.decode_workspace_bytes(B, Hl, S_max, DH))
         dev = k_cache.device
         self.out_local = torch.empty((B, Hl, DH), dtype=torch.float32, device=dev)
-        self.pos = torch.empty((B,), dtype=torch.int32, device=dev)
         self.graph = None
         self.comm, self._own_comm = comm, False
         if self.gather == "peer":
@@ -118,13 +117,12 @@ class ShardedDecoder:
     # ---- one step ---------------------------------------------------------------------
     def _local_step(self, q, q_prev, k_new, v_new, lens):
         """Append and decode on this rank; with the peer exchange the rows leave from the kernel."""
-        torch.sub(lens, 1, out=self.pos)
-        self.eng.kv_append(k_new, v_new, self.kc, self.vc, self.ks, self.vs, self.pos)
         if self.gather == "peer":
-            self.eng.decode_int8_push(self.comm, q, q_prev, self.kc, self.vc, self.ks, self.vs, lens, self.params)
-            self.comm.wait(self.gathered)
+            self.eng.decode_step(q, q_prev, k_new, v_new, self.kc, self.vc, self.ks, self.vs, lens, self.params,
+                                 out=self.gathered, comm=self.comm)
         else:
-            self.eng.decode_int8(q, q_prev, self.kc, self.vc, self.ks, self.vs, lens, self.params, out=self.out_local)
+            self.eng.decode_step(q, q_prev, k_new, v_new, self.kc, self.vc, self.ks, self.vs, lens, self.params,
+                                 out=self.out_local)
 
     def _finish(self):
         if self.gather == "peer":

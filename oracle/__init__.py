@@ -88,9 +88,29 @@ def lib() -> C.CDLL:
     return L
 
 
+def _cpu_has_avx2_fma() -> bool:
+    try:
+        with open("/proc/cpuinfo") as f:
+            flags = next((ln for ln in f if ln.startswith("flags")), "")
+        return " avx2" in flags and " fma" in flags and " bmi2" in flags
+    except OSError:
+        return False
+
+
+@lru_cache(maxsize=None)
+def ref_v3():
+    """The reference CPU headers built for x86-64-v3, or None (not built / this CPU lacks AVX2+FMA)."""
+    if not _cpu_has_avx2_fma():
+        return None
+    return _load_ref(os.path.join(HERE, "_ref", "liblogos_ref_v3.so"))
+
+
 @lru_cache(maxsize=None)
 def ref():
-    path = os.path.join(HERE, "_ref", "liblogos_ref.so")
+    return _load_ref(os.path.join(HERE, "_ref", "liblogos_ref.so"))
+
+
+def _load_ref(path):
     if not os.path.exists(path):
         return None
     L = C.CDLL(path)

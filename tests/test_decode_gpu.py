@@ -198,3 +198,33 @@ def test_decode_step_replayed_as_cuda_graph(engine):
         assert got.data_ptr() != want.data_ptr() and out is dec.graph_out
         assert torch.equal(got, want), f"round {rnd}"
         assert torch.equal(dec.kc, ref.kc) and torch.equal(dec.vc, ref.vc)
+
+
+def test_dense_decode_rejects_viscosity_outside_unit_interval(engine):
+    """The dense kernel carries the diffusion-folded weights as unsigned digits, which only holds for
+    nu in [0, 1]; anything else is refused instead of being clipped silently."""
+    dev = lambda a: torch.from_numpy(a).cuda()
+    B, H, S = 1, 1, 64
+    kq, vq, ks, vs = make_cache(B, H, S, [S], 31)
+    q = dev(syn.normal((B, H, 64), 31, 3).astype(np.float16))
+    engine.reserve(engine.decode_workspace_bytes(B, H, S, 64))
+    for nu in (-0.1, 1.5):
+        p = L.Params.make(0.125, True, 0, 0, 0.1, nu, 1.0, L.DIFFUSE_CAUSAL)
+        with pytest.raises(L.LogosError) as err:
+            engine.decode_int8(q, q, dev(kq), dev(vq), dev(ks), dev(vs), dev(np.array([S], np.int32)), p)
+        assert err.value.status == L.ERR_UNSUPPORTED
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 1.5, 0.0, L.DIFFUSE_CAUSAL)    # alpha 0: diffusion is off, nu is unused
+    engine.decode_int8(q, q, dev(kq), dev(vq), dev(ks), dev(vs), dev(np.array([S], np.int32)), p)
+    engine.synchronize()
+
+
+@pytest.mark.parametrize("chunk", [128, 256, 512, 1024])
+def test_every_split_size_against_the_oracle(engine, chunk):
+    p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    engine.set_option(L.OPT_DECODE_CHUNK, chunk)
+    try:
+        run_case(engine, 2, 3, 2048, [2048, 777], p, seed=32)
+    finally:
+        engine.set_option(L.OPT_DECODE_CHUNK, 0)
+    with pytest.raises(L.LogosError):
+        engine.set_option(L.OPT_DECODE_CHUNK, 300)

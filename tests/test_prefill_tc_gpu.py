@@ -126,3 +126,26 @@ def test_many_ragged_items_per_cta(engine, engine_general, case):
     for (b, h) in [(0, 0), (1, 17), (2, 39)]:
         q, k, v = (t[b, h].float().cpu().numpy() for t in (Q, K, V))
         assert_close(got[b, h].cpu().numpy(), O.attention_rows(q, k, v, op), f"case={case} head {(b, h)} vs oracle")
+
+
+@pytest.mark.parametrize("stride", [0, 16])
+def test_window_configuration_full_size_sampled(engine, stride):
+    """Shunyam window attention at the benchmark's own size (B=8, H=16, S=8192, window 64, 1 % of the K
+    entries x8), with the reference's landmark stride 16 (cuda/train_gpu.cu:1172-1173) and without:
+    sampled heads and row ranges against the oracle -- the first block, rows around the window length,
+    block boundaries of both kernels' tilings, and the last rows (about 508 landmarks per row there)."""
+    B, H, S, W = 8, 16, 8192, 64
+    g = torch.Generator(device="cuda").manual_seed(62 + stride)
+    Q, K, V = (torch.randn((B, H, S, 64), device="cuda", generator=g) for _ in range(3))
+    K[torch.rand(K.shape, device="cuda", generator=g) < 0.01] *= 8
+    Q, K, V = Q.bfloat16(), K.bfloat16(), V.bfloat16()
+    p = L.Params.make(0.125, True, W, stride, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    out = engine.attention(Q, K, V, p, out_dtype=torch.float32)
+    engine.synchronize()
+    assert bool(torch.isfinite(out).all())
+    op = O.attn_params(0.125, True, W, stride, 0.1, 0.05, 1.0, O.DIFFUSE_CAUSAL)
+    for (b, h) in [(0, 0), (5, 9), (7, 15)]:
+        q, k, v = (t[b, h].float().cpu().numpy() for t in (Q, K, V))
+        for (r0, r1) in [(0, 140), (250, 262), (1020, 1030), (4090, 4102), (8120, 8192)]:
+            want = O.attention_rows(q, k, v, op, r0, r1)
+            assert_close(out[b, h, r0:r1].cpu().numpy(), want, f"stride {stride} head {(b, h)} rows {r0}:{r1}")
