@@ -251,7 +251,7 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
  * rank's end of that exchange: a block of device memory that the other ranks map and write with
  * ordinary peer stores (no TMA, no multicast), two staging slots of `gathered_bytes` each plus flags.
  *   set-up, once:  logos_comm_create on every rank; then either
- *                    logos_comm_handle -> exchange the 64-byte handles by any means -> logos_comm_connect
+ *                    logos_comm_handle -> exchange the 80-byte handles by any means -> logos_comm_connect
  *                    (one process per GPU: the blocks are shared through CUDA IPC), or
  *                    logos_comm_connect_local (all ranks are contexts of one process).
  *   per step:      a producing call (logos_decode_int8_push, logos_comm_push) stores this rank's rows
@@ -262,7 +262,7 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
  * The step counter is device memory, so a CUDA graph that holds a step replays unchanged.  Nothing here
  * allocates after logos_comm_create; destroy the comm after its last kernel has finished. */
 typedef struct logos_comm logos_comm;
-#define LOGOS_COMM_HANDLE_BYTES 64
+#define LOGOS_COMM_HANDLE_BYTES 80
 int logos_comm_create(logos_ctx* ctx, int rank, int world, size_t gathered_bytes, logos_comm** out);
 int logos_comm_handle(logos_comm* comm, void* handle_out /* LOGOS_COMM_HANDLE_BYTES */);
 int logos_comm_connect(logos_comm* comm, const void* handles /* world x LOGOS_COMM_HANDLE_BYTES, rank order */);

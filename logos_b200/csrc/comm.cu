@@ -18,6 +18,8 @@
 // No TMA, no multicast, no multimem: loads are local, stores are ordinary peer stores.
 // The only wait is in gather_wait_kernel and it is bounded by wall time (LOGOS_OPT_PEER_WAIT_MS);
 // when it runs out the kernel raises the context's status word and returns.
+#include <cuda.h>
+
 #include <cstring>
 #include <new>
 
@@ -102,14 +104,13 @@ push_kernel(const PushArgs a) {
         const uint4 v = a.local[i];
         for (int r = 0; r < a.peer.world; ++r) reinterpret_cast<uint4*>(a.peer.stage[r])[o] = v;
     }
-    __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
+    if (threadIdx.x == 0) {      // one fence per CTA: the barrier orders all threads' stores before it
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
         const unsigned prev = atomicAdd(a.peer.done, 1u);
         if (prev == gridDim.x - 1) {
             *a.peer.done = 0;
-            __threadfence_system();
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
             for (int r = 0; r < a.peer.world; ++r)
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer.flag[r]), "r"(step + 1u) : "memory");
         }
@@ -207,12 +208,30 @@ int logos_comm_create(logos_ctx* ctx, int rank, int world, size_t gathered_bytes
     return LOGOS_OK;
 }
 
+// What a rank sends to its peers: the CUDA IPC handle of the allocation that holds its block, the
+// block's offset inside that allocation (an IPC mapping always starts at the allocation's base, and
+// the driver may place a small cudaMalloc inside a larger one), and a word that the block carries at
+// a known place, so that the peer can check it mapped the right memory.
+struct CommHandle {
+    cudaIpcMemHandle_t ipc;
+    unsigned long long offset;
+    unsigned long long magic;
+};
+static_assert(sizeof(CommHandle) == LOGOS_COMM_HANDLE_BYTES, "handle size");
+
 int logos_comm_handle(logos_comm* c, void* handle_out) {
     if (!c || !handle_out) return LOGOS_ERR_INVALID_ARG;
-    static_assert(sizeof(cudaIpcMemHandle_t) == LOGOS_COMM_HANDLE_BYTES, "IPC handle size");
-    cudaIpcMemHandle_t h;
+    CommHandle h;
+    memset(&h, 0, sizeof(h));
     LOGOS_CUDA_TRY(c->ctx, cudaSetDevice(c->ctx->device));
-    LOGOS_CUDA_TRY(c->ctx, cudaIpcGetMemHandle(&h, c->block));
+    LOGOS_CUDA_TRY(c->ctx, cudaIpcGetMemHandle(&h.ipc, c->block));
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (cuMemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(c->block)) != CUDA_SUCCESS)
+        return logos::fail(c->ctx, LOGOS_ERR_CUDA, "comm_handle: cuMemGetAddressRange failed");
+    h.offset = reinterpret_cast<CUdeviceptr>(c->block) - base;
+    h.magic = 0x4c4f474f53000000ull ^ (reinterpret_cast<unsigned long long>(c->block) * 0x9e3779b97f4a7c15ull) ^ (unsigned)c->rank;
+    LOGOS_CUDA_TRY(c->ctx, cudaMemcpy(c->block + logos::kCommMagicOff, &h.magic, sizeof(h.magic), cudaMemcpyHostToDevice));
     memcpy(handle_out, &h, sizeof(h));
     return LOGOS_OK;
 }
@@ -223,12 +242,16 @@ int logos_comm_connect(logos_comm* c, const void* handles) {
     LOGOS_CUDA_TRY(c->ctx, cudaSetDevice(c->ctx->device));
     for (int r = 0; r < c->world; ++r) {
         if (r == c->rank) continue;
-        cudaIpcMemHandle_t h;
+        CommHandle h;
         memcpy(&h, static_cast<const unsigned char*>(handles) + (size_t)r * sizeof(h), sizeof(h));
         void* p = nullptr;
-        LOGOS_CUDA_TRY(c->ctx, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-        c->peer[r] = static_cast<unsigned char*>(p);
-        c->opened[r] = true;
+        LOGOS_CUDA_TRY(c->ctx, cudaIpcOpenMemHandle(&p, h.ipc, cudaIpcMemLazyEnablePeerAccess));
+        c->ipc_base[r] = p;
+        c->peer[r] = static_cast<unsigned char*>(p) + h.offset;
+        unsigned long long seen = 0;
+        LOGOS_CUDA_TRY(c->ctx, cudaMemcpy(&seen, c->peer[r] + logos::kCommMagicOff, sizeof(seen), cudaMemcpyDeviceToHost));
+        if (seen != h.magic)
+            return logos::fail(c->ctx, LOGOS_ERR_CUDA, "comm_connect: the mapping of rank %d's block does not show its mark", r);
     }
     c->connected = true;
     return LOGOS_OK;
@@ -266,7 +289,7 @@ int logos_comm_destroy(logos_comm* c) {
     cudaSetDevice(c->ctx->device);
     cudaStreamSynchronize(c->ctx->stream);
     for (int r = 0; r < c->world; ++r)
-        if (c->opened[r] && c->peer[r]) cudaIpcCloseMemHandle(c->peer[r]);
+        if (c->ipc_base[r]) cudaIpcCloseMemHandle(c->ipc_base[r]);
     if (c->block) cudaFree(c->block);
     delete c;
     return LOGOS_OK;

@@ -51,7 +51,7 @@ struct logos_comm {
     size_t slot_bytes = 0;                 // bytes of one gathered tensor, rounded up to 256
     unsigned char* block = nullptr;        // this rank's block (cudaMalloc)
     unsigned char* peer[kMaxPeers] = {};   // every rank's block as seen from this device (peer[rank] == block)
-    bool opened[kMaxPeers] = {};           // mapped with cudaIpcOpenMemHandle (to be closed)
+    void* ipc_base[kMaxPeers] = {};        // what cudaIpcOpenMemHandle returned for a peer (to be closed)
     bool connected = false;
 };
 
@@ -62,6 +62,7 @@ constexpr size_t kCommFlagStride = 128;    // one flag word per source rank, a c
 constexpr size_t kCommStepOff = 1024;      // step counter, then the two completion counters
 constexpr size_t kCommDoneOff = 1028;
 constexpr size_t kCommCopyDoneOff = 1032;
+constexpr size_t kCommMagicOff = 1040;     // 8-byte mark written at hand-out, checked by peers after mapping
 constexpr size_t kCommStageOff = 4096;
 
 inline int fail(logos_ctx* ctx, int status, const char* fmt, ...) {

@@ -58,6 +58,7 @@ struct DecodeArgs {
     PeerEpilogue peer;     // world == 0: rows go to `out`
 };
 
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -76,17 +77,18 @@ __device__ __forceinline__ void emit_row(const DecodeArgs& a, int bh, int tid, f
     const int b = bh / a.H, h = bh - b * a.H;
     const size_t idx = (size_t)(step & 1u) * a.peer.slot_floats +
                        ((size_t)b * a.peer.H_total + a.peer.head0 + h) * kDH + tid;
-    if (tid < kDH) {
+    if (tid < kDH)
         for (int r = 0; r < a.peer.world; ++r) a.peer.stage[r][idx] = value;
-        __threadfence_system();
-    }
     __syncthreads();
+    // One fence for the CTA: the barrier above orders every thread's stores before thread 0's fence,
+    // and a release is cumulative over what was ordered before it.  (A system-scope fence waits for
+    // the peers' acknowledgements, microseconds over NVLink: one per row, not one per thread.)
     if (tid == 0) {
-        __threadfence_system();
+        fence_acq_rel_sys();
         const unsigned prev = atomicAdd(a.peer.done, 1u);
         if (prev == (unsigned)(n_pairs - 1)) {
             *a.peer.done = 0;             // ready for the next launch
-            __threadfence_system();
+            fence_acq_rel_sys();
             for (int r = 0; r < a.peer.world; ++r) st_release_sys(a.peer.flag[r], step + 1u);
         }
     }
@@ -748,14 +750,15 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
 }
 
 // Keys per split of the dense kernel, the one rule of both entry points: the largest chunk that
-// still gives the device kWavesWanted full waves of CTAs (a CTA is two warps, kCtasPerSm fit an SM);
-// `forced` != 0 (LOGOS_OPT_DECODE_CHUNK) overrides it.
-constexpr int kCtasPerSm = 10, kWavesWanted = 2;
+// still gives every SM about four CTAs.  Measured at 8192 keys with 128 to 1024 (sequence, head)
+// pairs, the largest chunk is the fastest or within 3 % of it at every size (33 / 62 / 99 / 187 us
+// against 42 / 72 / 131 / 245 us with 256-key chunks): a warp's fixed cost -- query digits, softmax,
+// partial record, merge -- outweighs a ragged last wave, so the chunk only shrinks for very few
+// pairs.  `forced` != 0 (LOGOS_OPT_DECODE_CHUNK) overrides the rule.
 int pick_chunk(int sm_count, int forced, int64_t BH, int S_max) {
     if (forced) return forced;
     int chunk = kMaxChunk;
-    while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)sm_count * kCtasPerSm * kWavesWanted)
-        chunk >>= 1;
+    while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)sm_count * 4) chunk >>= 1;
     return chunk;
 }
 

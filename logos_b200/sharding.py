@@ -72,7 +72,7 @@ def all_gather_heads(local: torch.Tensor, world: int, group=None, flat: torch.Te
 
 
 def connect_comm(comm, group=None) -> None:
-    """Exchange the ranks' 64-byte block handles over the process group and map the peers' blocks."""
+    """Exchange the ranks' block handles over the process group and map the peers' blocks."""
     handles = [None] * comm.world
     dist.all_gather_object(handles, comm.handle(), group=group)
     comm.connect(handles)

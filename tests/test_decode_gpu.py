@@ -195,9 +195,15 @@ def test_decode_step_replayed_as_cuda_graph(engine):
         got = dec.replay().clone()
         want = ref.step(q, qp, kn, vn, lens).clone()
         torch.cuda.synchronize()
-        assert got.data_ptr() != want.data_ptr() and out is dec.graph_out
+        assert got.data_ptr() != want.data_ptr() and out is dec.out_local
         assert torch.equal(got, want), f"round {rnd}"
         assert torch.equal(dec.kc, ref.kc) and torch.equal(dec.vc, ref.vc)
+    # while a captured graph is alive the workspace it points into cannot be replaced
+    with pytest.raises(L.LogosError) as err:
+        engine.reserve(engine.decode_workspace_bytes(64, 16, 8192, DH) * 4)
+    assert err.value.status == L.ERR_WORKSPACE
+    dec.release()
+    ref.release()
 
 
 def test_dense_decode_rejects_viscosity_outside_unit_interval(engine):
