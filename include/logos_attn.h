@@ -249,16 +249,21 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
  * the only exchange is the all-gather of the per-head outputs along the head axis.  The reference has
  * no counterpart (its head loop is serial on one GPU, cuda/ModelGPU.cu:892-988).  A logos_comm is one
  * rank's end of that exchange: a block of device memory that the other ranks map and write with
- * ordinary peer stores (no TMA, no multicast), two staging slots of `gathered_bytes` each plus flags.
+ * ordinary peer stores (no TMA, no multicast): two staging slots of `gathered_bytes` each, a row area for
+ * decode outputs (8 bytes per value, at most 2 MiB per slot, i.e. B * H * DH <= 262144 values) and flags.
  *   set-up, once:  logos_comm_create on every rank; then either
  *                    logos_comm_handle -> exchange the 80-byte handles by any means -> logos_comm_connect
  *                    (one process per GPU: the blocks are shared through CUDA IPC), or
  *                    logos_comm_connect_local (all ranks are contexts of one process).
- *   per step:      a producing call (logos_decode_int8_push, logos_comm_push) stores this rank's rows
- *                  into every rank's staging slot and raises this rank's flag; logos_comm_wait queues a
- *                  kernel that waits for all ranks' flags of the step -- at most LOGOS_OPT_PEER_WAIT_MS,
- *                  then logos_ctx_synchronize reports LOGOS_ERR_KERNEL_TIMEOUT -- and copies the slot to
- *                  `gathered`.  Exactly one producing call per wait, in the same order on every rank.
+ *   per step:      a producing call stores this rank's rows into every rank's block, then a collecting
+ *                  call queues a kernel that waits until all ranks' rows of the step have arrived -- at
+ *                  most LOGOS_OPT_PEER_WAIT_MS, then logos_ctx_synchronize reports
+ *                  LOGOS_ERR_KERNEL_TIMEOUT -- and writes them to `gathered`.  Two pairs exist:
+ *                    logos_decode_int8_push / logos_decode_int8_collect   decode rows (small): every value
+ *                        travels as an 8-byte word that carries its own arrival mark, no fence or flag;
+ *                    logos_comm_push / logos_comm_wait                    any per-head tensor (large): plain
+ *                        copies, then one flag per rank.
+ *                  Exactly one producing call per collecting call, in the same order on every rank.
  * The step counter is device memory, so a CUDA graph that holds a step replays unchanged.  Nothing here
  * allocates after logos_comm_create; destroy the comm after its last kernel has finished. */
 typedef struct logos_comm logos_comm;
@@ -276,7 +281,9 @@ int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, cons
                            const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                            const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
                            const logos_attn_params* params);
-/* logos_decode_int8_push followed by logos_comm_wait into `gathered` (float [B][H_local * world][DH]). */
+/* The collecting half: waits for every rank's rows of the step and writes float [B][H_total][DH]. */
+int logos_decode_int8_collect(logos_ctx* ctx, logos_comm* comm, float* gathered, int B, int H_total, int DH);
+/* logos_decode_int8_push followed by logos_decode_int8_collect into `gathered` (float [B][H_local * world][DH]). */
 int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
                              const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                              const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,

@@ -319,9 +319,9 @@ int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, cons
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: comm is not connected or belongs to another context");
     if (!params_ok(params))
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: bad parameter block");
-    if (B <= 0 || H_local <= 0 || DH <= 0 || (size_t)B * H_local * comm->world * DH * sizeof(float) > comm->slot_bytes)
-        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: gathered output exceeds the comm's slot of %zu bytes",
-                           comm->slot_bytes);
+    if (B <= 0 || H_local <= 0 || DH <= 0 || (size_t)B * H_local * comm->world * DH * 8 > comm->row_slot_bytes)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: gathered output exceeds the comm's row area (%zu bytes per slot, 8 per value)",
+                           comm->row_slot_bytes);
     PeerEpilogue pe;
     logos::comm_peer_epilogue(comm, H_local, &pe);
     return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
@@ -335,7 +335,12 @@ int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, co
     const int rc = logos_decode_int8_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local,
                                           S_max, DH, params);
     if (rc != LOGOS_OK) return rc;
-    return logos::comm_wait(ctx, comm, gathered, (size_t)B * H_local * comm->world * DH * sizeof(float));
+    return logos::comm_collect_rows(ctx, comm, gathered, B, H_local * comm->world, DH);
+}
+
+int logos_decode_int8_collect(logos_ctx* ctx, logos_comm* comm, float* gathered, int B, int H_total, int DH) {
+    if (!ctx || !comm) return LOGOS_ERR_INVALID_ARG;
+    return logos::comm_collect_rows(ctx, comm, gathered, B, H_total, DH);
 }
 
 int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* q_prev_host,

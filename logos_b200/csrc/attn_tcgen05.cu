@@ -14,25 +14,24 @@
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
 // A work item = 256 query rows of one head as two 128-row tiles that share every K/V tile.  The CTA
-// (640 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
+// (384 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
 // rings run on across items, so one item's epilogue overlaps the other tile's work and the next
-// item's loads.  Roles:
-//   warps 0-7 / 8-15  softmax of tile 0 / tile 1.  A query row (= TMEM lane) is shared by two
-//              threads in different warps, each owning 64 of the tile's 128 score columns: they
-//              read S with tcgen05.ld (twice: once for the maximum, once for the weights, instead
-//              of holding 64 scores in registers), trade the half-row maximum and the stencil's
-//              boundary scores through shared memory, write FP16 weights back to tensor memory
-//              with tcgen05.st and finally O / l to global memory;
-//   warp 16    TMA producers: lane 0 loads Q, Q_prev per item (two buffers) and the K tiles, lane 1 the
+// item's loads.  Roles, one warpgroup each so that registers can be moved between them (setmaxnreg):
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1, one thread per query row (= TMEM lane) with the
+//              row's 128 scores in registers: one tcgen05.ld of the row, then the S columns are
+//              handed back at once (the next QK^T runs under this tile's exponentials); maximum,
+//              weights and the diffusion stencil stay inside the thread; FP16 weights go back to
+//              tensor memory with tcgen05.st, and finally O / l to global memory;
+//   warp 8     TMA producers: lane 0 loads Q, Q_prev per item (two buffers) and the K tiles, lane 1 the
 //              V tiles; K and V have separate two-stage rings (a K stage is free as soon as its scores
 //              are done).  This warp also initialises the barriers, so its first loads leave before
 //              the CTA's set-up (TMEM allocation, first CTA-wide barrier) has finished;
-//   warps 17,18  MMA issuers, one per query tile: S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}) from
+//   warps 9,10  MMA issuers, one per query tile: S_g = Q_adv,g K^T (M128 N128 K16 x 4 x {hi,lo}) from
 //              shared-memory descriptors, O_g += W_g V (M128 N64 K16 x 8) with W read from tensor
 //              memory; completion via tcgen05.commit; the scores of the next tile are issued before
 //              the current tile's weights are waited for.  The whole warp runs the loop, one elected
 //              lane issues;
-//   warp 19    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
+//   warp 11    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
 //              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond).
 // TMEM (512 columns): S of tile 0 / 1 at [0,128) / [128,256), O at [256,320) / [320,384), FP16
 // weights (two keys per column) at [384,448) / [448,512).
@@ -54,13 +53,20 @@ constexpr int kBN = 128;              // keys per tile
 constexpr int kD = 64;                // head dimension
 constexpr int kTileBytes = kBM * kD * 2;      // 16 KiB: one 128 x 64 16-bit tile
 constexpr int kStages = 2;              // depth of the K ring and of the V ring (3 and 4 measured no faster)
-constexpr int kHalf = 64;             // score columns per softmax thread (two threads per row)
-constexpr int kSoftmaxWarps = 8 * kTiles;
+constexpr int kSoftmaxWarps = 4 * kTiles;   // one warpgroup per query tile, one thread per row
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr int kTmaWarp = kSoftmaxWarps;          // then one MMA warp per query tile (the first also owns TMEM)
 constexpr int kMmaWarp = kTmaWarp + 1;
 constexpr int kCvtWarp = kMmaWarp + kTiles;      // V converter warp
 constexpr int kTcThreads = 32 * (kCvtWarp + 1);
+static_assert(kTcThreads == 384 && kTmaWarp % 4 == 0, "three warpgroups: two of softmax threads, one of helpers");
+// registers per thread after the warpgroups have traded them (the kernel starts with 65536 / 384 = 168):
+// 256 softmax threads x 224 + 128 helper threads x 56 = 64512
+#ifndef LOGOS_TC_REGS_SOFTMAX
+#define LOGOS_TC_REGS_SOFTMAX 224
+#define LOGOS_TC_REGS_HELPER 56
+#endif
+constexpr int kRegsSoftmax = LOGOS_TC_REGS_SOFTMAX, kRegsHelper = LOGOS_TC_REGS_HELPER;
 constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 256 * kTiles;
 constexpr uint32_t kColO = 128 * kTiles, kColP = kColO + 64 * kTiles;   // S first, then O, then the weights
@@ -71,9 +77,8 @@ constexpr int kOffQ = 0;                                       // two buffers (w
 constexpr int kQBufBytes = 2 * kTiles * kTileBytes;
 constexpr int kOffK = kOffQ + 2 * kQBufBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffXch = kOffV + kStages * kTileBytes;          // row-pair exchange: [3][tiles][128] float4 (two step slots, one for the epilogue)
-constexpr int kOffBar = kOffXch + 3 * kTiles * kBM * 16;
-constexpr int kNumBars = 8 + 5 * kStages + 8 + 8;
+constexpr int kOffBar = kOffV + kStages * kTileBytes;
+constexpr int kNumBars = 8 + 5 * kStages + 8;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
 enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buffer
@@ -82,7 +87,8 @@ enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buf
            B_KFULL0 = 8, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
            B_VEMPTY0 = B_VFULL0 + kStages, B_VREADY0 = B_VEMPTY0 + kStages,
            B_SFULL0 = B_VREADY0 + kStages, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
-           B_PAIR0 /* eight: one per warp pair */, B_NUM = B_PAIR0 + 8 };
+           B_NUM };
+static_assert(B_NUM <= kNumBars, "barrier count");
 
 struct TcArgs {
     void* O;
@@ -305,11 +311,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
         for (int g = 0; g < kTiles; ++g) {
             mbar_init(bar(B_SFULL0 + g), 1);
-            mbar_init(bar(B_SEMPTY0 + g), 256);
-            mbar_init(bar(B_PFULL0 + g), 256);
+            mbar_init(bar(B_SEMPTY0 + g), kBM);
+            mbar_init(bar(B_PFULL0 + g), kBM);
             mbar_init(bar(B_PVDONE0 + g), 1);
         }
-        for (int p = 0; p < 4 * kTiles; ++p) mbar_init(bar(B_PAIR0 + p), 64);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -343,6 +348,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     const uint32_t tmem = *tmem_slot;
     // columns per query tile: S 128 (from column 0), O 64 (from kColO), FP16 weights 64 (from kColP, two keys per column)
 
+    // Registers move from the helper warpgroup to the two softmax warpgroups (a row of 128 scores lives
+    // in registers there).  Each setmaxnreg stands at the head of the branch it governs, so that the
+    // register budget of all code below it is unambiguous.
+    if (warp >= kTmaWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsHelper));
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
@@ -509,23 +519,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 __syncwarp();
             }
         }
+    }
     } else {
-        // ================= softmax warps: two threads per query row =================
-        // warp w: query tile g = w / 8, column half = (w / 4) % 2, TMEM lane quarter = w % 4.
-        // The two threads of a row sit in different warps; they trade the half-row maximum, the
-        // boundary scores of the diffusion stencil and finally the half-row sums through shared
-        // memory, synchronised by a 64-thread mbarrier of their warp pair (a bounded wait).
-        const int g = warp >> 3;
-        const int half = (warp >> 2) & 1;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+        // ================= softmax warpgroups: one thread per query row =================
+        // warp w: query tile g = w / 4, TMEM lane quarter = w % 4 (the lanes a warp may touch).
+        const int g = warp >> 2;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;         // row in tile = TMEM lane
         const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
-        const uint32_t tmem_S = tmem + (uint32_t)g * 128u + (uint32_t)half * 64u + lane_addr;
-        const uint32_t tmem_O = tmem + kColO + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
-        const uint32_t tmem_P = tmem + kColP + (uint32_t)g * 64u + (uint32_t)half * 32u + lane_addr;
-        const uint32_t pair_bar = bar(B_PAIR0 + g * 4 + quarter);
-        float* xch = reinterpret_cast<float*>(smem + kOffXch);   // [parity][g][row][4]: max0, max1, score col 0, score col 64
-        int pair_phase = 0;
+        const uint32_t tmem_S = tmem + (uint32_t)g * 128u + lane_addr;
+        const uint32_t tmem_O = tmem + kColO + (uint32_t)g * 64u + lane_addr;
+        const uint32_t tmem_P = tmem + kColP + (uint32_t)g * 64u + lane_addr;
         int s_run = 0;               // score tiles of this query tile taken so far, over all items
         bool ok = true;
         const float c = a.c;
@@ -539,13 +544,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const int qsel = it_of & 1;
             const int i_glob = q0 + g * kBM + r;
             const bool fine = mbar_wait(bar(B_QLOAD0 + qsel), (it_of >> 1) & 1, abort_flag);
-            // Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (4 chunks per thread)
+            // Q_adv = Q + eta (Q - Q_prev) as an exact hi + lo pair, in place (the row's 8 chunks)
             if (fine && has_lo && (g == 0 || tile1_live)) {
                 unsigned char* qh = smem + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes + r * 128;
                 unsigned char* ql = qh + kTileBytes;
-#pragma unroll
-                for (int cq = 0; cq < 4; ++cq) {
-                    const int cidx = half * 4 + cq;
+#pragma unroll 2
+                for (int cidx = 0; cidx < 8; ++cidx) {
                     const int pc = (cidx ^ (r & 7)) * 16;
                     uint4 cur = *reinterpret_cast<uint4*>(qh + pc);
                     uint4 prv = *reinterpret_cast<uint4*>(ql + pc);
@@ -591,87 +595,74 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         set_item(t);
         const int i_glob = q0 + g * kBM + r;
 
-        float m_run = -INFINITY;     // running reference maximum (log2 domain), same in both threads of a row
-        float l_run = 0.0f;          // running sum of this thread's weights
-        float s_carry = -INFINITY;   // half 1: scaled score of the first key of the tile above
+        float m_run = -INFINITY;     // running reference maximum (log2 domain)
+        float l_run = 0.0f;          // running sum of the row's weights
+        float s_carry = -INFINITY;   // scaled score of the first key of the tile above (for the stencil)
         int k_last = -1;
 
         for (int i = 0; ok && i < n_iter; ++i) {
             if (!active(g, i)) continue;
-            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN, kh = k0 + half * kHalf;
+            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN;
             k_last = k;
             if (!mbar_wait(bar(B_SFULL0 + g), s_run & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            // pass 1 over this thread's 64 score columns: maximum of the raw scores (c > 0); the scores
-            // are read again from TMEM in pass 2 instead of being held in 64 registers
+            // the whole row of scores into registers, then the S columns go back to the issuer at once:
+            // the next tile's QK^T runs while this tile's weights are computed
+            float s[kBN];
+            tc_ld32(tmem_S, s);
+            tc_ld32(tmem_S + 32, s + 32);
+            tc_ld32(tmem_S + 64, s + 64);
+            tc_ld32(tmem_S + 96, s + 96);
+            tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(B_SEMPTY0 + g));
+
             const int r_first = q0 + g * kBM;
             const bool edge = (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
                               (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
-            // visible columns of this thread's 64, relative to its first column: [lo_rel, hi_rel];
-            // the column offsets below are compile-time constants, so a masked element costs two
-            // compares against these bounds and a select
-            const int hi_rel = min(i_glob, S - 1) - kh;
-            const int lo_rel = (a.window > 0) ? i_glob - a.window - kh : -(1 << 30);
-            auto mask32 = [&](float (&v)[32], int off) {   // columns off .. off + 31
+            if (edge) {
+                // visible columns of the row, relative to the tile's first key: [lo_rel, hi_rel]
+                const int hi_rel = min(i_glob, S - 1) - k0;
+                const int lo_rel = (a.window > 0) ? i_glob - a.window - k0 : -(1 << 30);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = (off + j <= hi_rel && off + j >= lo_rel) ? v[j] : -INFINITY;
-            };
-            auto mask16 = [&](float (&v)[16], int off) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = (off + j <= hi_rel && off + j >= lo_rel) ? v[j] : -INFINITY;
-            };
-            float mxh, s_first;
+                for (int j = 0; j < kBN; ++j) s[j] = (j <= hi_rel && j >= lo_rel) ? s[j] : -INFINITY;
+            }
+            float mxr;
             {
-                float v0[32], v1[32];                 // both loads in flight before the first use
-                tc_ld32(tmem_S, v0);
-                tc_ld32(tmem_S + 32, v1);
-                tc_wait_ld();
-                if (edge) {
-                    mask32(v0, 0);
-                    mask32(v1, 32);
-                }
-                float m0 = fmaxf(v0[0], v0[1]), m1 = fmaxf(v1[0], v1[1]);
+                float m0 = fmaxf(s[0], s[1]), m1 = fmaxf(s[2], s[3]), m2 = fmaxf(s[4], s[5]), m3 = fmaxf(s[6], s[7]);
 #pragma unroll
-                for (int j = 2; j < 32; j += 2) {     // three-input maxima, two chains
-                    m0 = fmaxf(fmaxf(m0, v0[j]), v0[j + 1]);
-                    m1 = fmaxf(fmaxf(m1, v1[j]), v1[j + 1]);
+                for (int j = 8; j < kBN; j += 8) {     // three-input maxima, four chains
+                    m0 = fmaxf(fmaxf(m0, s[j]), s[j + 1]);
+                    m1 = fmaxf(fmaxf(m1, s[j + 2]), s[j + 3]);
+                    m2 = fmaxf(fmaxf(m2, s[j + 4]), s[j + 5]);
+                    m3 = fmaxf(fmaxf(m3, s[j + 6]), s[j + 7]);
                 }
-                mxh = fmaxf(m0, m1);
-                s_first = v0[0];
+                mxr = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
-            // trade with the other half of the row
-            float* x = xch + (((s_run & 1) * kTiles + g) * kBM + r) * 4;
-            x[half] = mxh * c;
-            x[2 + half] = s_first * c;
-            mbar_arrive(pair_bar);
-            if (!mbar_wait(pair_bar, pair_phase & 1, abort_flag)) { ok = false; break; }
-            ++pair_phase;
-            const float mx = fmaxf(x[0], x[1]);
-            float s_above;                    // scaled score of the key right above this thread's columns
-            if (half == 0) {
-                s_above = x[3];               // column 64 of this tile
-            } else {
-                s_above = s_carry;            // column 0 of the tile above
-                s_carry = x[2];
-            }
+            const float mx = mxr * c;                 // c > 0
+            const float s_first = s[0] * c;           // the tile below needs it for its last column's stencil
             // move the reference maximum only when it would grow by more than the threshold (weights
             // stay below 2^9, well inside FP16); the decision is warp-wide because the O correction is
-            // a warp-collective TMEM access, and identical in both warps of a pair (same rows, same data)
+            // a warp-collective TMEM access
             const bool want = (mx > m_run + kRescaleThreshold) || (m_run == -INFINITY && mx > -INFINITY);
             const bool any = __any_sync(0xffffffffu, want && k > 0 && m_run > -INFINITY);
             float m_new = want ? mx : m_run;
             if (any && m_new < mx) m_new = mx;       // correcting anyway: take the exact maximum
-            // before touching O or the weight buffer the previous O += W V must be complete
-            if (k > 0 && !mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) { ok = false; break; }
+            bool pv_done = (k == 0);                 // has the previous O += W V of this tile been waited for?
             if (any) {
+                if (!mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) { ok = false; break; }
+                pv_done = true;
                 tc_fence_after();
                 const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
-                float o[32];
-                tc_ld32(tmem_O, o);
-                tc_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[j] *= f;
-                tc_st32(tmem_O, o);
+                for (int hc = 0; hc < 2; ++hc) {
+                    float o[32];
+                    tc_ld32(tmem_O + 32 * hc, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= f;
+                    tc_st32(tmem_O + 32 * hc, o);
+                }
                 tc_wait_st();
                 tc_fence_before();
                 l_run *= f;
@@ -685,39 +676,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             // Arithmetic runs on packed pairs (key k, key k + 8) of a 16-key chunk so that the
             // neighbour pair of the stencil is again a register pair.  The row sum is taken before
             // the FP16 rounding: the two differ by at most 2^-12 relative, far inside the tolerance.
-            float nxt = DIFF ? ex2(s_above + neg_m) : 0.0f;             // -inf gives 0
+            float nxt = DIFF ? ex2(s_carry + neg_m) : 0.0f;             // -inf gives 0
+            s_carry = s_first;
             const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m), rho2 = make_float2(rho, rho);
             float2 lsum2 = make_float2(0.0f, 0.0f), lsum2b = make_float2(0.0f, 0.0f);
-            // stage A of a 16-column chunk: p = 2^(c s - m) as pairs (key j, key j + 8)
-            auto expo16 = [&](float (&v)[16], int cb, float2 (&P)[9]) {
-                if (edge) mask16(v, 16 * cb);
+            // chunks of 16 keys, highest first (the stencil walks downwards)
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float2 t = __ffma2_rn(make_float2(v[2 * e], v[2 * e + 1]), c2, nm2);
-                    const float p0 = ex2(t.x), p1 = ex2(t.y);          // keys 2e, 2e+1 of the chunk
+            for (int cb = kBN / 16 - 1; cb >= 0; --cb) {
+                float2 P[9];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {          // p = 2^(c s - m) as pairs (key j, key j + 8)
+                    const float2 tt = __ffma2_rn(make_float2(s[16 * cb + 2 * e], s[16 * cb + 2 * e + 1]), c2, nm2);
+                    const float p0 = ex2(tt.x), p1 = ex2(tt.y);          // keys 2e, 2e+1 of the chunk
                     if (2 * e < 8) { P[2 * e].x = p0; P[2 * e + 1].x = p1; }
                     else { P[2 * e - 8].y = p0; P[2 * e - 7].y = p1; }
                 }
-            };
-            // stage B: stencil, row sum, FP16 pack, store to the weight columns
-            auto store16 = [&](float2 (&P)[9], int cb) {
                 float2 W[8];
                 if (DIFF) {
                     P[8] = make_float2(P[0].y, nxt);                   // keys 8 and 16 (= first key of the chunk above)
                     nxt = P[0].x;
 #pragma unroll
                     for (int q = 0; q < 8; ++q) W[q] = __ffma2_rn(rho2, P[q + 1], P[q]);
-                    if (cb == 0 && kh == 0) W[0].x = fmaf(rho, P[0].x, W[0].x);   // V_s[0] = V[0]
+                    if (cb == 0 && k0 == 0) W[0].x = fmaf(rho, P[0].x, W[0].x);   // V_s[0] = V[0]
                 } else {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) W[q] = P[q];
                 }
-                uint32_t pk[8];
 #pragma unroll
                 for (int q = 0; q < 8; q += 2) {
                     lsum2 = __fadd2_rn(lsum2, W[q]);
                     lsum2b = __fadd2_rn(lsum2b, W[q + 1]);
                 }
+                uint32_t pk[8];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {                          // word e: keys 2e, 2e+1; word 4+e: keys 8+2e, 9+2e
                     __half2 h_lo = __floats2half2_rn(W[2 * e].x, W[2 * e + 1].x);
@@ -725,33 +715,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     pk[e] = *reinterpret_cast<uint32_t*>(&h_lo);
                     pk[4 + e] = *reinterpret_cast<uint32_t*>(&h_hi);
                 }
+                if (cb == kBN / 16 - 1 && !pv_done) {
+                    // the weight columns are still being read by the previous O += W V until it is done
+                    if (!mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) ok = false;
+                    tc_fence_after();
+                }
                 tc_st8(tmem_P + 8 * cb, pk);
-            };
-            // pass 2, highest columns first (the stencil walks downwards).  The exponentials of a chunk
-            // are issued ahead of the previous chunk's stencil / pack / store, and the chunk after it
-            // is already in flight from TMEM.
-            {
-                float va[16], vb[16];
-                float2 Pa[9], Pb[9];
-                tc_ld16(tmem_S + 48, va);
-                tc_wait_ld();
-                tc_ld16(tmem_S + 32, vb);
-                expo16(va, 3, Pa);
-                tc_wait_ld();
-                tc_ld16(tmem_S + 16, va);
-                expo16(vb, 2, Pb);
-                store16(Pa, 3);
-                tc_wait_ld();
-                tc_ld16(tmem_S, vb);
-                expo16(va, 1, Pa);
-                store16(Pb, 2);
-                tc_wait_ld();
-                tc_fence_before();                    // the scores have left TMEM: the next S may be written
-                mbar_arrive(bar(B_SEMPTY0 + g));
-                expo16(vb, 0, Pb);
-                store16(Pa, 1);
-                store16(Pb, 0);
             }
+            if (!ok) break;
             lsum2 = __fadd2_rn(lsum2, lsum2b);
             l_run += lsum2.x + lsum2.y;
             tc_wait_st();
@@ -760,7 +731,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             ++s_run;
         }
 
-        // ---- the next item's Q, then this item's epilogue: O / l, 32 channels per thread ----
+        // ---- the next item's Q, then this item's epilogue: O / l, the row's 64 channels ----
         {
             const int t_next = item_at(it + 1);
             if (ok && t_next < a.n_items) {
@@ -770,38 +741,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             }
         }
         if (ok && k_last >= 0) {
-            float* x = xch + ((2 * kTiles + g) * kBM + r) * 4;      // the epilogue's own slot
-            x[half] = l_run;
-            mbar_arrive(pair_bar);
-            ok = mbar_wait(pair_bar, pair_phase & 1, abort_flag);
-            ++pair_phase;
-            const float l_row = x[0] + x[1];
-            if (ok && mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) {
+            if (mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) {
                 tc_fence_after();
-                float o[32];
-                tc_ld32(tmem_O, o);
-                tc_wait_ld();
-                tc_fence_before();
-                if (i_glob < S) {
-                    const float inv = (l_row > 1e-9f) ? 1.0f / l_row : 0.0f;   // cuda/VedicGEMM.cu:1049
-                    const size_t row = ((size_t)bh * S + i_glob) * kD + half * 32;
-                    if (a.out_is_f32) {
-                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
+                const float inv = (l_run > 1e-9f) ? 1.0f / l_run : 0.0f;   // cuda/VedicGEMM.cu:1049
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
+                for (int hc = 0; hc < 2; ++hc) {
+                    float o[32];
+                    tc_ld32(tmem_O + 32 * hc, o);
+                    tc_wait_ld();
+                    if (i_glob < S) {
+                        const size_t row = ((size_t)bh * S + i_glob) * kD + hc * 32;
+                        if (a.out_is_f32) {
+                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t w[4];
+                            for (int j = 0; j < 8; ++j)
+                                dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
-                            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int j = 0; j < 4; ++j) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
+                                dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
                         }
                     }
                 }
+                tc_fence_before();
+            } else {
+                ok = false;
             }
         }
         }   // next work item

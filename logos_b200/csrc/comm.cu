@@ -7,17 +7,21 @@
 // exchange is done by the kernels themselves over peer-mapped memory:
 //   * every rank owns one block of device memory (logos_comm) that all peers map -- in the same
 //     process directly, across processes through a CUDA IPC handle;
-//   * the producing kernel (the decode kernel's epilogue, or push_kernel below for any other tensor)
-//     stores its rows into the staging slot of EVERY rank with plain st.global over NVLink, and the
-//     CTA that finishes last raises this rank's flag in every block;
-//   * gather_wait_kernel on each rank waits until all ranks' flags show the current step, copies
-//     the staging slot to the caller's tensor and advances the rank's step counter.
+//   * decode rows (small, latency-bound): the decode kernel's epilogue stores every value into the
+//     row area of EVERY rank as an 8-byte word {value, step + 1} with plain st.global over NVLink.  An
+//     aligned 8-byte store arrives whole, so each word is its own arrival flag: the sender needs no
+//     fence, no completion counter and no separate flag message.  collect_rows_kernel on each rank
+//     polls the words themselves, writes the packed fp32 rows to the caller's tensor and advances
+//     the rank's step counter.  Its launch overlaps the flight of the last stores.
+//   * any other per-head tensor (large, bandwidth-bound): push_kernel stores the local tensor into
+//     the staging slot of every rank, then one fence per CTA, a completion counter and a flag per
+//     rank; gather_wait_kernel waits for all ranks' flags, copies the slot out and advances the step.
 // Staging has two slots used in alternation (step parity): a rank that is already one step ahead
 // writes the other slot, and it cannot get two steps ahead because its own wait needs this rank's
 // next flag.  The step counter lives in device memory, so a CUDA graph of the step replays unchanged.
 // No TMA, no multicast, no multimem: loads are local, stores are ordinary peer stores.
-// The only wait is in gather_wait_kernel and it is bounded by wall time (LOGOS_OPT_PEER_WAIT_MS);
-// when it runs out the kernel raises the context's status word and returns.
+// The only waits are in the two receiving kernels and they are bounded by wall time
+// (LOGOS_OPT_PEER_WAIT_MS); when a wait runs out the kernel raises the context's status word and returns.
 #include <cuda.h>
 
 #include <cstring>
@@ -40,9 +44,9 @@ struct WaitArgs {
     int* status;
 };
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
     unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ unsigned long long global_ns() {
@@ -61,14 +65,17 @@ gather_wait_kernel(const WaitArgs w) {
         const unsigned* f = w.flags + threadIdx.x * (kCommFlagStride / sizeof(unsigned));
         const unsigned long long t0 = global_ns();
         unsigned spins = 0;
-        while ((int)(ld_acquire_sys(f) - (step + 1u)) < 0) {
+        // relaxed polls and one acquire fence at the end: an acquire on every poll would pay for a
+        // system-scope fence each time round
+        while ((int)(ld_relaxed_sys(f) - (step + 1u)) < 0) {
             if ((++spins & 31u) == 0u && global_ns() - t0 > w.limit_ns) {
                 // bits [16,24): the rank that did not arrive; 0x20000000 marks a peer wait
                 atomicCAS(w.status, 0, 0x20000000 | ((int)threadIdx.x << 16) | 1);
                 break;
             }
-            __nanosleep(64);
+            __nanosleep(32);
         }
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
     }
     __syncthreads();
     // staging -> the caller's tensor; the rows came from other GPUs, so they are read past L1
@@ -85,9 +92,67 @@ gather_wait_kernel(const WaitArgs w) {
     }
 }
 
+struct CollectArgs {
+    const uint4* rows;         // this rank's row area: two slots of slot_words 8-byte words, read two at a time
+    float2* dst;               // packed rows
+    unsigned* step;
+    unsigned* copy_done;
+    size_t slot_pairs, n_pairs;   // 16-byte units (two values) per slot / to collect
+    int H_total, DH, world;       // rows are [B][H_total][DH]; used to name a missing rank
+    unsigned long long limit_ns;
+    int* status;
+};
+
+// Polls the 8-byte words {value, mark} that the peers' decode kernels store into this rank's row area
+// until every mark shows the current step, and writes the values out packed.
+__global__ void __launch_bounds__(256)
+collect_rows_kernel(const CollectArgs c) {
+    __shared__ unsigned step_s;
+    if (threadIdx.x == 0) step_s = *reinterpret_cast<volatile unsigned*>(c.step);
+    __syncthreads();
+    const unsigned step = step_s, mark = step + 1u;
+    const uint4* src = c.rows + (size_t)(step & 1u) * c.slot_pairs;
+    const unsigned long long t0 = global_ns();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < c.n_pairs; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 w;
+        unsigned spins = 0;
+        for (;;) {
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src + i) : "memory");
+            if (w.y == mark && w.w == mark) break;
+            if ((++spins & 63u) == 0u && global_ns() - t0 > c.limit_ns) {
+                // which rank's rows are missing: value 2 i lies in head (2 i / DH) % H_total
+                const int rank = (int)(((2 * i) / (size_t)c.DH) % (size_t)c.H_total) / (c.H_total / c.world);
+                atomicCAS(c.status, 0, 0x20000000 | (rank << 16) | 1);
+                break;
+            }
+            __nanosleep(20);
+        }
+        c.dst[i] = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(c.copy_done, 1u);
+        if (prev == gridDim.x - 1) {       // every CTA has read the step: it may move on
+            *c.copy_done = 0;
+            *reinterpret_cast<volatile unsigned*>(c.step) = step + 1u;
+        }
+    }
+}
+
+// Where the flag protocol sends a tensor: every rank's staging slot and flag word.
+struct PushTargets {
+    float* stage[kMaxPeers];      // staging area of each rank: two slots of slot_floats floats (step parity)
+    unsigned* flag[kMaxPeers];    // in rank r's block: the word THIS rank sets to step + 1
+    const unsigned* step;
+    unsigned* done;               // CTAs of this launch that have stored their part; zero between launches
+    size_t slot_floats;
+    int world, H_total, head0;
+};
+
 struct PushArgs {
     const uint4* local;        // [B][H_local][row16] 16-byte vectors
-    PeerEpilogue peer;
+    PushTargets peer;
     int B, H_local;
     size_t row16;              // 16-byte vectors per (b, h) row
 };
@@ -127,6 +192,17 @@ int comm_ready(logos_ctx* ctx, const logos_comm* c) {
 }  // namespace
 
 void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out) {
+    for (int r = 0; r < c->world; ++r)
+        out->rows[r] = reinterpret_cast<uint2*>(c->peer[r] + kCommStageOff + 2 * c->slot_bytes);
+    out->step = reinterpret_cast<const unsigned*>(c->block + kCommStepOff);
+    out->slot_words = c->row_slot_bytes / sizeof(uint2);
+    out->world = c->world;
+    out->H_total = H_local * c->world;
+    out->head0 = H_local * c->rank;
+}
+
+namespace {
+void push_targets(const logos_comm* c, int H_local, PushTargets* out) {
     for (int r = 0; r < c->world; ++r) {
         out->stage[r] = reinterpret_cast<float*>(c->peer[r] + kCommStageOff);
         out->flag[r] = reinterpret_cast<unsigned*>(c->peer[r] + (size_t)c->rank * kCommFlagStride);
@@ -137,6 +213,34 @@ void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out) {
     out->world = c->world;
     out->H_total = H_local * c->world;
     out->head0 = H_local * c->rank;
+}
+}  // namespace
+
+int comm_collect_rows(logos_ctx* ctx, logos_comm* c, float* gathered, int B, int H_total, int DH) {
+    int rc = comm_ready(ctx, c);
+    if (rc != LOGOS_OK) return rc;
+    if (B <= 0 || H_total <= 0 || DH <= 0 || H_total % c->world != 0)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "collect_rows: bad extents");
+    const size_t values = (size_t)B * H_total * DH;
+    if (!gathered || values == 0 || (values & 1u) || values * sizeof(uint2) > c->row_slot_bytes ||
+        (reinterpret_cast<uintptr_t>(gathered) & 7u))
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "collect_rows: %zu values do not fit the row area (%zu bytes per slot)",
+                    values, c->row_slot_bytes);
+    CollectArgs a;
+    a.rows = reinterpret_cast<const uint4*>(c->block + kCommStageOff + 2 * c->slot_bytes);
+    a.dst = reinterpret_cast<float2*>(gathered);
+    a.step = reinterpret_cast<unsigned*>(c->block + kCommStepOff);
+    a.copy_done = reinterpret_cast<unsigned*>(c->block + kCommCopyDoneOff);
+    a.slot_pairs = c->row_slot_bytes / sizeof(uint4);
+    a.n_pairs = values / 2;
+    a.H_total = H_total; a.DH = DH; a.world = c->world;
+    a.limit_ns = (unsigned long long)ctx->peer_wait_ms * 1000000ull;
+    a.status = ctx->tc_status;
+    size_t ctas = (a.n_pairs + 255) / 256;
+    if (ctas > (size_t)ctx->sm_count * 4) ctas = (size_t)ctx->sm_count * 4;
+    collect_rows_kernel<<<(unsigned)ctas, 256, 0, ctx->stream>>>(a);
+    LOGOS_LAUNCH_CHECK(ctx, "collect_rows_kernel");
+    return LOGOS_OK;
 }
 
 int comm_wait(logos_ctx* ctx, logos_comm* c, void* gathered, size_t bytes) {
@@ -172,7 +276,7 @@ int comm_push(logos_ctx* ctx, logos_comm* c, const void* local, int B, int H_loc
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "comm_push: gathered tensor exceeds the slot of %zu bytes", c->slot_bytes);
     PushArgs a;
     a.local = reinterpret_cast<const uint4*>(local);
-    comm_peer_epilogue(c, H_local, &a.peer);
+    push_targets(c, H_local, &a.peer);
     a.B = B; a.H_local = H_local; a.row16 = row_bytes / 16;
     size_t n = (size_t)B * H_local * a.row16, ctas = (n + 255) / 256;
     if (ctas > (size_t)ctx->sm_count * 8) ctas = (size_t)ctx->sm_count * 8;
@@ -194,7 +298,10 @@ int logos_comm_create(logos_ctx* ctx, int rank, int world, size_t gathered_bytes
     if (!c) return LOGOS_ERR_CUDA;
     c->ctx = ctx; c->rank = rank; c->world = world;
     c->slot_bytes = (gathered_bytes + 255) & ~(size_t)255;
-    const size_t total = logos::kCommStageOff + 2 * c->slot_bytes;
+    // the row area takes 8 bytes per fp32 value of a gathered decode output, up to a cap: decode
+    // outputs are small, the staging slots may be sized for a prefill tensor
+    c->row_slot_bytes = 2 * c->slot_bytes < logos::kCommRowSlotMax ? 2 * c->slot_bytes : logos::kCommRowSlotMax;
+    const size_t total = logos::kCommStageOff + 2 * c->slot_bytes + 2 * c->row_slot_bytes;
     if (cudaSetDevice(ctx->device) != cudaSuccess || cudaMalloc(&c->block, total) != cudaSuccess ||
         cudaMemset(c->block, 0, total) != cudaSuccess) {
         const cudaError_t e = cudaGetLastError();
@@ -225,9 +332,16 @@ int logos_comm_handle(logos_comm* c, void* handle_out) {
     memset(&h, 0, sizeof(h));
     LOGOS_CUDA_TRY(c->ctx, cudaSetDevice(c->ctx->device));
     LOGOS_CUDA_TRY(c->ctx, cudaIpcGetMemHandle(&h.ipc, c->block));
+    // the driver entry point is looked up at run time: the library must load where there is no driver
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess || !fn)
+        return logos::fail(c->ctx, LOGOS_ERR_CUDA, "comm_handle: cuMemGetAddressRange is not available");
     CUdeviceptr base = 0;
     size_t size = 0;
-    if (cuMemGetAddressRange(&base, &size, reinterpret_cast<CUdeviceptr>(c->block)) != CUDA_SUCCESS)
+    if (reinterpret_cast<RangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(c->block)) != CUDA_SUCCESS)
         return logos::fail(c->ctx, LOGOS_ERR_CUDA, "comm_handle: cuMemGetAddressRange failed");
     h.offset = reinterpret_cast<CUdeviceptr>(c->block) - base;
     h.magic = 0x4c4f474f53000000ull ^ (reinterpret_cast<unsigned long long>(c->block) * 0x9e3779b97f4a7c15ull) ^ (unsigned)c->rank;

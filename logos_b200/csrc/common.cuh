@@ -32,15 +32,15 @@ struct logos_ctx {
 };
 
 // Heads spread over several GPUs: where a finished decode row goes.  Every rank owns one block of
-// device memory that its peers can write (logos_comm); a row is stored into the staging slot of
-// EVERY rank, and when all rows of this rank are out the rank raises its flag in every block.
+// device memory that its peers can write (logos_comm).  A row is stored into the row area of EVERY
+// rank, each value as one 8-byte word {value bits, step + 1}: an aligned 8-byte store arrives whole,
+// so the word is its own arrival flag and the sender needs no fence, no counter and no second
+// message; the receiving kernel polls the words themselves (collect_rows_kernel in comm.cu).
 constexpr int kMaxPeers = 8;
 struct PeerEpilogue {
-    float* stage[kMaxPeers];      // staging area of each rank: two slots of slot_floats floats (step parity)
-    unsigned* flag[kMaxPeers];    // in rank r's block: the word THIS rank sets to step + 1
-    const unsigned* step;         // this rank's step counter (advanced by the wait kernel)
-    unsigned* done;               // rows of this launch already stored; zero between launches
-    size_t slot_floats;
+    uint2* rows[kMaxPeers];       // row area of each rank: two slots of slot_words words (step parity)
+    const unsigned* step;         // this rank's step counter (advanced by the collecting kernel)
+    size_t slot_words;
     int world;                    // 0: no peers, rows go to DecodeArgs::out
     int H_total, head0;           // heads of the whole model, first head of this rank
 };
@@ -49,6 +49,7 @@ struct logos_comm {
     logos_ctx* ctx = nullptr;
     int rank = 0, world = 1;
     size_t slot_bytes = 0;                 // bytes of one gathered tensor, rounded up to 256
+    size_t row_slot_bytes = 0;             // bytes of one slot of the row area: 8 per fp32 value
     unsigned char* block = nullptr;        // this rank's block (cudaMalloc)
     unsigned char* peer[kMaxPeers] = {};   // every rank's block as seen from this device (peer[rank] == block)
     void* ipc_base[kMaxPeers] = {};        // what cudaIpcOpenMemHandle returned for a peer (to be closed)
@@ -64,6 +65,7 @@ constexpr size_t kCommDoneOff = 1028;
 constexpr size_t kCommCopyDoneOff = 1032;
 constexpr size_t kCommMagicOff = 1040;     // 8-byte mark written at hand-out, checked by peers after mapping
 constexpr size_t kCommStageOff = 4096;
+constexpr size_t kCommRowSlotMax = 2u << 20;   // bytes of one row-area slot at most (2 x 1 MiB of fp32 rows)
 
 inline int fail(logos_ctx* ctx, int status, const char* fmt, ...) {
     if (ctx) {
@@ -175,5 +177,6 @@ int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const v
                  void* O, int B, int H, int S, int DH, const logos_attn_params*);
 void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out);
 int comm_wait(logos_ctx*, logos_comm*, void* gathered, size_t bytes);
+int comm_collect_rows(logos_ctx*, logos_comm*, float* gathered, int B, int H_total, int DH);
 int comm_push(logos_ctx*, logos_comm*, const void* local, int B, int H_local, size_t row_bytes);
 }  // namespace logos

@@ -58,40 +58,23 @@ struct DecodeArgs {
     PeerEpilogue peer;     // world == 0: rows go to `out`
 };
 
-__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 // The finished row of pair bh (thread d < 64 holds channel d); called by every thread of the CTA.
-// Without peers the row goes to `out`.  With peers it goes into the current staging slot of every
-// rank at this rank's head offset, with plain stores over NVLink; the CTA that stores the rank's last
-// row of the launch then raises this rank's flag in every block (release at system scope, after
-// fences that order all rows before it).  Nobody waits here: the receiving side has its own kernel.
-__device__ __forceinline__ void emit_row(const DecodeArgs& a, int bh, int tid, float value, int n_pairs) {
+// Without peers the row goes to `out`.  With peers every value goes, as one 8-byte word {bits, step + 1},
+// into the current row-area slot of every rank at this rank's head offset -- plain stores over NVLink,
+// nothing to wait for: the word carries its own arrival mark.
+__device__ __forceinline__ void emit_row(const DecodeArgs& a, int bh, int tid, float value) {
+    if (tid >= kDH) return;
     if (a.peer.world == 0) {
-        if (tid < kDH) a.out[(int64_t)bh * kDH + tid] = value;
+        a.out[(int64_t)bh * kDH + tid] = value;
         return;
     }
     const unsigned step = *a.peer.step;
     const int b = bh / a.H, h = bh - b * a.H;
-    const size_t idx = (size_t)(step & 1u) * a.peer.slot_floats +
+    const size_t idx = (size_t)(step & 1u) * a.peer.slot_words +
                        ((size_t)b * a.peer.H_total + a.peer.head0 + h) * kDH + tid;
-    if (tid < kDH)
-        for (int r = 0; r < a.peer.world; ++r) a.peer.stage[r][idx] = value;
-    __syncthreads();
-    // One fence for the CTA: the barrier above orders every thread's stores before thread 0's fence,
-    // and a release is cumulative over what was ordered before it.  (A system-scope fence waits for
-    // the peers' acknowledgements, microseconds over NVLink: one per row, not one per thread.)
-    if (tid == 0) {
-        fence_acq_rel_sys();
-        const unsigned prev = atomicAdd(a.peer.done, 1u);
-        if (prev == (unsigned)(n_pairs - 1)) {
-            *a.peer.done = 0;             // ready for the next launch
-            fence_acq_rel_sys();
-            for (int r = 0; r < a.peer.world; ++r) st_release_sys(a.peer.flag[r], step + 1u);
-        }
-    }
+    const unsigned bits = __float_as_uint(value), mark = step + 1u;
+    for (int r = 0; r < a.peer.world; ++r)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.peer.rows[r] + idx), "r"(bits), "r"(mark) : "memory");
 }
 
 // Four int8 lanes of a 32-bit word -> four floats.  x ^ 0x80 is the value biased
@@ -559,7 +542,6 @@ decode_dense_kernel(const DecodeArgs a) {
     }
 
     const float vs = a.v_scale[bh];
-    const int n_pairs = gridDim.y;
 
     if (n_splits == 1) {
         float r = 0.0f;
@@ -570,7 +552,7 @@ decode_dense_kernel(const DecodeArgs a) {
                 r = (1.0f - a.alpha) * r_std + a.alpha * r;
             }
         }
-        emit_row(a, bh, tid, r * vs, n_pairs);
+        emit_row(a, bh, tid, r * vs);
         return;
     }
 
@@ -616,7 +598,7 @@ decode_dense_kernel(const DecodeArgs a) {
         if (BLEND) r = (1.0f - a.alpha) * r_path[PATHS - 1] + a.alpha * r_path[0];
         r_out = r * vs;
     }
-    emit_row(a, bh, tid, r_out, n_pairs);
+    emit_row(a, bh, tid, r_out);
 }
 
 // ---------------------------------------------------------------------------
@@ -640,7 +622,7 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row_in_warp = lane >> 2, part = lane & 3;
     if (len == 0) {
-        emit_row(a, bh, tid, 0.0f, gridDim.x);
+        emit_row(a, bh, tid, 0.0f);
         return;
     }
     // enumeration of visible keys: landmarks before the window, then the window
@@ -746,7 +728,7 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
         }
         r *= a.v_scale[bh];
     }
-    emit_row(a, bh, tid, r, gridDim.x);
+    emit_row(a, bh, tid, r);
 }
 
 // Keys per split of the dense kernel, the one rule of both entry points: the largest chunk that

@@ -177,6 +177,11 @@ class Engine:
                                                    _ptr(v_cache), _ptr(k_scale), _ptr(v_scale), _ptr(lens), B, H,
                                                    S_max, DH, C.byref(params)))
 
+    def decode_int8_collect(self, comm: "Comm", gathered: torch.Tensor):
+        """Wait for every rank's rows of the step and write them to gathered ([B, H, DH] fp32)."""
+        B, H, DH = gathered.shape
+        self._check(self.lib.logos_decode_int8_collect(self.h, comm.h, _ptr(gathered), B, H, DH))
+
     def decode_step_host(self, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, lens, params,
                          out):
         """All of q, q_prev, k_new, v_new, lens, out are HOST (ideally pinned) tensors."""

@@ -60,6 +60,7 @@ SIGNATURES = {
     "logos_comm_connect_local": (_i, [C.POINTER(_vp), _i]),
     "logos_comm_destroy": (_i, [_vp]),
     "logos_decode_int8_push": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
+    "logos_decode_int8_collect": (_i, [_vp, _vp, _vp, _i, _i, _i]),
     "logos_decode_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
     "logos_decode_step_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
     "logos_decode_step_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,

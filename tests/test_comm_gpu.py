@@ -81,7 +81,7 @@ def test_local_ranks_match_one_gpu_bit_for_bit(engine, ranks, world, window):
                 e.decode_int8_push(comms[r], _slice(q, lo, hi), _slice(qp, lo, hi), _slice(kq, lo, hi),
                                    _slice(vq, lo, hi), _slice(ks, lo, hi), _slice(vs, lo, hi), lens, p)
             for r in range(world):          # ... then nobody has to wait
-                comms[r].wait(outs[r])
+                engs[r].decode_int8_collect(comms[r], outs[r])
             for e in engs:
                 e.synchronize()
             for r in range(world):
