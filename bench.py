@@ -42,6 +42,7 @@ REPEATS = 7      # the `steps` loop is timed this many times; the median is repo
 # from a hardware-counter capture of a 256-pair launch (268.55 MB read + 4.20 MB written).  Pairs are
 # independent, so a launch moves this times its number of pairs.
 DECODE_TRAFFIC_PER_PAIR = (268.55e6 + 4.20e6) / 256
+L_OPT_WORKSPACE_LOCK = 3            # logos_option of include/logos_attn.h
 METRIC = "int8_kv_decode_attention_bandwidth_8k_ctx"
 UNIT = "GB/s"
 
@@ -328,6 +329,87 @@ def measure_attention(eng, dev, world, rank, cfg, steps, warmup, barrier, max_ov
     return out
 
 
+def measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks, layers=16, batch=32, prompt=2048, steps=128) -> dict:
+    """Benchmark configuration 5: the 16-layer attention stack (d 1024, 16 heads, vocabulary 8192, weights
+    ~ N(0, 0.02)), 32 prompts of 2048 uniform-random token ids prefilled into the INT8 cache, then 128
+    decode steps with Shunyam window 64 / stride 16; heads sharded over the GPUs, per-head outputs gathered.
+    Reports tokens/s of the decode phase, the time of each phase and the attention kernels' own share."""
+    import torch
+    from logos_b200.stack import AttentionStack, StackConfig, make_weights
+    cfg = StackConfig(num_layers=layers, max_seq_len=prompt + steps)
+    w = make_weights(cfg, seed=5, std=0.02, device=dev)
+    st = AttentionStack(eng, cfg, w, batch=batch, rank=rank, world=world, comm=comm)
+    del w
+    g = torch.Generator(device=dev).manual_seed(5000)
+    ids = torch.randint(0, cfg.vocab_size, (batch, prompt), device=dev, generator=g)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    st.prefill(ids)                                    # warm-up (lazy set-up, allocator)
+    barrier()
+    ev[0].record()
+    logits = st.prefill(ids)
+    ev[1].record()
+    barrier()
+    prefill_ms = max_over_ranks(ev[0].elapsed_time(ev[1]))
+    graph, gids, glogits = st.capture_decode()
+    tok = logits.argmax(dim=1)
+    barrier()
+    ev[0].record()
+    for _ in range(steps):
+        gids.copy_(tok)
+        graph.replay()
+        if comm is not None:
+            comm.steps += layers                       # one exchange per layer inside the replayed step
+        tok = glogits.argmax(dim=1)
+    ev[1].record()
+    barrier()
+    decode_ms = max_over_ranks(ev[0].elapsed_time(ev[1]))
+    finite = bool(torch.isfinite(glogits).all())
+    # the attention kernels alone, on one layer's tensors
+    Hl, S = st.Hl, prompt
+    Q, K, V = (torch.randn((batch, Hl, S, DH), device=dev, generator=g).bfloat16() for _ in range(3))
+    for _ in range(2):
+        O = eng.attention(Q, K, V, st.params)
+    ev[0].record()
+    for _ in range(5):
+        eng.attention(Q, K, V, st.params, out=O)
+    ev[1].record()
+    torch.cuda.synchronize()
+    attn_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / 5)
+    kc, vc, ks, vs = st.cache.layer(0)
+    q = torch.randn((batch, Hl, DH), device=dev, generator=g).half()
+    lens = st.cache.lens.clone()
+    o = torch.empty((batch, Hl, DH), device=dev)
+    for _ in range(3):
+        eng.decode_int8(q, q, kc, vc, ks, vs, lens, st.params, out=o)
+    ev[0].record()
+    for _ in range(20):
+        eng.decode_int8(q, q, kc, vc, ks, vs, lens, st.params, out=o)
+    ev[1].record()
+    torch.cuda.synchronize()
+    dec_attn_ms = max_over_ranks(ev[0].elapsed_time(ev[1]) / 20)
+    ctx = prompt + steps
+    keys = min(ctx, cfg.window + 1) + max(0, (ctx - 1 - cfg.window + cfg.stride - 1) // cfg.stride)   # window + landmarks
+    peaks = measured_peaks()
+    graph.reset()
+    eng.set_option(L_OPT_WORKSPACE_LOCK, 0)
+    win_bytes = 4 * batch * cfg.num_heads * S * DH * 2
+    return {"workload": f"stack_l{layers}_d1024_h16_b{batch}_prompt{prompt}_decode{steps}_window64_stride16",
+            "n_gpus": world, "tokens_per_s_decode": batch * steps / (decode_ms * 1e-3),
+            "tokens_per_s_prefill": batch * prompt / (prefill_ms * 1e-3),
+            "prefill_ms": prefill_ms, "decode_ms_per_step": decode_ms / steps, "logits_finite": finite,
+            "launch": "prefill eager, decode step replayed as one CUDA graph (all layers)",
+            "attention_only": {
+                "prefill_attention_ms_per_layer": attn_ms,
+                "prefill_attention_share_of_phase": attn_ms * layers / prefill_ms,
+                "prefill_attention_gbs": win_bytes / world / (attn_ms * 1e-3) / 1e9,
+                "prefill_attention_frac_of_hbm_peak": win_bytes / world / (attn_ms * 1e-3) / 1e9 / peaks["hbm"],
+                "decode_attention_ms_per_layer": dec_attn_ms,
+                "decode_attention_share_of_step": dec_attn_ms * layers / (decode_ms / steps),
+                "decode_visible_keys_per_query_at_end": keys,
+                "decode_attention_bytes_per_step_per_layer": batch * cfg.num_heads * keys * DH * 2,
+                "note": "decode attention reads ~200 scattered rows per pair: latency-bound, not a bandwidth figure"}}
+
+
 def reference_gpu_kernels(eng, dev) -> list:
     """One head of the prefill and of the window configuration through the reference's own CUDA path
     (ns_advect_kernel + ns_diffuse_kernel + cuda_flash_attention_fwd, compiled unmodified for sm_100a)
@@ -426,7 +508,7 @@ def run_ours(args) -> None:
     if world > 1:
         biggest = B * H * DH * 4
         if args.workload != "decode" or not args.no_secondary:
-            biggest = max(biggest, 8 * H * 8192 * DH * 2)
+            biggest = max(biggest, 8 * H * 8192 * DH * 2, 32 * H * 2048 * DH * 2)
         comm = Comm(eng, rank, world, biggest)
         connect_comm(comm)
 
@@ -438,6 +520,16 @@ def run_ours(args) -> None:
         eng.close()
         if world > 1:
             dist.destroy_process_group()
+
+    if args.workload == "stack":
+        r = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
+        if rank == 0:
+            print(json.dumps({"metric": "stack_decode_tokens_per_s", "value": r["tokens_per_s_decode"], "unit": "tokens/s",
+                              "n_gpus": world, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                              "dtype": "bf16 projections, int8 KV", "data": "synthetic", "config": {"workload": r["workload"]},
+                              "detail": r}))
+        finish()
+        return
 
     if args.workload in ("prefill", "prefill8k", "window", "window_lm"):
         cfg = dict({"prefill": PREFILL, "prefill8k": PREFILL_8K, "window": WINDOW, "window_lm": WINDOW_LM}[args.workload])
@@ -593,6 +685,8 @@ def run_ours(args) -> None:
         line["secondary"] = [measure_attention(eng, dev, world, rank, cfg, max(3, args.steps // 4), 3, barrier,
                                                max_over_ranks, comm)
                              for cfg in (PREFILL, PREFILL_8K, WINDOW, WINDOW_LM)]
+        torch.cuda.empty_cache()
+        line["stack"] = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["baselines"] = {"reference_gpu_kernels_on_this_gpu": reference_gpu_kernels(eng, dev),
                              "configuration_1_reference_cpu_forward": configuration1_cpu_baseline()}
@@ -612,7 +706,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU legs and the reference's GPU kernels")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack"],
                     help="decode is the benchmark; the others time one attention kernel alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")

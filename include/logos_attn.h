@@ -82,6 +82,14 @@ int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream);
 /* Grows the context-owned workspace to at least `bytes` (cudaMalloc; not a hot call).  Growing frees
  * the old block: see LOGOS_OPT_WORKSPACE_LOCK when captured graphs use it. */
 int logos_ctx_reserve(logos_ctx* ctx, size_t bytes);
+/* The allocator logos_ctx_reserve takes the workspace from, for hosts whose memory pool owns the device
+ * (null functions restore cudaMalloc / cudaFree).  alloc returns 0 and a 256-byte aligned device pointer,
+ * or non-zero; then logos_ctx_reserve fails with LOGOS_ERR_WORKSPACE and the context keeps the
+ * workspace it had.  A block is always released through the free function that was current when it
+ * was allocated. */
+typedef int (*logos_alloc_fn)(void** device_ptr, size_t bytes, void* user);
+typedef void (*logos_free_fn)(void* device_ptr, void* user);
+int logos_ctx_set_allocator(logos_ctx* ctx, logos_alloc_fn alloc, logos_free_fn free_fn, void* user);
 /* Uses caller memory as workspace instead (256-byte aligned device memory). */
 int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes);
 /* Waits for the context's stream and reports LOGOS_ERR_KERNEL_TIMEOUT if a kernel gave up
@@ -165,6 +173,13 @@ int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t sr
                       int8_t* dst, int64_t dst_stride, float* scales, int n_tensors,
                       int64_t elems);
 
+/* logos_kv_quantize without its first pass: absmax[t] = max|x| of tensor t is already known (the
+ * projection GEMM below reduces it in its epilogue, over exactly the values it stored).  Same bytes
+ * and scales as logos_kv_quantize on the same tensors. */
+int logos_kv_quantize_absmax(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,
+                             int8_t* dst, int64_t dst_stride, const float* absmax, float* scales,
+                             int n_tensors, int64_t elems);
+
 /* Stand-in for nikhilam_decompress / nikhilam_dequantize_kernel
  * (cuda/ModelGPU.cu:343-351,388-395): dst = (float)q * scale. */
 int logos_kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const float* scales,
@@ -242,6 +257,29 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
                               const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                               const float* v_scale, const int32_t* len, int B, int H, int S_max,
                               int DH, const logos_attn_params* params, float* out);
+
+/* ---- projections either side of the attention ---------------------------- */
+
+/* The reference projects head by head: three [seq x d]·[d x 64] GEMMs per head for Q, K, V
+ * (cuda/ModelGPU.cu:899-906, amp_gemm -> cuda_gemm_fp16_fp32out, cuda/MixedPrecision.cuh:301-330, on
+ * the FP16 shadow of the weights, cuda/MixedPrecision.cuh:149-161), one [seq x 64]·[64 x d] per head
+ * summed into `concat` (cuda/ModelGPU.cu:974-988), one [seq x d]·[d x d] for W_proj (:990-1015).  Here:
+ *
+ * logos_qkv_project -- all heads' Q, K and V of a layer in ONE tensor-core GEMM, X [B*S][D_model] times
+ *   the stacked weights, written straight into the attention layout [B][H][S][64] (same 16-bit dtype as
+ *   X).  Wt_qkv is the K-major 16-bit shadow of the stacked weight: row n = (which * H + h) * 64 + c holds
+ *   column c of W_Q[h] (which 0), W_K[h] (1) or W_V[h] (2), i.e. Wt_qkv[n][k] = W[k][c].  With k_absmax /
+ *   v_absmax (float [B][H], both or neither) the epilogue also leaves max|x| of every stored K and V
+ *   tensor there, ready for logos_kv_quantize_absmax.  DH is 64; D_model a multiple of 8.
+ *
+ * logos_project -- C [M][N] = A [M][K] · W (+ residual [M][N]), A and the K-major shadow Wt [N][K] in
+ *   one 16-bit dtype, C and the residual in out_dtype (that dtype or LOGOS_F32).  With the heads'
+ *   outputs laid side by side ([M][H*64]) and W_O[h] stacked along K it is the reference's sum over
+ *   heads; with W_proj it is the output projection plus the residual add that follows it. */
+int logos_qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt_qkv, void* Q, void* K, void* V,
+                      int B, int S, int H, int D_model, float* k_absmax, float* v_absmax);
+int logos_project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual,
+                  void* C, int M, int N, int K);
 
 /* ---- heads over several GPUs -------------------------------------------- */
 

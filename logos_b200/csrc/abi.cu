@@ -14,6 +14,19 @@ bool params_ok(const logos_attn_params* p) {
            p->ns_alpha >= 0.0f && p->ns_alpha <= 1.0f && p->window >= 0;
 }
 
+// the workspace block and how to give it back
+void release_workspace(logos_ctx* ctx) {
+    if (ctx->owns_workspace && ctx->workspace) {
+        if (ctx->ws_free_fn) ctx->ws_free_fn(ctx->workspace, ctx->ws_free_user);
+        else cudaFree(ctx->workspace);
+    }
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    ctx->owns_workspace = false;
+    ctx->ws_free_fn = nullptr;
+    ctx->ws_free_user = nullptr;
+}
+
 }  // namespace
 
 extern "C" {
@@ -70,7 +83,7 @@ int logos_ctx_create(int device, logos_ctx** out) {
 int logos_ctx_destroy(logos_ctx* ctx) {
     if (!ctx) return LOGOS_OK;
     cudaSetDevice(ctx->device);
-    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
+    release_workspace(ctx);
     if (ctx->absmax_scratch) cudaFree(ctx->absmax_scratch);
     if (ctx->tc_status) cudaFree(ctx->tc_status);
     delete ctx;
@@ -83,6 +96,14 @@ int logos_ctx_set_stream(logos_ctx* ctx, void* cuda_stream) {
     return LOGOS_OK;
 }
 
+int logos_ctx_set_allocator(logos_ctx* ctx, logos_alloc_fn alloc, logos_free_fn free_fn, void* user) {
+    if (!ctx || ((alloc == nullptr) != (free_fn == nullptr))) return LOGOS_ERR_INVALID_ARG;
+    ctx->alloc_fn = alloc;
+    ctx->free_fn = free_fn;
+    ctx->alloc_user = user;
+    return LOGOS_OK;
+}
+
 int logos_ctx_reserve(logos_ctx* ctx, size_t bytes) {
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
     if (ctx->workspace && ctx->workspace_bytes >= bytes) return LOGOS_OK;
@@ -90,19 +111,33 @@ int logos_ctx_reserve(logos_ctx* ctx, size_t bytes) {
         return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "reserve: the workspace is locked (a captured graph uses it) and holds "
                            "%zu bytes, %zu wanted; reserve the largest size before capturing", ctx->workspace_bytes, bytes);
     LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    // Work queued on the stream may still use the old block.
-    LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
-    ctx->workspace = nullptr;
-    ctx->workspace_bytes = 0;
-    ctx->owns_workspace = false;
+    // the new block first: if it cannot be had, the context keeps what it has
     void* p = nullptr;
-    LOGOS_CUDA_TRY(ctx, cudaMalloc(&p, bytes));
+    if (ctx->alloc_fn) {
+        if (ctx->alloc_fn(&p, bytes, ctx->alloc_user) != 0 || !p)
+            return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "reserve: the caller's allocator could not supply %zu bytes", bytes);
+        if (reinterpret_cast<uintptr_t>(p) & 255u) {
+            ctx->free_fn(p, ctx->alloc_user);
+            return logos::fail(ctx, LOGOS_ERR_ALIGNMENT, "reserve: the caller's allocator returned a block that is not 256-byte aligned");
+        }
+    } else if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "reserve: cudaMalloc of %zu bytes failed", bytes);
+    }
+    // Work queued on the stream may still use the old block.
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
     // arrival counters at the head of the workspace must start at zero
-    LOGOS_CUDA_TRY(ctx, cudaMemset(p, 0, bytes));
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    if (e != cudaSuccess) {
+        if (ctx->alloc_fn) ctx->free_fn(p, ctx->alloc_user); else cudaFree(p);
+        return logos::fail(ctx, LOGOS_ERR_CUDA, "reserve: %s", cudaGetErrorString(e));
+    }
+    release_workspace(ctx);
     ctx->workspace = p;
     ctx->workspace_bytes = bytes;
     ctx->owns_workspace = true;
+    ctx->ws_free_fn = ctx->alloc_fn ? ctx->free_fn : nullptr;
+    ctx->ws_free_user = ctx->alloc_user;
     return LOGOS_OK;
 }
 
@@ -114,7 +149,7 @@ int logos_ctx_set_workspace(logos_ctx* ctx, void* device_ptr, size_t bytes) {
         return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "set_workspace: the workspace is locked (a captured graph uses it)");
     LOGOS_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (ctx->owns_workspace && ctx->workspace) cudaFree(ctx->workspace);
+    release_workspace(ctx);
     ctx->workspace = device_ptr;
     ctx->workspace_bytes = bytes;
     ctx->owns_workspace = false;
@@ -254,6 +289,26 @@ int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t sr
                       int64_t elems) {
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
     return logos::kv_quantize(ctx, src_dtype, src, src_stride, dst, dst_stride, scales, n_tensors, elems);
+}
+
+int logos_kv_quantize_absmax(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,
+                             int8_t* dst, int64_t dst_stride, const float* absmax, float* scales, int n_tensors,
+                             int64_t elems) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!absmax) return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_quantize_absmax: absmax table missing");
+    return logos::kv_quantize(ctx, src_dtype, src, src_stride, dst, dst_stride, scales, n_tensors, elems, absmax);
+}
+
+int logos_project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual,
+                  void* C, int M, int N, int K) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::project(ctx, dtype, out_dtype, A, Wt, residual, C, M, N, K);
+}
+
+int logos_qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt_qkv, void* Q, void* K, void* V,
+                      int B, int S, int H, int D_model, float* k_absmax, float* v_absmax) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::qkv_project(ctx, dtype, X, Wt_qkv, Q, K, V, B, S, H, D_model, k_absmax, v_absmax);
 }
 
 int logos_kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const float* scales,

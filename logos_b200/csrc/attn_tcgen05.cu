@@ -14,7 +14,7 @@
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
 // A work item = 256 query rows of one head as two 128-row tiles that share every K/V tile.  The CTA
-// (384 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
+// (512 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
 // rings run on across items, so one item's epilogue overlaps the other tile's work and the next
 // item's loads.  Roles, one warpgroup each so that registers can be moved between them (setmaxnreg):
 //   warps 0-3 / 4-7  softmax of tile 0 / tile 1, one thread per query row (= TMEM lane) with the
@@ -31,21 +31,24 @@
 //              memory; completion via tcgen05.commit; the scores of the next tile are issued before
 //              the current tile's weights are waited for.  The whole warp runs the loop, one elected
 //              lane issues;
-//   warp 11    V converter: the MMA takes one type for both operands, so for BF16 inputs this warp
-//              turns each V tile into FP16 in place (exact in FP16's normal range, saturating beyond).
+//   warp 11    spare (a warpgroup is four warps);
+//   warps 12-15  V converters: the MMA takes one type for both operands and the weights are FP16, so for
+//              BF16 inputs every V tile is turned into FP16 in place (exact in FP16's normal range,
+//              saturating beyond), eight 16-byte chunks per thread per tile.  (One warp alone needed
+//              several thousand cycles per tile and set the pace of the kernel; done by the softmax
+//              threads it lengthened their chain by a tenth.)
 // TMEM (512 columns): S of tile 0 / 1 at [0,128) / [128,256), O at [256,320) / [320,384), FP16
 // weights (two keys per column) at [384,448) / [448,512).
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA raises an abort
 // flag, all roles leave their loops, TMEM is freed and the status word tells the host.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_ptx.cuh"
 
 namespace logos {
 namespace {
 
-constexpr int kBM = 128;              // rows of one query tile (= TMEM lanes)
+using namespace tc;
+
 constexpr int kTiles = 2;             // query tiles per CTA (2: both share every K/V tile, one CTA per SM)
 constexpr int kCtasPerSm = kTiles == 1 ? 2 : 1;   // one tile per CTA: two CTAs share an SM and its 512 TMEM columns
 constexpr int kBQ = kBM * kTiles;     // query rows per CTA
@@ -57,17 +60,17 @@ constexpr int kSoftmaxWarps = 4 * kTiles;   // one warpgroup per query tile, one
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr int kTmaWarp = kSoftmaxWarps;          // then one MMA warp per query tile (the first also owns TMEM)
 constexpr int kMmaWarp = kTmaWarp + 1;
-constexpr int kCvtWarp = kMmaWarp + kTiles;      // V converter warp
-constexpr int kTcThreads = 32 * (kCvtWarp + 1);
-static_assert(kTcThreads == 384 && kTmaWarp % 4 == 0, "three warpgroups: two of softmax threads, one of helpers");
-// registers per thread after the warpgroups have traded them (the kernel starts with 65536 / 384 = 168):
-// 256 softmax threads x 224 + 128 helper threads x 56 = 64512
+constexpr int kCvtWarp = kTmaWarp + 4;           // first of the four V converter warps (a warpgroup of their own)
+constexpr int kCvtThreads = 128;
+constexpr int kTcThreads = 32 * (kCvtWarp + 4);
+static_assert(kTcThreads == 512 && kTmaWarp % 4 == 0, "four warpgroups: two of softmax threads, two of helpers");
+// registers per thread after the warpgroups have traded them (the kernel starts with 65536 / 512 = 128):
+// 256 softmax threads x 208 + 256 helper threads x 48 = 65536
 #ifndef LOGOS_TC_REGS_SOFTMAX
-#define LOGOS_TC_REGS_SOFTMAX 224
-#define LOGOS_TC_REGS_HELPER 56
+#define LOGOS_TC_REGS_SOFTMAX 208
+#define LOGOS_TC_REGS_HELPER 48
 #endif
 constexpr int kRegsSoftmax = LOGOS_TC_REGS_SOFTMAX, kRegsHelper = LOGOS_TC_REGS_HELPER;
-constexpr uint32_t kSpinLimit = 1u << 22;     // bounded mbarrier polls per wait
 constexpr uint32_t kTmemCols = 256 * kTiles;
 constexpr uint32_t kColO = 128 * kTiles, kColP = kColO + 64 * kTiles;   // S first, then O, then the weights
 constexpr float kRescaleThreshold = 8.0f;     // log2 units before the running max is moved
@@ -101,134 +104,6 @@ struct TcArgs {
     int* status;        // device word: non-zero = a wait ran out
 };
 
-// ---- PTX wrappers -------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t limit = kSpinLimit) {
-    for (uint32_t it = 0; it < limit; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
-    }
-    // record who gave up first: bits [0,16) = shared-memory address of the barrier, [16,30) = thread id
-    atomicCAS(const_cast<int*>(abort_flag), 0, (int)((bar & 0xffffu) | (threadIdx.x << 16)) | 0x40000000);   // the kernel's teardown turns the address into an offset
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                           uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same, with the A operand read from tensor memory: lane = row, one 32-bit column = two 16-bit
-// K elements (the lower index in the lower half), 8 columns per k-step of 16.
-__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t* r) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
-                 ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
-    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
-// Bits: [0,14) start >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
-// [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// Instruction descriptor for kind::f16 with fp32 accumulation, M = 128.
-// Bits: [4,6) D format (1 = F32), [7,10) A format, [10,13) B format (0 = F16, 1 = BF16),
-// 15 A major, 16 B major (0 = K, 1 = MN), [17,23) N >> 3, [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int b_mn_major, int n) {
-    return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)b_mn_major << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-}
-
-__device__ __forceinline__ uint32_t f32_to_16(float x, bool f16) {
-    return f16 ? (uint32_t)__half_as_ushort(__float2half_rn(x))
-               : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
-}
 // -------------------------------------------------------------------------------------
 template <bool DIFF>
 __global__ void __launch_bounds__(kTcThreads, kCtasPerSm)
@@ -307,7 +182,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mbar_init(bar(B_KEMPTY0 + s), kTiles);   // one arrival per MMA issuer
             mbar_init(bar(B_VFULL0 + s), 1);
             mbar_init(bar(B_VEMPTY0 + s), kTiles);
-            mbar_init(bar(B_VREADY0 + s), 32);    // the converter warp
+            mbar_init(bar(B_VREADY0 + s), kCvtThreads);    // the converter warpgroup
         }
         for (int g = 0; g < kTiles; ++g) {
             mbar_init(bar(B_SFULL0 + g), 1);
@@ -390,37 +265,40 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 }
             }
         }
-    } else if (warp == kCvtWarp) {
-        // ================= V converter (BF16 inputs only) =================
-        // BF16 V -> FP16 in place (exact for |v| in FP16's normal range, saturating beyond), so that
-        // weights and V share one type; 1024 16-byte chunks per tile over 32 lanes.
+    } else if (warp >= kCvtWarp) {
+        // ================= V converters (BF16 inputs only) =================
+        // BF16 V -> FP16 in place: 1024 16-byte chunks per tile over 128 threads, all eight loads of a
+        // thread in flight before the first conversion.
         if (!f16) {
-            bool ok = true;
+            const int ct = tid - kCvtWarp * 32;
             int n_total = 0;
             for (int it = 0, t = item_at(0); t < a.n_items; ++it, t = item_at(it)) {
                 set_item(t);
                 n_total += n_iter;
             }
-            for (int nv = 0; ok && nv < n_total; ++nv) {
+            for (int nv = 0; nv < n_total; ++nv) {
                 const int st = nv % kStages;
-                if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) break;
                 unsigned char* vt = smem + kOffV + st * kTileBytes;
-#pragma unroll 4
-                for (int q = 0; q < 32; ++q) {
-                    uint4* pch = reinterpret_cast<uint4*>(vt + (lane + 32 * q) * 16);
-                    uint4 v = *pch;
-                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+                uint4 v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    uint32_t* w = reinterpret_cast<uint32_t*>(&v[q]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
                         asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
                     }
-                    *pch = v;
+                    *reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16) = v[q];
                 }
                 fence_async_smem();
                 mbar_arrive(bar(B_VREADY0 + st));
             }
         }
+    } else if (warp == kMmaWarp + kTiles) {
+        // spare warp of the first helper warpgroup: nothing to do
     } else if (warp >= kMmaWarp) {
         // ================= MMA issuers: one warp per query tile =================
         // The whole warp runs the loop and the waits, one elected lane issues the MMAs and commits:
@@ -629,15 +507,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             }
             float mxr;
             {
-                float m0 = fmaxf(s[0], s[1]), m1 = fmaxf(s[2], s[3]), m2 = fmaxf(s[4], s[5]), m3 = fmaxf(s[6], s[7]);
+                float mc[8];                            // three-input maxima, eight independent chains
 #pragma unroll
-                for (int j = 8; j < kBN; j += 8) {     // three-input maxima, four chains
-                    m0 = fmaxf(fmaxf(m0, s[j]), s[j + 1]);
-                    m1 = fmaxf(fmaxf(m1, s[j + 2]), s[j + 3]);
-                    m2 = fmaxf(fmaxf(m2, s[j + 4]), s[j + 5]);
-                    m3 = fmaxf(fmaxf(m3, s[j + 6]), s[j + 7]);
-                }
-                mxr = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                for (int q = 0; q < 8; ++q) mc[q] = fmaxf(s[2 * q], s[2 * q + 1]);
+#pragma unroll
+                for (int j = 16; j < kBN; j += 16)
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) mc[q] = fmaxf(fmaxf(mc[q], s[j + 2 * q]), s[j + 2 * q + 1]);
+                mxr = fmaxf(fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3])), fmaxf(fmaxf(mc[4], mc[5]), fmaxf(mc[6], mc[7])));
             }
             const float mx = mxr * c;                 // c > 0
             const float s_first = s[0] * c;           // the tile below needs it for its last column's stencil
@@ -680,17 +557,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             s_carry = s_first;
             const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m), rho2 = make_float2(rho, rho);
             float2 lsum2 = make_float2(0.0f, 0.0f), lsum2b = make_float2(0.0f, 0.0f);
-            // chunks of 16 keys, highest first (the stencil walks downwards)
+            // chunks of 16 keys, highest first (the stencil walks downwards); the exponentials of the
+            // next chunk are issued before the current chunk's stencil, sum, pack and store, so that the
+            // exponential unit and the arithmetic pipes of this warp work at the same time
+            auto expo16 = [&](int cb, float2 (&P)[9]) {                // p = 2^(c s - m) as pairs (key j, key j + 8)
 #pragma unroll
-            for (int cb = kBN / 16 - 1; cb >= 0; --cb) {
-                float2 P[9];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {          // p = 2^(c s - m) as pairs (key j, key j + 8)
+                for (int e = 0; e < 8; ++e) {
                     const float2 tt = __ffma2_rn(make_float2(s[16 * cb + 2 * e], s[16 * cb + 2 * e + 1]), c2, nm2);
                     const float p0 = ex2(tt.x), p1 = ex2(tt.y);          // keys 2e, 2e+1 of the chunk
                     if (2 * e < 8) { P[2 * e].x = p0; P[2 * e + 1].x = p1; }
                     else { P[2 * e - 8].y = p0; P[2 * e - 7].y = p1; }
                 }
+            };
+            auto store16 = [&](int cb, float2 (&P)[9]) {
                 float2 W[8];
                 if (DIFF) {
                     P[8] = make_float2(P[0].y, nxt);                   // keys 8 and 16 (= first key of the chunk above)
@@ -715,12 +594,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     pk[e] = *reinterpret_cast<uint32_t*>(&h_lo);
                     pk[4 + e] = *reinterpret_cast<uint32_t*>(&h_hi);
                 }
-                if (cb == kBN / 16 - 1 && !pv_done) {
+                tc_st8(tmem_P + 8 * cb, pk);
+            };
+            {
+                float2 Pa[9], Pb[9];
+                expo16(7, Pa);
+                expo16(6, Pb);
+                if (!pv_done) {
                     // the weight columns are still being read by the previous O += W V until it is done
                     if (!mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) ok = false;
                     tc_fence_after();
                 }
-                tc_st8(tmem_P + 8 * cb, pk);
+                store16(7, Pa);
+                expo16(5, Pa);
+                store16(6, Pb);
+                expo16(4, Pb);
+                store16(5, Pa);
+                expo16(3, Pa);
+                store16(4, Pb);
+                expo16(2, Pb);
+                store16(3, Pa);
+                expo16(1, Pa);
+                store16(2, Pb);
+                expo16(0, Pb);
+                store16(1, Pa);
+                store16(0, Pb);
             }
             if (!ok) break;
             lsum2 = __fadd2_rn(lsum2, lsum2b);
@@ -901,22 +799,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 }
 
 // ---- host side ------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
 // [BH][S][64] 16-bit tensor, box = 128 rows x 64 channels of one head, 128-byte swizzle
 bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
     EncodeTiledFn fn = encode_fn();

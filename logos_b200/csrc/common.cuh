@@ -26,6 +26,11 @@ struct logos_ctx {
     int decode_chunk = 0;             // LOGOS_OPT_DECODE_CHUNK: 0 = chosen from the problem size
     int peer_wait_ms = 2000;          // LOGOS_OPT_PEER_WAIT_MS
     bool workspace_locked = false;    // LOGOS_OPT_WORKSPACE_LOCK
+    logos_alloc_fn alloc_fn = nullptr;   // caller's allocator for the workspace (null: cudaMalloc / cudaFree)
+    logos_free_fn free_fn = nullptr;
+    void* alloc_user = nullptr;
+    logos_free_fn ws_free_fn = nullptr;  // how the current workspace block is given back (null: cudaFree)
+    void* ws_free_user = nullptr;
     const void* smem_set[48] = {};    // kernels whose dynamic shared-memory limit this context has raised
     int smem_set_n = 0;
     char err[512] = {0};
@@ -156,7 +161,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // Kernel-side entry points implemented in the other translation units.
 namespace logos {
-int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*, int, int64_t);
+int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*, int, int64_t,
+                const float* absmax_known = nullptr);
+int project(logos_ctx*, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual, void* C,
+            int M, int N, int K);
+int qkv_project(logos_ctx*, int dtype, const void* X, const void* Wt, void* Q, void* K, void* V, int B, int S,
+                int H, int D, float* k_absmax, float* v_absmax);
 int kv_dequantize(logos_ctx*, const int8_t*, int64_t, const float*, float*, int64_t, int, int64_t);
 // pos_bias is added to every pos[b]: -1 appends at len - 1 when `pos` is the length after the append
 int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const float*,

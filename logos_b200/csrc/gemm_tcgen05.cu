@@ -1,0 +1,296 @@
+// gemm_tcgen05.cu -- the projections either side of the attention path as tcgen05 GEMMs.
+//
+// LOGOS projects every head separately: per head and layer three skinny GEMMs [seq x d]·[d x 64]
+// for Q, K, V (cuda/ModelGPU.cu:899-906, through amp_gemm -> cuda_gemm_fp16_fp32out,
+// cuda/MixedPrecision.cuh:301-330, on an FP16 shadow of the weights), then [seq x 64]·[64 x d] per
+// head summed into `concat` (cuda/ModelGPU.cu:974-988) and one [seq x d]·[d x d] for W_proj
+// (cuda/ModelGPU.cu:990-1015).  Here a layer's Q, K, V come from ONE GEMM [M x d]·[d x 3 H 64]
+// whose epilogue writes them straight into the attention engine's [B][H][S][64] layout and, for K
+// and V, reduces max|x| per (sequence, head) tensor -- the first pass of the Nikhilam quantiser
+// (absmax_kernel, cuda/ModelGPU.cu:308-326) -- so the cache can be quantised without re-reading them.
+// The sum over heads of head_out_h·W_O[h] is one GEMM with the heads concatenated along K.
+//
+// C[M][N] = A[M][K] · W, fp32 accumulation.  A is row-major 16-bit (BF16 or FP16).  The weight is
+// kept K-major, Wt[N][K] (a 16-bit shadow made once at load time, like the reference's FP16 shadow,
+// cuda/MixedPrecision.cuh:149-161), so both operands are loaded as 128-byte-swizzled K-major tiles
+// and one MMA covers a 128 x 128 block.  One CTA per 128 x 128 output tile, two CTAs per SM (the
+// epilogue of one overlaps the main loop of the other), 192 threads:
+//   warp 0    TMA producer: A and W tiles of 128 rows x 64 k into a three-stage ring;
+//   warp 1    MMA issuer (one elected lane): four M128 N128 K16 MMAs per stage into 128 TMEM columns;
+//   warps 2-5 epilogue: one thread per output row reads its 128 accumulator columns from TMEM.
+// Every mbarrier wait is bounded; a wait that runs out raises the context's status word.
+#include "tcgen05_ptx.cuh"
+
+namespace logos {
+namespace {
+
+using namespace tc;
+
+constexpr int kGN = 128;                 // output columns per CTA
+constexpr int kGK = 64;                  // k per stage (one 128-byte swizzle atom of 16-bit values)
+constexpr int kGStages = 3;
+constexpr int kGTile = kBM * kGK * 2;    // 16 KiB: one operand tile
+constexpr int kGThreads = 192;
+constexpr int kGOffBar = 2 * kGStages * kGTile;
+constexpr int kGSmem = kGOffBar + (2 * kGStages + 1) * 8 + 64 + 1024;
+
+struct GemmArgs {
+    int M, N, K;
+    int f16;                 // operands are FP16 (else BF16)
+    int mode;                // 0: C row-major (+ residual); 1: Q, K, V scatter
+    // mode 0
+    void* C; const void* R;  // [M][N]; R may be null; same dtype as C
+    int c_is_f32;
+    // mode 1: N = 3 H 64, rows m = b S + s
+    void* q; void* k; void* v;         // [B][H][S][64], 16-bit, operand dtype
+    int S, H;
+    unsigned* k_absmax; unsigned* v_absmax;   // [B][H] float bits (non-negative), atomicMax; may be null
+    int* status;
+};
+
+__device__ __forceinline__ uint32_t pack16(float x, float y, bool f16) {
+    if (f16) { __half2 h = __floats2half2_rn(x, y); return *reinterpret_cast<uint32_t*>(&h); }
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float round16(float x, bool f16) {
+    return f16 ? __half2float(__float2half_rn(x)) : __bfloat162float(__float2bfloat16_rn(x));
+}
+
+__global__ void __launch_bounds__(kGThreads, 2)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const GemmArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + kGOffBar;
+    auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(kGStages + s); };
+    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * kGStages);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kGOffBar + (2 * kGStages + 1) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kGOffBar + (2 * kGStages + 1) * 8 + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kGN, m0 = blockIdx.y * kBM;
+    const int n_kb = (a.K + kGK - 1) / kGK;
+
+    if (warp == 0 && lane == 0) {
+        for (int s = 0; s < kGStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int s = kb % kGStages;
+                if (kb >= kGStages && !mbar_wait(empty(s), ((kb / kGStages) - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(full(s), 2 * kGTile);
+                tma_load_3d(sbase + (2 * s) * kGTile, &mapA, kb * kGK, m0, 0, full(s));
+                tma_load_3d(sbase + (2 * s + 1) * kGTile, &mapW, kb * kGK, n0, 0, full(s));
+            }
+        }
+    } else if (warp == 1) {
+        uint32_t elected;
+        asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(elected));
+        const bool leader = elected != 0;
+        const int fmt = a.f16 ? 0 : 1;
+        const uint32_t idesc = instr_desc(fmt, fmt, 0, kGN);
+        bool ok = true;
+        for (int kb = 0; ok && kb < n_kb; ++kb) {
+            const int s = kb % kGStages;
+            ok = __all_sync(0xffffffffu, mbar_wait(full(s), (kb / kGStages) & 1, abort_flag)) != 0;
+            if (!ok) break;
+            tc_fence_after();
+            if (leader) {
+                const uint32_t sa = sbase + (2 * s) * kGTile, sw = sa + kGTile;
+#pragma unroll
+                for (int kk = 0; kk < kGK / 16; ++kk)
+                    tc_mma_f16(tmem, smem_desc(sa + 32 * kk), smem_desc(sw + 32 * kk), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(empty(s));                    // the stage is free once these MMAs have read it
+                if (kb == n_kb - 1) tc_commit(acc_full);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- epilogue: thread = output row, TMEM lane quarter = warp % 4 ----
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane, m = m0 + row;
+        const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16);
+        const bool f16 = a.f16 != 0;
+        if (mbar_wait(acc_full, 0, abort_flag)) {
+            tc_fence_after();
+            if (a.mode == 0) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < kGN; c0 += 32) {
+                    float v[32];
+                    tc_ld32(t_row + c0, v);
+                    tc_wait_ld();
+                    const int n = n0 + c0;
+                    if (m < a.M && n < a.N) {          // N is a multiple of 32
+                        const size_t off = (size_t)m * a.N + n;
+                        if (a.c_is_f32) {
+                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C) + off);
+                            const float4* res = a.R ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.R) + off) : nullptr;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float4 r4 = res ? res[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                                dst[j] = make_float4(v[4 * j] + r4.x, v[4 * j + 1] + r4.y, v[4 * j + 2] + r4.z, v[4 * j + 3] + r4.w);
+                            }
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.C) + off);
+                            const uint4* res = a.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.R) + off) : nullptr;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint32_t w[4];
+                                uint4 r4 = res ? res[j] : make_uint4(0, 0, 0, 0);
+                                const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r4);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
+                                    if (res) {
+                                        if (f16) {
+                                            float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
+                                            x += rr.x; y += rr.y;
+                                        } else {
+                                            x += __uint_as_float(rw[e] << 16); y += __uint_as_float(rw[e] & 0xffff0000u);
+                                        }
+                                    }
+                                    w[e] = pack16(x, y, f16);
+                                }
+                                dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+            } else {
+                // Q, K, V scatter: the tile's two 64-column groups are two (projection, head) slices
+                const int b = m / a.S, s = m - b * a.S;
+#pragma unroll 1
+                for (int gi = 0; gi < 2; ++gi) {
+                    const int hg = (n0 + 64 * gi) / 64;              // head slot among 3 H
+                    const int which = hg / a.H, h = hg - which * a.H;
+                    float amax = 0.0f;
+                    unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.q : (which == 1 ? a.k : a.v));
+                    const bool live = m < a.M && which < 3;
+                    uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)b * a.H + h) * a.S + s) * 64);
+#pragma unroll 1
+                    for (int hc = 0; hc < 2; ++hc) {
+                        float v[32];
+                        tc_ld32(t_row + 64 * gi + 32 * hc, v);
+                        tc_wait_ld();
+                        if (live) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
+                                    w[e] = pack16(x, y, f16);
+                                    amax = fmaxf(amax, fmaxf(fabsf(round16(x, f16)), fabsf(round16(y, f16))));
+                                }
+                                dst[4 * hc + j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                    // max|x| of the stored (rounded) values per (sequence, head) tensor: one atomic per warp when
+                    // its 32 rows lie in one sequence, else one per row; non-negative floats order like integers
+                    unsigned* tgt = which == 1 ? a.k_absmax : (which == 2 ? a.v_absmax : nullptr);
+                    if (tgt) {
+                        const int b_first = __shfl_sync(0xffffffffu, b, 0), b_last = __shfl_sync(0xffffffffu, b, 31);
+                        const bool all_live = __all_sync(0xffffffffu, live);
+                        if (b_first == b_last && all_live) {
+                            amax = warp_max(amax);
+                            if (lane == 0) atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
+                        } else if (live) {
+                            atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    }
+}
+
+// [rows][K] 16-bit row-major matrix, box = 128 rows x 64 k, 128-byte swizzle
+bool make_map_2d(CUtensorMap* m, const void* base, int rows, int K, bool f16) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, 1};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
+    cuuint32_t box[3] = {(cuuint32_t)kGK, (cuuint32_t)kBM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % 8) != 0 || (a.N % 64) != 0)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "projection: M, N, K = %d, %d, %d (K a multiple of 8, N of 64)", a.M, a.N, a.K);
+    if (!aligned16(A) || !aligned16(Wt))
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "projection: operands must be 16-byte aligned");
+    if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "projection: status word missing");
+    CUtensorMap ma, mw;
+    if (!make_map_2d(&ma, A, a.M, a.K, a.f16 != 0) || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0))
+        return fail(ctx, LOGOS_ERR_CUDA, "projection: cuTensorMapEncodeTiled failed");
+    a.status = ctx->tc_status;
+    if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel, kGSmem)) return rc;
+    dim3 grid((a.N + kGN - 1) / kGN, (a.M + kBM - 1) / kBM);
+    gemm_tc_kernel<<<grid, kGThreads, kGSmem, ctx->stream>>>(ma, mw, a);
+    LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
+    return LOGOS_OK;
+}
+
+}  // namespace
+
+int project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual, void* C,
+            int M, int N, int K) {
+    if (!A || !Wt || !C) return fail(ctx, LOGOS_ERR_INVALID_ARG, "project: null pointer");
+    if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project: operands must be BF16 or FP16");
+    if (out_dtype != dtype && out_dtype != LOGOS_F32) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project: output is the operand type or fp32");
+    if (!aligned16(C) || (residual && !aligned16(residual)) || (N % 64) != 0)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project: C and the residual must be 16-byte aligned, N a multiple of 64");
+    GemmArgs a{};
+    a.M = M; a.N = N; a.K = K; a.f16 = dtype == LOGOS_F16; a.mode = 0;
+    a.C = C; a.R = residual; a.c_is_f32 = out_dtype == LOGOS_F32;
+    return launch_gemm(ctx, A, Wt, a);
+}
+
+int qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt, void* Q, void* K, void* V, int B, int S,
+                int H, int D, float* k_absmax, float* v_absmax) {
+    if (!X || !Wt || !Q || !K || !V || B <= 0 || S <= 0 || H <= 0 || D <= 0)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "qkv_project: bad pointer or extent");
+    if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "qkv_project: operands must be BF16 or FP16");
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V)) return fail(ctx, LOGOS_ERR_ALIGNMENT, "qkv_project: outputs must be 16-byte aligned");
+    if ((k_absmax == nullptr) != (v_absmax == nullptr))
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "qkv_project: the two absmax tables are given together or not at all");
+    if (k_absmax) {
+        LOGOS_CUDA_TRY(ctx, cudaMemsetAsync(k_absmax, 0, sizeof(float) * (size_t)B * H, ctx->stream));
+        LOGOS_CUDA_TRY(ctx, cudaMemsetAsync(v_absmax, 0, sizeof(float) * (size_t)B * H, ctx->stream));
+    }
+    GemmArgs a{};
+    a.M = B * S; a.N = 3 * H * 64; a.K = D; a.f16 = dtype == LOGOS_F16; a.mode = 1;
+    a.q = Q; a.k = K; a.v = V; a.S = S; a.H = H;
+    a.k_absmax = reinterpret_cast<unsigned*>(k_absmax); a.v_absmax = reinterpret_cast<unsigned*>(v_absmax);
+    return launch_gemm(ctx, X, Wt, a);
+}
+
+}  // namespace logos

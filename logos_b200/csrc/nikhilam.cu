@@ -176,20 +176,23 @@ int blocks_for(const logos_ctx* ctx, int64_t work_items, int n_tensors) {
 
 template <typename T>
 int quantize_typed(logos_ctx* ctx, const T* src, int64_t src_stride, int8_t* dst,
-                   int64_t dst_stride, float* scales, int n_tensors, int64_t elems) {
+                   int64_t dst_stride, float* scales, int n_tensors, int64_t elems, const float* absmax_known) {
     bool vec = (elems % 16 == 0) && aligned16(src) && aligned16(dst) &&
                ((src_stride * (int64_t)sizeof(T)) % 16 == 0) && (dst_stride % 16 == 0);
-    float* amax = ctx->absmax_scratch;
-    LOGOS_CUDA_TRY(ctx, cudaMemsetAsync(amax, 0, sizeof(float) * n_tensors, ctx->stream));
+    // the per-tensor max|x|: computed here (first pass over the tensor), or handed in by a producer that
+    // already had every value in its registers (the projection GEMM's epilogue)
+    const float* amax = absmax_known ? absmax_known : ctx->absmax_scratch;
     dim3 grid(blocks_for(ctx, vec ? elems / 16 : elems, n_tensors), n_tensors);
-    if (vec) {
-        absmax_kernel<T, true><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, elems, amax);
+    if (!absmax_known) {
+        LOGOS_CUDA_TRY(ctx, cudaMemsetAsync(ctx->absmax_scratch, 0, sizeof(float) * n_tensors, ctx->stream));
+        if (vec) absmax_kernel<T, true><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, elems, ctx->absmax_scratch);
+        else absmax_kernel<T, false><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, elems, ctx->absmax_scratch);
         LOGOS_LAUNCH_CHECK(ctx, "absmax_kernel");
+    }
+    if (vec) {
         quantize_kernel<T, true><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, dst,
                                                                       dst_stride, amax, scales, elems);
     } else {
-        absmax_kernel<T, false><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, elems, amax);
-        LOGOS_LAUNCH_CHECK(ctx, "absmax_kernel");
         quantize_kernel<T, false><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, dst,
                                                                        dst_stride, amax, scales, elems);
     }
@@ -200,25 +203,25 @@ int quantize_typed(logos_ctx* ctx, const T* src, int64_t src_stride, int8_t* dst
 }  // namespace
 
 int kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride, int8_t* dst,
-                int64_t dst_stride, float* scales, int n_tensors, int64_t elems) {
+                int64_t dst_stride, float* scales, int n_tensors, int64_t elems, const float* absmax_known) {
     if (!src || !dst || !scales || n_tensors <= 0 || elems <= 0 || src_stride < elems ||
         dst_stride < elems)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_quantize: bad pointer, extent or stride");
     if (n_tensors > 65535)
         return fail(ctx, LOGOS_ERR_UNSUPPORTED, "kv_quantize: more than 65535 tensors per call");
-    if (n_tensors > ctx->absmax_slots)
+    if (!absmax_known && n_tensors > ctx->absmax_slots)
         return fail(ctx, LOGOS_ERR_WORKSPACE, "kv_quantize: absmax scratch holds %d tensors",
                     ctx->absmax_slots);
     switch (src_dtype) {
         case LOGOS_F32:
             return quantize_typed(ctx, (const float*)src, src_stride, dst, dst_stride, scales,
-                                  n_tensors, elems);
+                                  n_tensors, elems, absmax_known);
         case LOGOS_BF16:
             return quantize_typed(ctx, (const __nv_bfloat16*)src, src_stride, dst, dst_stride,
-                                  scales, n_tensors, elems);
+                                  scales, n_tensors, elems, absmax_known);
         case LOGOS_F16:
             return quantize_typed(ctx, (const __half*)src, src_stride, dst, dst_stride, scales,
-                                  n_tensors, elems);
+                                  n_tensors, elems, absmax_known);
     }
     return fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_quantize: unknown dtype %d", src_dtype);
 }

@@ -90,6 +90,43 @@ class Engine:
                                                 _ptr(V), _ptr(out), B, H, S, DH, C.byref(params)))
         return out
 
+    # ---- projections -----------------------------------------------------------
+    def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False):
+        """X: [B*S, D] 16-bit; Wt_qkv: [3*H*64, D] (K-major shadow of the stacked W_Q | W_K | W_V) ->
+        Q, K, V [B, H, S, 64] and, with absmax, the tables max|K|, max|V| [B, H] for the quantiser."""
+        D = X.shape[1]
+        assert X.is_contiguous() and Wt_qkv.is_contiguous() and Wt_qkv.shape == (3 * H * 64, D) and X.shape[0] == B * S
+        Q, K, V = (torch.empty((B, H, S, 64), dtype=X.dtype, device=X.device) for _ in range(3))
+        ka = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None
+        va = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None
+        self._check(self.lib.logos_qkv_project(self.h, _DT[X.dtype], _ptr(X), _ptr(Wt_qkv), _ptr(Q), _ptr(K), _ptr(V),
+                                              B, S, H, D, _ptr(ka), _ptr(va)))
+        return (Q, K, V, ka, va) if absmax else (Q, K, V)
+
+    def project(self, A, Wt, residual=None, out_dtype=None, out=None):
+        """A: [M, K] 16-bit, Wt: [N, K] (K-major shadow of W [K, N]) -> A·W (+ residual) [M, N]."""
+        M, K = A.shape
+        N = Wt.shape[0]
+        assert A.is_contiguous() and Wt.is_contiguous() and Wt.shape[1] == K
+        out_dtype = out_dtype or A.dtype
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=A.device)
+        if residual is not None:
+            assert residual.dtype == out.dtype and residual.shape == out.shape and residual.is_contiguous()
+        self._check(self.lib.logos_project(self.h, _DT[A.dtype], _DT[out.dtype], _ptr(A), _ptr(Wt), _ptr(residual),
+                                          _ptr(out), M, N, K))
+        return out
+
+    def nikhilam_compress_absmax(self, x, absmax, cache):
+        """nikhilam_compress of x ([n..., S, DH]) into `cache` ([n, S_max, DH]) when max|x| per tensor is known."""
+        S, DH = x.shape[-2:]
+        n = x.numel() // (S * DH)
+        scales = torch.empty(x.shape[:-2], dtype=torch.float32, device=x.device)
+        self._check(self.lib.logos_kv_quantize_absmax(self.h, _DT[x.dtype], _ptr(x), S * DH, _ptr(cache),
+                                                     cache.shape[-2] * cache.shape[-1], _ptr(absmax), _ptr(scales), n,
+                                                     S * DH))
+        return scales
+
     # ---- Nikhilam INT8 KV ----------------------------------------------------
     def prefill(self, Q, K, V, params: L.Params, k_cache, v_cache, k_scale, v_scale, out_dtype=None, out=None):
         """One layer's prefill in one call: the raw K, V ([B,H,S,DH]) quantised into rows [0, S) of the

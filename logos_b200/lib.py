@@ -21,6 +21,10 @@ OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK = 0, 1
 COMM_HANDLE_BYTES = 80
 
 
+ALLOC_FN = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p)   # logos_alloc_fn
+FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)                                 # logos_free_fn
+
+
 class LogosError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"logos_attn status {status}: {message}")
@@ -51,6 +55,7 @@ SIGNATURES = {
     "logos_ctx_set_stream": (_i, [_vp, _vp]),
     "logos_ctx_reserve": (_i, [_vp, _sz]),
     "logos_ctx_set_workspace": (_i, [_vp, _vp, _sz]),
+    "logos_ctx_set_allocator": (_i, [_vp, _vp, _vp, _vp]),
     "logos_ctx_synchronize": (_i, [_vp]),
     "logos_last_error": (C.c_char_p, [_vp]),
     "logos_ctx_set_option": (_i, [_vp, _i, _i]),
@@ -74,6 +79,9 @@ SIGNATURES = {
     "logos_selftest_umma": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "logos_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_kv_quantize": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _i, _i64]),
+    "logos_kv_quantize_absmax": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i, _i64]),
+    "logos_project": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "logos_qkv_project": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "logos_kv_dequantize": (_i, [_vp, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
     "logos_kv_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_decode_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),

@@ -1,0 +1,79 @@
+"""The tensor-core projection GEMMs (logos_project, logos_qkv_project) against fp64 products of the
+same 16-bit-rounded operands, the Q/K/V scatter into the attention layout, and the epilogue's per-tensor
+max|x| against the quantiser's own first pass (bytes and scales must come out identical)."""
+import numpy as np
+import pytest
+import torch
+
+from logos_b200 import lib as L
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(A, W):
+    return (A.double() @ W.double()).float()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 1024), (300, 1024, 1024), (32, 3072, 1024), (1, 64, 72)])
+def test_project_matches_fp64_product(engine, dtype, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    A = (torch.randn((M, K), device="cuda", generator=g)).to(dtype)
+    W = (torch.randn((K, N), device="cuda", generator=g) * 0.02).to(dtype)
+    Wt = W.t().contiguous()
+    want = _ref(A, W)
+    got = engine.project(A, Wt, out_dtype=torch.float32)
+    engine.synchronize()
+    tol = 2e-5 * K ** 0.5 + 1e-6                         # fp32 accumulation of K products of magnitude ~0.02
+    assert float((got - want).abs().max()) <= tol
+    # 16-bit output with a residual: the rounding of (product + residual)
+    R = torch.randn((M, N), device="cuda", generator=g).to(dtype)
+    got16 = engine.project(A, Wt, residual=R)
+    engine.synchronize()
+    ref16 = (want + R.float()).to(dtype)
+    # the accumulation order differs from the fp64 product, so allow the last bit of the 16-bit result
+    ulp = (ref16.float().abs() * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10)).clamp_min(1e-3)
+    assert bool(((got16.float() - ref16.float()).abs() <= ulp).all())
+    R32 = R.float()
+    got32 = engine.project(A, Wt, residual=R32, out_dtype=torch.float32)
+    engine.synchronize()
+    assert float((got32 - (want + R32)).abs().max()) <= tol + 1e-6
+
+
+@pytest.mark.parametrize("B,S,H,D", [(2, 128, 2, 256), (3, 200, 4, 512), (1, 77, 1, 64), (2, 256, 16, 1024)])
+def test_qkv_project_scatter_and_absmax(engine, B, S, H, D):
+    g = torch.Generator(device="cuda").manual_seed(B * 100 + S)
+    X = torch.randn((B * S, D), device="cuda", generator=g).bfloat16()
+    Wq, Wk, Wv = (torch.randn((H, D, 64), device="cuda", generator=g) * 0.05 for _ in range(3))
+    Wq, Wk, Wv = Wq.bfloat16(), Wk.bfloat16(), Wv.bfloat16()
+    # K-major shadow of the stacked weight: row (which * H + h) * 64 + c = column c of W_which[h]
+    Wt = torch.cat([W.transpose(1, 2).reshape(H * 64, D) for W in (Wq, Wk, Wv)], dim=0).contiguous()
+    Q, K, V, ka, va = engine.qkv_project(X, Wt, B, S, H, absmax=True)
+    engine.synchronize()
+    Xf = X.double().view(B, S, D)
+    for got, W in ((Q, Wq), (K, Wk), (V, Wv)):
+        want = torch.einsum("bsd,hdc->bhsc", Xf, W.double()).float()
+        assert got.shape == (B, H, S, 64)
+        err = (got.float() - want).abs()
+        assert bool((err <= want.abs() * 2.0 ** -7 + 1e-3).all()), float(err.max())
+    # the epilogue's max|x| is the maximum of exactly the stored values
+    assert torch.equal(ka, K.float().abs().amax(dim=(2, 3)))
+    assert torch.equal(va, V.float().abs().amax(dim=(2, 3)))
+    # ... so the cache quantised from it is the one the two-pass quantiser makes
+    S_max = S + 5
+    kc1 = torch.zeros((B, H, S_max, 64), dtype=torch.int8, device="cuda")
+    kc2 = torch.zeros_like(kc1)
+    s1 = engine.nikhilam_compress_absmax(K, ka, kc1.view(B * H, S_max, 64))
+    _, s2 = engine.nikhilam_compress(K, cache=kc2.view(B * H, S_max, 64))
+    engine.synchronize()
+    assert torch.equal(s1, s2) and torch.equal(kc1, kc2)
+
+
+def test_projection_argument_checks(engine):
+    A = torch.zeros((4, 60), device="cuda", dtype=torch.bfloat16)       # K not a multiple of 8
+    Wt = torch.zeros((64, 60), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(L.LogosError):
+        engine.project(A, Wt)
+    A32 = torch.zeros((4, 64), device="cuda")
+    with pytest.raises(KeyError if False else L.LogosError):
+        engine.project(A32, torch.zeros((64, 64), device="cuda"))       # fp32 operands are not taken
