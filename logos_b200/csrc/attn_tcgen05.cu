@@ -14,7 +14,7 @@
 //     visited from the diagonal downwards so that p_{r+1} of the tile above is known.
 //
 // A work item = 256 query rows of one head as two 128-row tiles that share every K/V tile.  The CTA
-// (512 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
+// (384 threads, one per SM) is persistent: it walks its share of the item list, and all barriers and
 // rings run on across items, so one item's epilogue overlaps the other tile's work and the next
 // item's loads.  Roles, one warpgroup each so that registers can be moved between them (setmaxnreg):
 //   warps 0-3 / 4-7  softmax of tile 0 / tile 1, one thread per query row (= TMEM lane) with the
@@ -31,12 +31,12 @@
 //              memory; completion via tcgen05.commit; the scores of the next tile are issued before
 //              the current tile's weights are waited for.  The whole warp runs the loop, one elected
 //              lane issues;
-//   warp 11    spare (a warpgroup is four warps);
-//   warps 12-15  V converters: the MMA takes one type for both operands and the weights are FP16, so for
-//              BF16 inputs every V tile is turned into FP16 in place (exact in FP16's normal range,
-//              saturating beyond), eight 16-byte chunks per thread per tile.  (One warp alone needed
-//              several thousand cycles per tile and set the pace of the kernel; done by the softmax
-//              threads it lengthened their chain by a tenth.)
+//   warp 11    V converter: the MMA takes one type for both operands and the weights are FP16, so for
+//              BF16 inputs this warp turns every V tile into FP16 in place (exact in FP16's normal range,
+//              saturating beyond).  (Measured alternatives, all slower: the softmax threads doing it
+//              lengthened their chain by a tenth; four converter warps in a warpgroup of their own left
+//              the softmax threads 208 registers, 3 %; this warp with more loads in flight took issue
+//              slots and shared-memory bandwidth from the softmax warps of its scheduler in bursts, 5 %.)
 // TMEM (512 columns): S of tile 0 / 1 at [0,128) / [128,256), O at [256,320) / [320,384), FP16
 // weights (two keys per column) at [384,448) / [448,512).
 //
@@ -60,15 +60,15 @@ constexpr int kSoftmaxWarps = 4 * kTiles;   // one warpgroup per query tile, one
 constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps;
 constexpr int kTmaWarp = kSoftmaxWarps;          // then one MMA warp per query tile (the first also owns TMEM)
 constexpr int kMmaWarp = kTmaWarp + 1;
-constexpr int kCvtWarp = kTmaWarp + 4;           // first of the four V converter warps (a warpgroup of their own)
-constexpr int kCvtThreads = 128;
-constexpr int kTcThreads = 32 * (kCvtWarp + 4);
-static_assert(kTcThreads == 512 && kTmaWarp % 4 == 0, "four warpgroups: two of softmax threads, two of helpers");
-// registers per thread after the warpgroups have traded them (the kernel starts with 65536 / 512 = 128):
-// 256 softmax threads x 208 + 256 helper threads x 48 = 65536
+constexpr int kCvtWarp = kMmaWarp + kTiles;      // V converter warp
+constexpr int kCvtThreads = 32;
+constexpr int kTcThreads = 32 * (kCvtWarp + 1);
+static_assert(kTcThreads == 384 && kTmaWarp % 4 == 0, "three warpgroups: two of softmax threads, one of helpers");
+// registers per thread after the warpgroups have traded them (the kernel starts with 65536 / 384 = 168):
+// 256 softmax threads x 224 + 128 helper threads x 56 = 64512
 #ifndef LOGOS_TC_REGS_SOFTMAX
-#define LOGOS_TC_REGS_SOFTMAX 208
-#define LOGOS_TC_REGS_HELPER 48
+#define LOGOS_TC_REGS_SOFTMAX 224
+#define LOGOS_TC_REGS_HELPER 56
 #endif
 constexpr int kRegsSoftmax = LOGOS_TC_REGS_SOFTMAX, kRegsHelper = LOGOS_TC_REGS_HELPER;
 constexpr uint32_t kTmemCols = 256 * kTiles;
@@ -267,8 +267,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         }
     } else if (warp >= kCvtWarp) {
         // ================= V converters (BF16 inputs only) =================
-        // BF16 V -> FP16 in place: 1024 16-byte chunks per tile over 128 threads, all eight loads of a
-        // thread in flight before the first conversion.
+        // BF16 V -> FP16 in place: 1024 16-byte chunks per tile over 32 lanes.
         if (!f16) {
             const int ct = tid - kCvtWarp * 32;
             int n_total = 0;
@@ -280,25 +279,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 const int st = nv % kStages;
                 if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) break;
                 unsigned char* vt = smem + kOffV + st * kTileBytes;
-                uint4 v[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    uint32_t* w = reinterpret_cast<uint32_t*>(&v[q]);
+#pragma unroll 4
+                for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
+                    uint4* pch = reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
+                    uint4 v = *pch;
+                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
                         asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
                     }
-                    *reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16) = v[q];
+                    *pch = v;
                 }
                 fence_async_smem();
                 mbar_arrive(bar(B_VREADY0 + st));
             }
         }
-    } else if (warp == kMmaWarp + kTiles) {
-        // spare warp of the first helper warpgroup: nothing to do
     } else if (warp >= kMmaWarp) {
         // ================= MMA issuers: one warp per query tile =================
         // The whole warp runs the loop and the waits, one elected lane issues the MMAs and commits:
