@@ -48,6 +48,8 @@ def build(force: bool = False) -> None:
     ref_tree = os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
     if os.path.isdir(os.path.join(ref_tree, "include")):
         subprocess.check_call(["make", "-C", HERE, "ref", "refgpu"], stdout=subprocess.DEVNULL)
+        if os.path.exists(os.path.join(HERE, "..", "logos_b200", "liblogos_attn_shim.so")):
+            subprocess.check_call(["make", "-C", HERE, "refmodel"], stdout=subprocess.DEVNULL)
 
 
 @lru_cache(maxsize=None)
@@ -150,6 +152,13 @@ def refgpu():
     L.refgpu_flash_attention_fwd.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int, C.c_float, C.c_int,
                                              C.c_int, C.c_int, C.c_int]
     return L
+
+
+def refmodel(kind: str):
+    """Path of oracle/_ref/refmodel_stock or refmodel_dropin (the reference's ModelGPU::forward as a
+    program), or None when it was not built."""
+    path = os.path.join(HERE, "_ref", f"refmodel_{kind}")
+    return path if os.path.exists(path) else None
 
 
 # ---------------------------------------------------------------- numpy front ends

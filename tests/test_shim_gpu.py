@@ -37,3 +37,22 @@ def test_drop_in_symbol_matches_the_cpu_model(driver, tmp_path, seq, window, str
     p = O.attn_params(0.125, True, window, stride, 0.0, 0.0, 0.0, O.DIFFUSE_NONE)
     want = O.attention_rows(q, k, v, p)
     assert_close(got, want, f"shim seq={seq} window={window}", 2e-5, 1e-5)
+
+
+def test_reference_model_forward_with_the_drop_in_symbol(tmp_path):
+    """The reference's ModelGPU::forward (cuda/ModelGPU.cu, compiled unchanged) on a small seeded model,
+    once with the reference's own cuda_flash_attention_fwd and once linked against liblogos_attn_shim.so
+    (the reference's definition renamed away at compile time of cuda/VedicGEMM.cu): the logits agree.
+    Shunyam is active (seq > window), so the drop-in also has to honour window and stride."""
+    stock, dropin = O.refmodel("stock"), O.refmodel("dropin")
+    if stock is None or dropin is None:
+        pytest.skip("oracle/_ref/refmodel_* were not built (reference tree absent at build time)")
+    args = ["96", "128", "2", "2", "150", "32", "8"]          # vocab d_model heads layers seq window stride
+    env = dict(os.environ, LD_LIBRARY_PATH=PKG + ":" + os.environ.get("LD_LIBRARY_PATH", ""))
+    outs = []
+    for exe, name in ((stock, "stock.bin"), (dropin, "dropin.bin")):
+        res = subprocess.run([exe, str(tmp_path / name), *args], capture_output=True, text=True, timeout=300, env=env)
+        assert res.returncode == 0, res.stderr[-2000:]
+        outs.append(np.fromfile(str(tmp_path / name), dtype=np.float32).reshape(150, 96))
+    assert np.isfinite(outs[0]).all() and np.abs(outs[0]).max() > 1e-3
+    assert_close(outs[1], outs[0], "logits with the drop-in symbol vs the reference's own kernel", 2e-4, 1e-4)
