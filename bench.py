@@ -410,6 +410,35 @@ def measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks, layers=1
                 "note": "decode attention reads ~200 scattered rows per pair: latency-bound, not a bandwidth figure"}}
 
 
+def measure_projection(eng, dev, batch, steps, warmup) -> dict:
+    """The fused Q/K/V projection of configuration 5's prefill alone: [batch * 2048, 1024] x [1024, 3072] BF16
+    with the scatter into [B][H][S][64] and the quantiser's max|x| in the epilogue."""
+    import torch
+    S, D, Hh = 2048, 1024, H
+    g = torch.Generator(device=dev).manual_seed(77)
+    X = torch.randn((batch * S, D), device=dev, generator=g).bfloat16()
+    Wt = (torch.randn((3 * Hh * DH, D), device=dev, generator=g) * 0.02).bfloat16()
+    for _ in range(warmup):
+        eng.qkv_project(X, Wt, batch, S, Hh, absmax=True)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(steps):
+        Q, K, V, ka, va = eng.qkv_project(X, Wt, batch, S, Hh, absmax=True)
+    ev[1].record()
+    eng.synchronize()
+    ms = ev[0].elapsed_time(ev[1]) / steps
+    flops = 2.0 * batch * S * D * 3 * Hh * DH
+    # spot check against an fp64 product of the same BF16 operands
+    rows = torch.tensor([0, 1, S - 1, batch * S - 1], device=dev)
+    want = (X[rows].double() @ Wt[Hh * DH:Hh * DH + DH].double().t()).float()          # K of head 0
+    got = torch.stack([K[int(r) // S, 0, int(r) % S].float() for r in rows])
+    peaks = measured_peaks()
+    return {"workload": f"qkv_projection_m{batch * S}_n{3 * Hh * DH}_k{D}_bf16", "ms_per_step": ms,
+            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "bound": "tensor", "peak": peaks["tensor"],
+            "peak_kind": peaks["kind"] + " burst", "frac": flops / (ms * 1e-3) / 1e12 / peaks["tensor"],
+            "max_abs_err_vs_fp64_product": float((got - want).abs().max())}
+
+
 def reference_gpu_kernels(eng, dev) -> list:
     """One head of the prefill and of the window configuration through the reference's own CUDA path
     (ns_advect_kernel + ns_diffuse_kernel + cuda_flash_attention_fwd, compiled unmodified for sm_100a)
@@ -520,6 +549,17 @@ def run_ours(args) -> None:
         eng.close()
         if world > 1:
             dist.destroy_process_group()
+
+    if args.workload == "qkv":
+        r = measure_projection(eng, dev, args.batch if args.batch != 64 else 32, args.steps, args.warmup)
+        print(json.dumps({"metric": r["workload"], "value": r["value"], "unit": r["unit"], "n_gpus": 1, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": {"workload": r["workload"]},
+                          "max_abs_err_vs_fp64_product": r["max_abs_err_vs_fp64_product"],
+                          "roofline": {"bound": "tensor", "achieved": r["value"], "peak": r["peak"], "peak_kind": r["peak_kind"],
+                                       "frac": r["frac"], "traffic": None}, "gpu_launches": args.steps}))
+        finish()
+        return
 
     if args.workload == "stack":
         r = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
@@ -687,6 +727,8 @@ def run_ours(args) -> None:
                              for cfg in (PREFILL, PREFILL_8K, WINDOW, WINDOW_LM)]
         torch.cuda.empty_cache()
         line["stack"] = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
+        if world == 1:
+            line["secondary"].append(measure_projection(eng, dev, 32, 5, 3))
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["baselines"] = {"reference_gpu_kernels_on_this_gpu": reference_gpu_kernels(eng, dev),
                              "configuration_1_reference_cpu_forward": configuration1_cpu_baseline()}
@@ -706,7 +748,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU legs and the reference's GPU kernels")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack", "qkv"],
                     help="decode is the benchmark; the others time one attention kernel alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")
