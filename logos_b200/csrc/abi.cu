@@ -244,15 +244,12 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: bad parameter block");
     if (!logos::dtype_ok(in_dtype) || !logos::dtype_ok(out_dtype))
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: unknown dtype");
-    // Shunyam with landmarks: the gather kernel.  Everything else the tensor-core kernel takes, a pure
-    // window included (measured 8 % faster there than the gather kernel at 8192 tokens); the gather
-    // kernel keeps the pure-window shapes the tensor-core kernel declines.
-    const bool win_ok = !ctx->force_general && logos::attention_window_eligible(in_dtype, out_dtype, DH, params, S);
-    if (win_ok && params->stride > 0)
-        return logos::attention_window(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+    // What the tensor-core kernel takes (causal, Shunyam window with or without landmarks) goes there; the
+    // gather kernel keeps the Shunyam shapes it declines (viscosity above 1/2); everything else is fp32 SIMT.
     if (!ctx->force_general && logos::attention_tc_eligible(in_dtype, out_dtype, DH, params, S))
         return logos::attention_tc(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
-    if (win_ok) return logos::attention_window(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+    if (!ctx->force_general && logos::attention_window_eligible(in_dtype, out_dtype, DH, params, S))
+        return logos::attention_window(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
     return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
 }
 

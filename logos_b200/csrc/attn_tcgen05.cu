@@ -80,8 +80,9 @@ constexpr int kOffQ = 0;                                       // two buffers (w
 constexpr int kQBufBytes = 2 * kTiles * kTileBytes;
 constexpr int kOffK = kOffQ + 2 * kQBufBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffBar = kOffV + kStages * kTileBytes;
-constexpr int kNumBars = 8 + 5 * kStages + 8;
+constexpr int kOffVP = kOffV + kStages * kTileBytes;           // one tile: the V[j-1] rows of a landmark tile (landmark kernels only)
+constexpr int kOffBar = kOffVP + kTileBytes;
+constexpr int kNumBars = 8 + 5 * kStages + 8 + 1;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
 enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buffer
@@ -90,6 +91,7 @@ enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buf
            B_KFULL0 = 8, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
            B_VEMPTY0 = B_VFULL0 + kStages, B_VREADY0 = B_VEMPTY0 + kStages,
            B_SFULL0 = B_VREADY0 + kStages, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
+           B_VPEMPTY,                                      // the V[j-1] buffer has been mixed into its V tile
            B_NUM };
 static_assert(B_NUM <= kNumBars, "barrier count");
 
@@ -99,16 +101,25 @@ struct TcArgs {
     float c;            // scale * log2(e)
     float eta, nu;
     int diffuse;        // 0 none, 1 causal
-    int window;         // > 0: sliding window active (pure window, no landmarks)
+    int window;         // > 0: sliding window active
+    int stride;         // > 0: every key j % stride == 0 below the window is visible too (landmark kernels)
     int n_qb, BH, n_items;   // query blocks per head, heads, work items = n_qb * BH
     int* status;        // device word: non-zero = a wait ran out
 };
 
 // -------------------------------------------------------------------------------------
-template <bool DIFF>
+// LM: Shunyam landmarks.  After an item's window tiles come its landmark tiles: 128 landmarks m = 128 lt ... at
+// keys m * stride, gathered by TMA through strided views of K and V (mapKl, mapVl: row pitch = stride rows).
+// They are ordinary key tiles for QK^T, softmax and PV, except that (i) the mask is "key strictly below the
+// row's window", (ii) neighbouring landmarks are not neighbouring keys, so the diffusion stencil cannot sit on
+// the weights: the converter warp mixes the landmark's V row with the row before it (mapVp: the same view
+// one row earlier) into V[j] + rho V[j-1] -- the same "everything divided by 1 - nu" units as the window
+// part -- and the row sum takes (1 + rho) p.
+template <bool DIFF, bool LM>
 __global__ void __launch_bounds__(kTcThreads, kCtasPerSm)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                  const __grid_constant__ CUtensorMap mapV, const TcArgs a) {
+                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapKl,
+                  const __grid_constant__ CUtensorMap mapVl, const __grid_constant__ CUtensorMap mapVp, const TcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -132,7 +143,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
     // part in iterations [first_iter(g), last_iter(g)]: above its diagonal and below its window it has
     // nothing to do.
     int qb = 0, bh = 0, q0 = 0, jt_hi = 0, jt_top0 = 0, jt_top1 = 0, jt_bot0 = 0, jt_bot1 = 0, n_iter = 0;
+    int n_win = 0, n_lt0 = 0, n_lt1 = 0;     // window iterations; landmark tiles each query tile needs
     bool tile1_live = false;
+    // landmark tiles whose first landmark lies strictly below the window of row i_last
+    auto lm_tiles = [&](int i_last) {
+        const int top = i_last - a.window - 1;                 // highest key a landmark of this row may have
+        return top < 0 ? 0 : (top / a.stride + 1 + kBN - 1) / kBN;
+    };
     auto set_item = [&](int t) {
         qb = a.n_qb - 1 - t / a.BH;
         bh = t % a.BH;
@@ -145,15 +162,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         jt_bot0 = (a.window > 0) ? max(0, q0 - a.window - 1) / kBN : 0;
         jt_bot1 = (a.window > 0) ? max(0, q0 + kBM - a.window - 1) / kBN : 0;
         const int jt_lo = kTiles == 2 ? min(jt_bot0, jt_bot1) : jt_bot0;
-        n_iter = jt_hi - jt_lo + 1;
+        n_win = jt_hi - jt_lo + 1;
         tile1_live = kTiles == 2 && (q0 + kBM) < S;   // query tile 1 may lie wholly beyond the sequence
+        if (LM) {
+            n_lt0 = lm_tiles(min(q0 + kBM, S) - 1);
+            n_lt1 = tile1_live ? lm_tiles(min(q0 + kBQ, S) - 1) : 0;
+        }
+        n_iter = n_win + (LM ? max(n_lt0, n_lt1) : 0);
     };
+    // iteration i of an item: i < n_win visits KV tile jt_hi - i, the others landmark tile i - n_win
     auto active = [&](int g, int i) {
+        if (LM && i >= n_win) return (i - n_win) < (g == 0 ? n_lt0 : n_lt1);
         const int jt = jt_hi - i;
         return g == 0 ? (jt <= jt_top0 && jt >= jt_bot0) : (tile1_live && jt <= jt_top1 && jt >= jt_bot1);
     };
-    auto first_iter = [&](int g) { return jt_hi - (g == 0 ? jt_top0 : jt_top1); };
-    auto last_iter = [&](int g) { return (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1; };
     // Items are sorted by length, so the CTAs take them in snake order: round r hands items r G ...
     // r G + G - 1 to CTAs 0 ... G - 1 in even rounds and G - 1 ... 0 in odd ones.  For the causal
     // shapes the longest CTA is then within 2 % of the mean (plain round-robin: 14 %).
@@ -169,6 +191,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             tma_load_3d(dst, &mapQ, 0, q0 + g * kBM, bh, bar(B_QLOAD0 + qsel));
             if (has_lo) tma_load_3d(dst + kTileBytes, &mapQ, 0, q0 + g * kBM - 1, bh, bar(B_QLOAD0 + qsel));
         }
+    };
+
+    // K or V tile of iteration i into ring stage st: a window tile, or a landmark tile through the strided views
+    auto load_k_tile = [&](int i, int st) {
+        mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
+        if (LM && i >= n_win) tma_load_3d(sbase + kOffK + st * kTileBytes, &mapKl, 0, (i - n_win) * kBN, bh, bar(B_KFULL0 + st));
+        else tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, (jt_hi - i) * kBN, bh, bar(B_KFULL0 + st));
+    };
+    int n_vp = 0;       // V[j-1] tiles requested so far (the buffer is single: wait until the last one was mixed)
+    auto load_v_tile = [&](int i, int st) -> bool {
+        if (LM && i >= n_win) {
+            const int m0 = (i - n_win) * kBN;
+            if (DIFF) {
+                if (n_vp > 0 && !mbar_wait(bar(B_VPEMPTY), (n_vp - 1) & 1, abort_flag)) return false;
+                ++n_vp;
+                mbar_expect_tx(bar(B_VFULL0 + st), 2 * kTileBytes);
+                tma_load_3d(sbase + kOffVP, &mapVp, 0, m0 - 1, bh, bar(B_VFULL0 + st));   // row -1 of the first tile: zeros
+            } else {
+                mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
+            }
+            tma_load_3d(sbase + kOffV + st * kTileBytes, &mapVl, 0, m0, bh, bar(B_VFULL0 + st));
+        } else {
+            mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
+            tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, (jt_hi - i) * kBN, bh, bar(B_VFULL0 + st));
+        }
+        return true;
     };
 
     if (warp == kTmaWarp && lane == 0) {   // the producer sets the barriers up, so that its first loads can go out at once
@@ -190,6 +238,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mbar_init(bar(B_PFULL0 + g), kBM);
             mbar_init(bar(B_PVDONE0 + g), 1);
         }
+        mbar_init(bar(B_VPEMPTY), kCvtThreads);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -200,15 +249,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         set_item(item_at(0));
         if (lane == 0) {
             load_q(0);
-            for (int i = 0; i < min(kStages, n_iter); ++i) {
-                mbar_expect_tx(bar(B_KFULL0 + i), kTileBytes);
-                tma_load_3d(sbase + kOffK + i * kTileBytes, &mapK, 0, (jt_hi - i) * kBN, bh, bar(B_KFULL0 + i));
-            }
+            for (int i = 0; i < min(kStages, n_iter); ++i) load_k_tile(i, i);
         } else if (lane == 1) {
-            for (int i = 0; i < min(kStages, n_iter); ++i) {
-                mbar_expect_tx(bar(B_VFULL0 + i), kTileBytes);
-                tma_load_3d(sbase + kOffV + i * kTileBytes, &mapV, 0, (jt_hi - i) * kBN, bh, bar(B_VFULL0 + i));
-            }
+            for (int i = 0; i < min(kStages, n_iter); ++i) load_v_tile(i, i);
         }
     }
     if (warp == kMmaWarp) {   // TMEM allocation is warp-wide; this warp also frees it
@@ -244,10 +287,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 }
                 for (int i = 0; i < n_iter; ++i, ++nk) {
                     if (it == 0 && i < kStages) continue;
-                    const int st = nk % kStages, jt = jt_hi - i;
+                    const int st = nk % kStages;
                     if (nk >= kStages && !mbar_wait(bar(B_KEMPTY0 + st), ((nk / kStages) - 1) & 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(bar(B_KFULL0 + st), kTileBytes);
-                    tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, jt * kBN, bh, bar(B_KFULL0 + st));
+                    load_k_tile(i, st);
                 }
             }
         } else if (lane == 1) {
@@ -258,41 +300,71 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 set_item(t);
                 for (int i = 0; i < n_iter; ++i, ++nv) {
                     if (it == 0 && i < kStages) continue;
-                    const int st = nv % kStages, jt = jt_hi - i;
+                    const int st = nv % kStages;
                     if (nv >= kStages && !mbar_wait(bar(B_VEMPTY0 + st), ((nv / kStages) - 1) & 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
-                    tma_load_3d(sbase + kOffV + st * kTileBytes, &mapV, 0, jt * kBN, bh, bar(B_VFULL0 + st));
+                    if (!load_v_tile(i, st)) { ok = false; break; }
                 }
             }
         }
     } else if (warp >= kCvtWarp) {
-        // ================= V converters (BF16 inputs only) =================
-        // BF16 V -> FP16 in place: 1024 16-byte chunks per tile over 32 lanes.
-        if (!f16) {
+        // ================= V converter =================
+        // BF16 V -> FP16 in place (BF16 inputs), 1024 16-byte chunks per tile over 32 lanes; and for a
+        // landmark tile under diffusion the mix V[j] + rho V[j-1] of the gathered rows with the rows
+        // before them (FP16 out, whatever the input type).
+        if (!f16 || (LM && DIFF)) {
             const int ct = tid - kCvtWarp * 32;
-            int n_total = 0;
-            for (int it = 0, t = item_at(0); t < a.n_items; ++it, t = item_at(it)) {
+            const float rho_c = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;
+            int nv = 0;
+            bool ok = true;
+            for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
                 set_item(t);
-                n_total += n_iter;
-            }
-            for (int nv = 0; nv < n_total; ++nv) {
-                const int st = nv % kStages;
-                if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) break;
-                unsigned char* vt = smem + kOffV + st * kTileBytes;
-#pragma unroll 4
-                for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
-                    uint4* pch = reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
-                    uint4 v = *pch;
-                    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+                for (int i = 0; ok && i < n_iter; ++i, ++nv) {
+                    const int st = nv % kStages;
+                    if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) { ok = false; break; }
+                    unsigned char* vt = smem + kOffV + st * kTileBytes;
+                    if (LM && DIFF && i >= n_win) {
+                        const unsigned char* vp = smem + kOffVP;
+                        const bool first_tile = i == n_win;          // its row 0 is key 0: V_s[0] = V[0]
+#pragma unroll 2
+                        for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
+                            const int ch = ct + kCvtThreads * q;      // chunks 0..7 are row 0
+                            uint4 v = *reinterpret_cast<uint4*>(vt + ch * 16);
+                            uint4 pv = (first_tile && ch < 8) ? v : *reinterpret_cast<const uint4*>(vp + ch * 16);
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+                            const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
-                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                            for (int e = 0; e < 4; ++e) {
+                                float2 x, y;
+                                if (f16) {
+                                    x = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                                    y = __half22float2(*reinterpret_cast<const __half2*>(&pw[e]));
+                                } else {
+                                    x = make_float2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                                    y = make_float2(__uint_as_float(pw[e] << 16), __uint_as_float(pw[e] & 0xffff0000u));
+                                }
+                                const float lo = fmaf(rho_c, y.x, x.x), hi = fmaf(rho_c, y.y, x.y);
+                                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                            }
+                            *reinterpret_cast<uint4*>(vt + ch * 16) = v;
+                        }
+                        mbar_arrive(bar(B_VPEMPTY));
+                    } else if (!f16) {
+#pragma unroll 4
+                        for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
+                            uint4* pch = reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
+                            uint4 v = *pch;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                            }
+                            *pch = v;
+                        }
                     }
-                    *pch = v;
+                    fence_async_smem();
+                    mbar_arrive(bar(B_VREADY0 + st));
                 }
-                fence_async_smem();
-                mbar_arrive(bar(B_VREADY0 + st));
             }
         }
     } else if (warp >= kMmaWarp) {
@@ -319,16 +391,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const uint32_t a_p = tmem + kColP + (uint32_t)g * 64u;
             const uint32_t k_lo0 = lo_of(sbase + kOffK), v_lo0 = lo_of(sbase + kOffV);
             const uint32_t d_s = tmem + (uint32_t)g * 128u, d_o = tmem + kColO + (uint32_t)g * 64u;
-            const int v_bar = f16 ? B_VFULL0 : B_VREADY0;
+            const int v_bar = (f16 && !(LM && DIFF)) ? B_VFULL0 : B_VREADY0;   // tiles the converter has (not) to touch
             // running counters: K / V tiles taken from the rings, score tiles and products issued
             int nt_qk = 0, nt_pv = 0, s_qk = 0, s_pv = 0;
-            int it_first = 0, it_last = -1;
+            int k_item = 0;      // products of this tile issued so far in the item (the first one overwrites O)
             uint32_t qhi_lo = 0, qlo_lo = 0;
 
             auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
                 const int st = nt_qk % kStages;
                 if (!wait_w(bar(B_KFULL0 + st), (nt_qk / kStages) & 1)) return false;
-                if (i >= it_first && i <= it_last) {
+                if (active(g, i)) {
                     // the previous scores of this tile (of this item or the one before) must have left TMEM
                     if (s_qk > 0 && !wait_w(bar(B_SEMPTY0 + g), (s_qk - 1) & 1)) return false;
                     tc_fence_after();
@@ -349,8 +421,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 return true;
             };
             auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
-                const int st = nt_pv % kStages, k = i - it_first;
-                if (i >= it_first && i <= it_last) {
+                const int st = nt_pv % kStages, k = k_item;
+                if (active(g, i)) {
+                    ++k_item;
                     if (!wait_w(bar(B_PFULL0 + g), s_pv & 1)) return false;
                     if (!wait_w(bar(v_bar + st), (nt_pv / kStages) & 1)) return false;
                     tc_fence_after();
@@ -378,8 +451,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
                 set_item(t);
                 const int qsel = it & 1;
-                it_first = first_iter(g);
-                it_last = last_iter(g);
+                k_item = 0;
                 qhi_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes);
                 qlo_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g + 1) * kTileBytes);
                 ok = wait_w(bar(B_QREADY0 + 2 * qsel + g), (it >> 1) & 1);   // this tile's Q_adv is in place
@@ -472,11 +544,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         float m_run = -INFINITY;     // running reference maximum (log2 domain)
         float l_run = 0.0f;          // running sum of the row's weights
         float s_carry = -INFINITY;   // scaled score of the first key of the tile above (for the stencil)
-        int k_last = -1;
+        int k_last = -1, k_cnt = 0;  // index of the last / number of the iterations this tile has taken part in
 
         for (int i = 0; ok && i < n_iter; ++i) {
             if (!active(g, i)) continue;
-            const int k = i - first_iter(g), jt = jt_hi - i, k0 = jt * kBN;
+            const bool lm = LM && i >= n_win;                 // a landmark tile: keys (i - n_win) * 128 ... times stride
+            const int k = k_cnt++, jt = jt_hi - i, k0 = lm ? (i - n_win) * kBN : jt * kBN;   // first key / landmark of the tile
             k_last = k;
             if (!mbar_wait(bar(B_SFULL0 + g), s_run & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -492,12 +565,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mbar_arrive(bar(B_SEMPTY0 + g));
 
             const int r_first = q0 + g * kBM;
-            const bool edge = (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
+            const bool edge = lm || (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
                               (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
             if (edge) {
-                // visible columns of the row, relative to the tile's first key: [lo_rel, hi_rel]
-                const int hi_rel = min(i_glob, S - 1) - k0;
-                const int lo_rel = (a.window > 0) ? i_glob - a.window - k0 : -(1 << 30);
+                // visible columns of the row, relative to the tile's first key: [lo_rel, hi_rel]; in a landmark
+                // tile column c is key (k0 + c) * stride, visible when it lies strictly below the row's window
+                int hi_rel = min(i_glob, S - 1) - k0;
+                int lo_rel = (a.window > 0) ? i_glob - a.window - k0 : -(1 << 30);
+                if (lm) {
+                    const int top = i_glob - a.window - 1;
+                    hi_rel = (top < 0 ? -1 : top / a.stride) - k0;
+                    lo_rel = -(1 << 30);
+                }
 #pragma unroll
                 for (int j = 0; j < kBN; ++j) s[j] = (j <= hi_rel && j >= lo_rel) ? s[j] : -INFINITY;
             }
@@ -549,8 +628,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             // Arithmetic runs on packed pairs (key k, key k + 8) of a 16-key chunk so that the
             // neighbour pair of the stencil is again a register pair.  The row sum is taken before
             // the FP16 rounding: the two differ by at most 2^-12 relative, far inside the tolerance.
-            float nxt = DIFF ? ex2(s_carry + neg_m) : 0.0f;             // -inf gives 0
-            s_carry = s_first;
+            const bool stencil = DIFF && !lm;                           // landmarks: the mix sits in their V tile instead
+            float nxt = stencil ? ex2(s_carry + neg_m) : 0.0f;          // -inf gives 0
+            if (!lm) s_carry = s_first;
             const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m), rho2 = make_float2(rho, rho);
             float2 lsum2 = make_float2(0.0f, 0.0f), lsum2b = make_float2(0.0f, 0.0f);
             // chunks of 16 keys, highest first (the stencil walks downwards); the exponentials of the
@@ -567,7 +647,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             };
             auto store16 = [&](int cb, float2 (&P)[9]) {
                 float2 W[8];
-                if (DIFF) {
+                if (DIFF && (!LM || stencil)) {
                     P[8] = make_float2(P[0].y, nxt);                   // keys 8 and 16 (= first key of the chunk above)
                     nxt = P[0].x;
 #pragma unroll
@@ -618,7 +698,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             }
             if (!ok) break;
             lsum2 = __fadd2_rn(lsum2, lsum2b);
-            l_run += lsum2.x + lsum2.y;
+            // a landmark's weight stands for V[j] + rho V[j-1]: it counts (1 + rho) times in the row sum
+            l_run += (lsum2.x + lsum2.y) * ((LM && DIFF && lm) ? 1.0f + rho : 1.0f);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(B_PFULL0 + g));
@@ -796,11 +877,13 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 
 // ---- host side ------------------------------------------------------------------------
 // [BH][S][64] 16-bit tensor, box = 128 rows x 64 channels of one head, 128-byte swizzle
-bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
+// `rows` rows per head taken every `pitch` rows from `base` (pitch 1: the plain tensor; pitch = the landmark
+// stride: the strided view whose row m is key m * stride of the head)
+bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16, int rows = -1, int pitch = 1) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
-    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)S, (cuuint64_t)BH};
-    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)S * kD * 2};
+    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)(rows < 0 ? S : rows), (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)kD * 2 * pitch, (cuuint64_t)S * kD * 2};
     cuuint32_t box[3] = {(cuuint32_t)kD, (cuuint32_t)kBM, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
@@ -836,7 +919,6 @@ bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn
     if (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CENTRAL) return false;
     // the diffusion weights are carried with a factor 1 / (1 - nu): keep them inside FP16
     if (ns_any && (p->ns_nu < 0.0f || p->ns_nu > 0.5f)) return false;
-    if (shunyam_active(p->window, S) && p->stride > 0) return false;  // landmarks: general kernel
     return true;
 }
 
@@ -848,9 +930,20 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
         return fail(ctx, LOGOS_ERR_ALIGNMENT, "attention: tensors must be 16-byte aligned");
     if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "attention: status word missing");
     const bool f16 = in_dtype == LOGOS_F16;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mkl, mvl, mvp;
     if (!make_map(&mq, Q, BH, S, f16) || !make_map(&mk, K, BH, S, f16) || !make_map(&mv, V, BH, S, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed");
+    // Shunyam landmarks: strided views of K and V (row m = key m * stride) and of V one row earlier
+    // (row m = key (m + 1) * stride - 1, read at m - 1); each view ends inside its head's rows
+    const int lm_stride = (shunyam_active(p->window, S) && p->stride > 0) ? p->stride : 0;
+    mkl = mk; mvl = mv; mvp = mv;
+    if (lm_stride) {
+        const int n_lm = (S + lm_stride - 1) / lm_stride, n_prev = S / lm_stride;
+        const unsigned char* v_prev = reinterpret_cast<const unsigned char*>(V) + (size_t)(lm_stride - 1) * kD * 2;
+        if (!make_map(&mkl, K, BH, S, f16, n_lm, lm_stride) || !make_map(&mvl, V, BH, S, f16, n_lm, lm_stride) ||
+            !make_map(&mvp, n_prev > 0 ? v_prev : V, BH, S, f16, n_prev > 0 ? n_prev : 1, lm_stride))
+            return fail(ctx, LOGOS_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed for the landmark views");
+    }
     const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
     TcArgs a;
     a.O = O; a.S = S;
@@ -861,18 +954,22 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     a.nu = ns_any ? p->ns_nu : 0.0f;
     a.diffuse = (ns_any && p->diffuse_mode == LOGOS_DIFFUSE_CAUSAL) ? 1 : 0;
     a.window = shunyam_active(p->window, S) ? p->window : 0;
+    a.stride = lm_stride;
     a.status = ctx->tc_status;
     a.n_qb = (S + kBQ - 1) / kBQ;
     a.BH = BH;
     a.n_items = a.n_qb * BH;
     dim3 grid(a.n_items < ctx->sm_count ? a.n_items : ctx->sm_count);   // persistent: one CTA per SM
-    if (a.diffuse) {
-        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<true>, kSmemBytes)) return rc;
-        prefill_tc_kernel<true><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
-    } else {
-        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<false>, kSmemBytes)) return rc;
-        prefill_tc_kernel<false><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, a);
-    }
+#define LOGOS_LAUNCH_TC(DIFF_, LM_)                                                                             \
+    do {                                                                                                        \
+        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<DIFF_, LM_>, kSmemBytes)) return rc;              \
+        prefill_tc_kernel<DIFF_, LM_><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mkl, mvl, mvp, a); \
+    } while (0)
+    if (a.diffuse && lm_stride) LOGOS_LAUNCH_TC(true, true);
+    else if (a.diffuse) LOGOS_LAUNCH_TC(true, false);
+    else if (lm_stride) LOGOS_LAUNCH_TC(false, true);
+    else LOGOS_LAUNCH_TC(false, false);
+#undef LOGOS_LAUNCH_TC
     LOGOS_LAUNCH_CHECK(ctx, "prefill_tc_kernel");
     return LOGOS_OK;
 }

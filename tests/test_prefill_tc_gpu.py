@@ -71,6 +71,21 @@ def test_window_with_landmarks(engine, engine_general, S, dtype):
         run(engine, engine_general, 1, 2, S, dtype, case, 70 + n, outliers=(n == 0))
 
 
+def test_gather_kernel_keeps_the_shapes_the_tensor_core_kernel_declines(engine, engine_general):
+    """Viscosity above 1/2 is outside the tcgen05 kernel's FP16 weight range: Shunyam shapes then run on the
+    mma.sync gather kernel (window + landmark tiles), everything else on the fp32 kernel."""
+    run(engine, engine_general, 1, 2, 700, torch.bfloat16, (64, 0.1, 0.6, L.DIFFUSE_CAUSAL, 16), 90)
+    run(engine, engine_general, 1, 2, 300, torch.float16, (16, 0.1, 0.7, L.DIFFUSE_CAUSAL, 0), 91)
+
+
+@pytest.mark.parametrize("S,stride", [(2500, 16), (2500, 3), (4096, 64), (1500, 1)])
+def test_landmarks_over_many_tiles(engine, engine_general, S, stride):
+    """Several landmark tiles per work item (more than 128 landmarks), strides that do and do not divide the
+    tile size, stride 1 (every key a landmark: full causal attention)."""
+    run(engine, engine_general, 1, 2, S, torch.bfloat16, (64, 0.1, 0.05, L.DIFFUSE_CAUSAL, stride), 95, outliers=True)
+    run(engine, engine_general, 1, 1, S, torch.float16, (32, 0.0, 0.0, L.DIFFUSE_NONE, stride), 96)
+
+
 def test_outlier_keys_long_sequence(engine, engine_general):
     # 1 % of K entries x8: large score spread, the lazy re-scaling of O must still be exact enough
     run(engine, engine_general, 1, 2, 1024, torch.bfloat16, CASES[1], 50, outliers=True)
