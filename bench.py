@@ -358,8 +358,6 @@ def measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks, layers=1
     for _ in range(steps):
         gids.copy_(tok)
         graph.replay()
-        if comm is not None:
-            comm.steps += layers                       # one exchange per layer inside the replayed step
         tok = glogits.argmax(dim=1)
     ev[1].record()
     barrier()

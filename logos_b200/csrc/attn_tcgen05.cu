@@ -311,7 +311,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         // BF16 V -> FP16 in place (BF16 inputs), 1024 16-byte chunks per tile over 32 lanes; and for a
         // landmark tile under diffusion the mix V[j] + rho V[j-1] of the gathered rows with the rows
         // before them (FP16 out, whatever the input type).
-        if (!f16 || (LM && DIFF)) {
+        if (!LM) {
+            // without landmarks every tile is treated alike: one flat loop over all the CTA's tiles
+            if (!f16) {
+                const int ct = tid - kCvtWarp * 32;
+                int n_total = 0;
+                for (int it = 0, t = item_at(0); t < a.n_items; ++it, t = item_at(it)) {
+                    set_item(t);
+                    n_total += n_iter;
+                }
+                for (int nv = 0; nv < n_total; ++nv) {
+                    const int st = nv % kStages;
+                    if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) break;
+                    unsigned char* vt = smem + kOffV + st * kTileBytes;
+#pragma unroll 4
+                    for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
+                        uint4* pch = reinterpret_cast<uint4*>(vt + (ct + kCvtThreads * q) * 16);
+                        uint4 v = *pch;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xffff0000u);
+                            asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(hi), "f"(lo));
+                        }
+                        *pch = v;
+                    }
+                    fence_async_smem();
+                    mbar_arrive(bar(B_VREADY0 + st));
+                }
+            }
+        } else if (!f16 || DIFF) {
             const int ct = tid - kCvtWarp * 32;
             const float rho_c = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;
             int nv = 0;
@@ -395,12 +424,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             // running counters: K / V tiles taken from the rings, score tiles and products issued
             int nt_qk = 0, nt_pv = 0, s_qk = 0, s_pv = 0;
             int k_item = 0;      // products of this tile issued so far in the item (the first one overwrites O)
+            int it_first = 0, it_last = -1;   // without landmarks a tile's iterations are one range
+            auto mine = [&](int i) { return LM ? active(g, i) : (i >= it_first && i <= it_last); };
             uint32_t qhi_lo = 0, qlo_lo = 0;
 
             auto issue_qk = [&](int i) {   // S_g = Q_adv,g K(i)^T, then this issuer's release of the K stage
                 const int st = nt_qk % kStages;
                 if (!wait_w(bar(B_KFULL0 + st), (nt_qk / kStages) & 1)) return false;
-                if (active(g, i)) {
+                if (mine(i)) {
                     // the previous scores of this tile (of this item or the one before) must have left TMEM
                     if (s_qk > 0 && !wait_w(bar(B_SEMPTY0 + g), (s_qk - 1) & 1)) return false;
                     tc_fence_after();
@@ -422,7 +453,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             };
             auto issue_pv = [&](int i) {   // O_g (+)= W_g(i) V(i), then this issuer's release of the V stage
                 const int st = nt_pv % kStages, k = k_item;
-                if (active(g, i)) {
+                if (mine(i)) {
                     ++k_item;
                     if (!wait_w(bar(B_PFULL0 + g), s_pv & 1)) return false;
                     if (!wait_w(bar(v_bar + st), (nt_pv / kStages) & 1)) return false;
@@ -452,6 +483,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 set_item(t);
                 const int qsel = it & 1;
                 k_item = 0;
+                if (!LM) {
+                    it_first = jt_hi - (g == 0 ? jt_top0 : jt_top1);
+                    it_last = (g == 0 || tile1_live) ? jt_hi - (g == 0 ? jt_bot0 : jt_bot1) : -1;
+                }
                 qhi_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g) * kTileBytes);
                 qlo_lo = lo_of(sbase + kOffQ + qsel * kQBufBytes + (2 * g + 1) * kTileBytes);
                 ok = wait_w(bar(B_QREADY0 + 2 * qsel + g), (it >> 1) & 1);   // this tile's Q_adv is in place
