@@ -27,6 +27,24 @@ void release_workspace(logos_ctx* ctx) {
     ctx->ws_free_user = nullptr;
 }
 
+
+// decode whose rows go to every rank of the comm; `follows_append`: the launch before it is the engine's append
+int decode_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev, const int8_t* k_cache,
+                const int8_t* v_cache, const float* k_scale, const float* v_scale, const int32_t* len, int B,
+                int H_local, int S_max, int DH, const logos_attn_params* params, bool follows_append) {
+    if (!ctx || !comm) return LOGOS_ERR_INVALID_ARG;
+    if (comm->ctx != ctx || !comm->connected)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: comm is not connected or belongs to another context");
+    if (!params_ok(params))
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: bad parameter block");
+    if (B <= 0 || H_local <= 0 || DH <= 0 || (size_t)B * H_local * comm->world * DH * 8 > comm->row_slot_bytes)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: gathered output exceeds the comm's row area (%zu bytes per slot, 8 per value)",
+                           comm->row_slot_bytes);
+    PeerEpilogue pe;
+    logos::comm_peer_epilogue(comm, H_local, &pe);
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
+                              nullptr, &pe, follows_append);
+}
 }  // namespace
 
 extern "C" {
@@ -347,7 +365,8 @@ int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, co
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step: bad parameter block");
     int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, -1);
     if (rc != LOGOS_OK) return rc;
-    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out,
+                              nullptr, /*follows_append*/ true);
 }
 
 int logos_decode_step_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
@@ -358,36 +377,28 @@ int logos_decode_step_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* 
     int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max,
                               DH, -1);
     if (rc != LOGOS_OK) return rc;
-    return logos_decode_int8_gather(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max,
-                                    DH, params, gathered);
+    rc = decode_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
+                     /*follows_append*/ true);
+    if (rc != LOGOS_OK) return rc;
+    return logos::comm_collect_rows(ctx, comm, gathered, B, H_local * comm->world, DH, /*follows_decode*/ true);
 }
 
 int logos_decode_int8_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
                            const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                            const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
                            const logos_attn_params* params) {
-    if (!ctx || !comm) return LOGOS_ERR_INVALID_ARG;
-    if (comm->ctx != ctx || !comm->connected)
-        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: comm is not connected or belongs to another context");
-    if (!params_ok(params))
-        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: bad parameter block");
-    if (B <= 0 || H_local <= 0 || DH <= 0 || (size_t)B * H_local * comm->world * DH * 8 > comm->row_slot_bytes)
-        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8_push: gathered output exceeds the comm's row area (%zu bytes per slot, 8 per value)",
-                           comm->row_slot_bytes);
-    PeerEpilogue pe;
-    logos::comm_peer_epilogue(comm, H_local, &pe);
-    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
-                              nullptr, &pe);
+    return decode_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH, params,
+                       false);
 }
 
 int logos_decode_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,
                              const int8_t* k_cache, const int8_t* v_cache, const float* k_scale,
                              const float* v_scale, const int32_t* len, int B, int H_local, int S_max, int DH,
                              const logos_attn_params* params, float* gathered) {
-    const int rc = logos_decode_int8_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local,
-                                          S_max, DH, params);
+    const int rc = decode_push(ctx, comm, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H_local, S_max, DH,
+                               params, false);
     if (rc != LOGOS_OK) return rc;
-    return logos::comm_collect_rows(ctx, comm, gathered, B, H_local * comm->world, DH);
+    return logos::comm_collect_rows(ctx, comm, gathered, B, H_local * comm->world, DH, /*follows_decode*/ true);
 }
 
 int logos_decode_int8_collect(logos_ctx* ctx, logos_comm* comm, float* gathered, int B, int H_total, int DH) {
@@ -435,7 +446,7 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
     int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_len, B, H, S_max, DH, -1);
     if (rc != LOGOS_OK) return rc;
     rc = logos::decode_int8(ctx, d_q, q_prev_host ? d_qp : nullptr, k_cache, v_cache, k_scale, v_scale, d_len, B,
-                            H, S_max, DH, params, d_out);
+                            H, S_max, DH, params, d_out, nullptr, /*follows_append*/ true);
     if (rc != LOGOS_OK) return rc;
     LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, d_out, vec * sizeof(float), cudaMemcpyDeviceToHost, st));
     LOGOS_CUDA_TRY(ctx, cudaStreamSynchronize(st));

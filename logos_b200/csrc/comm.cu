@@ -130,6 +130,9 @@ collect_rows_kernel(const CollectArgs c) {
         }
         c.dst[i] = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
     }
+    // launched to overlap the decode kernel before it (the words above carry their own marks, so nothing
+    // of that kernel had to be complete to read them): this kernel still may not end before it has
+    grid_wait_for_earlier();
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned prev = atomicAdd(c.copy_done, 1u);
@@ -216,7 +219,8 @@ void push_targets(const logos_comm* c, int H_local, PushTargets* out) {
 }
 }  // namespace
 
-int comm_collect_rows(logos_ctx* ctx, logos_comm* c, float* gathered, int B, int H_total, int DH) {
+int comm_collect_rows(logos_ctx* ctx, logos_comm* c, float* gathered, int B, int H_total, int DH,
+                      bool follows_decode) {
     int rc = comm_ready(ctx, c);
     if (rc != LOGOS_OK) return rc;
     if (B <= 0 || H_total <= 0 || DH <= 0 || H_total % c->world != 0)
@@ -238,6 +242,10 @@ int comm_collect_rows(logos_ctx* ctx, logos_comm* c, float* gathered, int B, int
     a.status = ctx->tc_status;
     size_t ctas = (a.n_pairs + 255) / 256;
     if (ctas > (size_t)ctx->sm_count * 4) ctas = (size_t)ctx->sm_count * 4;
+    if (follows_decode) {      // the kernel before this one on the stream is the decode that feeds it
+        LOGOS_CUDA_TRY(ctx, launch_overlapped(collect_rows_kernel, dim3((unsigned)ctas), dim3(256), 0, ctx->stream, a));
+        return LOGOS_OK;
+    }
     collect_rows_kernel<<<(unsigned)ctas, 256, 0, ctx->stream>>>(a);
     LOGOS_LAUNCH_CHECK(ctx, "collect_rows_kernel");
     return LOGOS_OK;

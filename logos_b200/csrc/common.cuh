@@ -112,6 +112,32 @@ inline int ensure_smem_limit(logos_ctx* ctx, Fn* kernel, int bytes) {
     return LOGOS_OK;
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_overlapped() may begin as soon as every
+// CTA of the kernel before it on the stream has passed grid_release_dependents() (or exited); what that
+// earlier kernel wrote is only safe to read after grid_wait_for_earlier().  Both calls do nothing in a
+// kernel that was launched the ordinary way, and everything older than the previous kernel is complete
+// and visible as usual.
+__device__ __forceinline__ void grid_release_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_wait_for_earlier() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline size_t dtype_size(int dt) { return dt == LOGOS_F32 ? 4 : 2; }
@@ -173,7 +199,7 @@ int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const
               const float*, const int32_t* pos, int, int, int, int, int pos_bias = 0);
 int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
                 const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
-                float*, const PeerEpilogue* peer = nullptr);
+                float*, const PeerEpilogue* peer = nullptr, bool follows_append = false);
 size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
@@ -187,6 +213,7 @@ int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const v
                  void* O, int B, int H, int S, int DH, const logos_attn_params*);
 void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out);
 int comm_wait(logos_ctx*, logos_comm*, void* gathered, size_t bytes);
-int comm_collect_rows(logos_ctx*, logos_comm*, float* gathered, int B, int H_total, int DH);
+int comm_collect_rows(logos_ctx*, logos_comm*, float* gathered, int B, int H_total, int DH,
+                      bool follows_decode = false);
 int comm_push(logos_ctx*, logos_comm*, const void* local, int B, int H_local, size_t row_bytes);
 }  // namespace logos

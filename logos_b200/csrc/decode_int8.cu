@@ -293,6 +293,12 @@ decode_dense_kernel(const DecodeArgs a) {
     float* p_ns = sc[warp][0];
     float* p_std = sc[warp][PATHS - 1];
 
+    // Launched to overlap the append kernel before it: everything but the newest cache row is older than that
+    // kernel and may be read at once; a CTA whose range holds row pos (or ends just before it: the halo) waits
+    // for the append to finish first.  The collect kernel after this one may start as soon as every CTA is here.
+    grid_release_dependents();
+    if (c1 >= pos) grid_wait_for_earlier();
+
     if (nw > 0) {
         // first K tile goes out before any arithmetic
         uint4 ka[4], kb[4];
@@ -763,7 +769,7 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH) {
 int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
                 const int8_t* v_cache, const float* k_scale, const float* v_scale,
                 const int32_t* len, int B, int H, int S_max, int DH,
-                const logos_attn_params* p, float* out, const PeerEpilogue* peer) {
+                const logos_attn_params* p, float* out, const PeerEpilogue* peer, bool follows_append) {
     if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || (!out && !peer) || !p || B <= 0 ||
         H <= 0 || S_max <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad pointer or extent");
@@ -838,6 +844,11 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
         a.counters = nullptr; a.partials = nullptr;
     }
     dim3 grid(n_splits, BH);
+    if (follows_append) {      // the kernel before this one on the stream is the engine's append of row len - 1
+        if (blend) LOGOS_CUDA_TRY(ctx, launch_overlapped(decode_dense_kernel<true>, grid, dim3(kDenseThreads), 0, ctx->stream, a));
+        else       LOGOS_CUDA_TRY(ctx, launch_overlapped(decode_dense_kernel<false>, grid, dim3(kDenseThreads), 0, ctx->stream, a));
+        return LOGOS_OK;
+    }
     if (blend) decode_dense_kernel<true><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
     else       decode_dense_kernel<false><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
     LOGOS_LAUNCH_CHECK(ctx, "decode_dense_kernel");

@@ -152,6 +152,7 @@ __global__ void append_kernel(const T* __restrict__ k_new, const T* __restrict__
                               int8_t* __restrict__ k_cache, int8_t* __restrict__ v_cache,
                               const float* __restrict__ k_scale, const float* __restrict__ v_scale,
                               const int32_t* __restrict__ pos, int pos_bias, int H, int S_max, int DH) {
+    grid_release_dependents();            // a decode kernel launched to overlap may start: it waits where it reads the row
     int bh = blockIdx.x;
     int b = bh / H;
     int row = pos[b] + pos_bias;
