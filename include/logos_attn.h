@@ -281,6 +281,65 @@ int logos_qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt_q
 int logos_project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual,
                   void* C, int M, int N, int K);
 
+/* logos_project_heads -- logos_project whose A operand is the attention's own output, still head-major
+ *   ([B][H][S][64], what logos_attention_fwd writes): C [B*S][N] = sum over heads of head_out[b][h] ·
+ *   W_O[h] (+ residual), Wt_o [N][H*64] K-major.  The kernel fetches head h's rows as k block h, so the
+ *   per-token concatenation of the head outputs (include/Attention.hpp:292-299, cuda/ModelGPU.cu:974-988)
+ *   never exists in memory. */
+int logos_project_heads(logos_ctx* ctx, int dtype, int out_dtype, const void* head_out, const void* Wt_o,
+                        const void* residual, void* C, int B, int S, int H, int N);
+
+/* INT8 -> BF16 / FP16: logos_kv_dequantize's fp32 product rounded once to the 16-bit type; tensors of a
+ * multiple of 16 values, 16-byte aligned.  (A 16-bit attention over K and V that went through the cache.) */
+int logos_kv_dequantize16(logos_ctx* ctx, int dst_dtype, const int8_t* src, int64_t src_stride,
+                          const float* scales, void* dst, int64_t dst_stride, int n_tensors, int64_t elems);
+
+/* ---- multi-head attention forward in one call ---------------------------- */
+
+/* Replaces MultiHeadAttention::forward (include/Attention.hpp:290-300; per head AttentionHead::forward,
+ * :218-267) and the attention half of ModelGPU::forward's layer loop (cuda/ModelGPU.cu:892-1015) for all
+ * heads and sequences at once:
+ *   Q, K, V = X · W_{Q,K,V}            one GEMM, written in the engine's [B][H][S][64] layout
+ *   [cache]  K, V -> INT8 + scale      when k_cache is given (the order of cuda/ModelGPU.cu:908); with
+ *                                      LOGOS_MHA_ATTEND_DEQUANTIZED the attention then reads them back
+ *                                      from the cache (K and V "passed through" the quantiser)
+ *   head_out = attention(Q, K, V)      Navier-Stokes prologue, masks, softmax as `params` says
+ *   concat   = sum_h head_out_h · W_O[h]
+ *   out      = concat · W_proj (+ residual)
+ * X: [B*S][D_model] in `dtype` (BF16 or FP16); Wt_qkv [3*H*64][D_model], Wt_o [D_model][H*64], Wt_proj
+ * [D_model][D_model]: K-major 16-bit shadows of the weights in the same dtype (INTEGRATION.md gives the
+ * index maps; for the CPU classes, which keep columns [h*64, h*64+64) of head_out_h · W_O[h], Wt_o is block
+ * diagonal).  out, residual: [B*S][D_model] in out_dtype (`dtype` or LOGOS_F32); residual may be NULL.
+ * k_cache, v_cache: int8 [B][H][S_max][64], k_scale, v_scale: float [B][H]; the four together or all NULL.
+ * scratch: device memory of logos_mha_workspace_bytes(B, S, H, D_model) bytes, 256-byte aligned, owned by
+ * the caller and free again when the call's work on the stream has finished.  H * 64 need not equal D_model. */
+#define LOGOS_MHA_ATTEND_DEQUANTIZED 1
+size_t logos_mha_workspace_bytes(int B, int S, int H, int D_model);
+int logos_mha_forward(logos_ctx* ctx, int dtype, int out_dtype, const void* X, const void* Wt_qkv,
+                      const void* Wt_o, const void* Wt_proj, const void* residual, void* out, int B, int S,
+                      int H, int D_model, const logos_attn_params* params, int8_t* k_cache, int8_t* v_cache,
+                      float* k_scale, float* v_scale, int S_max, int flags, void* scratch, size_t scratch_bytes);
+
+/* The same forward in fp32 with the CPU classes' own weight layout -- the drop-in for
+ * `Tensor MultiHeadAttention::forward(const Tensor& X)` (include/Attention.hpp:290-300) on one sequence:
+ * X [seq][d_model]; W_Q, W_K, W_V [H][d_model][d_k]; W_O [H][d_k][d_model]; W_proj [d_model][d_model], all
+ * row-major fp32 as Tensor stores them, d_k = d_model / H <= 128.  Per head Q, K, V = X · W, the attention
+ * `params` describes (blend included), head_out · W_O[h] of which columns [0, d_k) go to columns
+ * [h d_k, (h+1) d_k) of concat, then concat · W_proj.  kv_int8 != 0 passes K and V through the Nikhilam
+ * quantiser and back before the attention (cuda/ModelGPU.cu:908, nikhilam_decompress).  The GEMMs are
+ * fp32 FMA loops in k order (logos_gemm_f32), the attention is logos_attention_fwd in fp32.
+ * scratch: logos_mha_f32_workspace_bytes(seq, d_model, H) bytes of device memory, 256-byte aligned. */
+size_t logos_mha_f32_workspace_bytes(int seq, int d_model, int H);
+int logos_mha_forward_f32(logos_ctx* ctx, const float* X, const float* W_Q, const float* W_K, const float* W_V,
+                          const float* W_O, const float* W_proj, float* out, int seq, int d_model, int H,
+                          const logos_attn_params* params, int kv_int8, void* scratch, size_t scratch_bytes);
+
+/* C_b [M][N] = A_b [M][K] · B_b [K][N] for b < batch, row-major fp32 with leading dimensions and batch
+ * strides in elements (stride 0: one operand for the whole batch); fp32 FMA accumulation in k order --
+ * the arithmetic of the reference's vedic_gemm (include/VedicGEMM.hpp) up to the order of the additions. */
+int logos_gemm_f32(logos_ctx* ctx, const float* A, int lda, int64_t strideA, const float* B, int ldb,
+                   int64_t strideB, float* C, int ldc, int64_t strideC, int M, int N, int K, int batch);
+
 /* ---- heads over several GPUs -------------------------------------------- */
 
 /* The path shards by (sequence, head): GPU r of N owns heads [r H/N, (r+1) H/N) and their cache, and

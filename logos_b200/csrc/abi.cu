@@ -28,6 +28,30 @@ void release_workspace(logos_ctx* ctx) {
 }
 
 
+// scratch of logos_mha_forward: Q, K, V, head outputs ([B][H][S][64], 16-bit), concat ([B*S][D], 16-bit),
+// two tables of max|x| per (sequence, head); every part 256-byte aligned
+struct mha_layout { size_t q, k, v, o, concat, kmax, vmax, total; };
+mha_layout mha_scratch(int B, int S, int H, int D) {
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t heads = up((size_t)B * H * S * 64 * 2), cc = up((size_t)B * S * D * 2), tab = up((size_t)B * H * 4);
+    mha_layout l;
+    l.q = 0; l.k = heads; l.v = 2 * heads; l.o = 3 * heads; l.concat = 4 * heads;
+    l.kmax = l.concat + cc; l.vmax = l.kmax + tab; l.total = l.vmax + tab;
+    return l;
+}
+
+// scratch of logos_mha_forward_f32: Q, K, V, head outputs ([H][seq][d_k] fp32), concat ([seq][d_model]), the INT8
+// copies of K and V and their scales
+struct mha_f32_layout { size_t q, k, v, o, concat, k8, v8, scales, total; };
+mha_f32_layout mha_f32_scratch(int seq, int D, int H) {
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t heads = up((size_t)seq * D * 4), bytes8 = up((size_t)seq * D);
+    mha_f32_layout l;
+    l.q = 0; l.k = heads; l.v = 2 * heads; l.o = 3 * heads; l.concat = 4 * heads;
+    l.k8 = 5 * heads; l.v8 = l.k8 + bytes8; l.scales = l.v8 + bytes8; l.total = l.scales + up((size_t)2 * H * 4);
+    return l;
+}
+
 // decode whose rows go to every rank of the comm; `follows_append`: the launch before it is the engine's append
 int decode_push(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev, const int8_t* k_cache,
                 const int8_t* v_cache, const float* k_scale, const float* v_scale, const int32_t* len, int B,
@@ -297,6 +321,129 @@ int logos_prefill_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q
         }
     }
     return logos_attention_fwd(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+}
+
+int logos_project_heads(logos_ctx* ctx, int dtype, int out_dtype, const void* head_out, const void* Wt_o,
+                        const void* residual, void* C, int B, int S, int H, int N) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::project_heads(ctx, dtype, out_dtype, head_out, Wt_o, residual, C, B, S, H, N);
+}
+
+int logos_kv_dequantize16(logos_ctx* ctx, int dst_dtype, const int8_t* src, int64_t src_stride,
+                          const float* scales, void* dst, int64_t dst_stride, int n_tensors, int64_t elems) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::kv_dequantize16(ctx, dst_dtype, src, src_stride, scales, dst, dst_stride, n_tensors, elems);
+}
+
+size_t logos_mha_workspace_bytes(int B, int S, int H, int D_model) {
+    if (B <= 0 || S <= 0 || H <= 0 || D_model <= 0) return 0;
+    const mha_layout l = mha_scratch(B, S, H, D_model);
+    return l.total;
+}
+
+int logos_mha_forward(logos_ctx* ctx, int dtype, int out_dtype, const void* X, const void* Wt_qkv,
+                      const void* Wt_o, const void* Wt_proj, const void* residual, void* out, int B, int S,
+                      int H, int D_model, const logos_attn_params* params, int8_t* k_cache, int8_t* v_cache,
+                      float* k_scale, float* v_scale, int S_max, int flags, void* scratch, size_t scratch_bytes) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!X || !Wt_qkv || !Wt_o || !Wt_proj || !out || !scratch || B <= 0 || S <= 0 || H <= 0 || D_model <= 0)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward: bad pointer or extent");
+    if (!params_ok(params)) return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward: bad parameter block");
+    if (dtype != LOGOS_BF16 && dtype != LOGOS_F16)
+        return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED, "mha_forward: X and the weight shadows are BF16 or FP16");
+    const int given = (k_cache != nullptr) + (v_cache != nullptr) + (k_scale != nullptr) + (v_scale != nullptr);
+    if (given != 0 && given != 4)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward: caches and scales are given together or not at all");
+    if (given == 4 && S > S_max)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward: S = %d exceeds S_max = %d", S, S_max);
+    if ((flags & LOGOS_MHA_ATTEND_DEQUANTIZED) && given != 4)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward: attending the dequantised K and V needs the caches");
+    if ((int64_t)B * H > 65535)
+        return logos::fail(ctx, LOGOS_ERR_UNSUPPORTED, "mha_forward: more than 65535 (sequence, head) tensors");
+    const mha_layout l = mha_scratch(B, S, H, D_model);
+    if (scratch_bytes < l.total || (reinterpret_cast<uintptr_t>(scratch) & 255u))
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "mha_forward: scratch of %zu bytes, 256-byte aligned, needed (%zu given)",
+                           l.total, scratch_bytes);
+    char* base = static_cast<char*>(scratch);
+    void *Q = base + l.q, *K = base + l.k, *V = base + l.v, *O = base + l.o, *concat = base + l.concat;
+    float* kmax = reinterpret_cast<float*>(base + l.kmax);
+    float* vmax = reinterpret_cast<float*>(base + l.vmax);
+
+    int rc = logos::qkv_project(ctx, dtype, X, Wt_qkv, Q, K, V, B, S, H, D_model, given ? kmax : nullptr,
+                                given ? vmax : nullptr);
+    if (rc != LOGOS_OK) return rc;
+    if (given) {
+        const int64_t elems = (int64_t)S * 64, dst_stride = (int64_t)S_max * 64;
+        rc = logos::kv_quantize(ctx, dtype, K, elems, k_cache, dst_stride, k_scale, B * H, elems, kmax);
+        if (rc != LOGOS_OK) return rc;
+        rc = logos::kv_quantize(ctx, dtype, V, elems, v_cache, dst_stride, v_scale, B * H, elems, vmax);
+        if (rc != LOGOS_OK) return rc;
+        if (flags & LOGOS_MHA_ATTEND_DEQUANTIZED) {
+            rc = logos::kv_dequantize16(ctx, dtype, k_cache, dst_stride, k_scale, K, elems, B * H, elems);
+            if (rc != LOGOS_OK) return rc;
+            rc = logos::kv_dequantize16(ctx, dtype, v_cache, dst_stride, v_scale, V, elems, B * H, elems);
+            if (rc != LOGOS_OK) return rc;
+        }
+    }
+    rc = logos_attention_fwd(ctx, dtype, dtype, Q, K, V, O, B, H, S, 64, params);
+    if (rc != LOGOS_OK) return rc;
+    rc = logos::project_heads(ctx, dtype, dtype, O, Wt_o, nullptr, concat, B, S, H, D_model);
+    if (rc != LOGOS_OK) return rc;
+    return logos::project(ctx, dtype, out_dtype, concat, Wt_proj, residual, out, B * S, D_model, D_model);
+}
+
+size_t logos_mha_f32_workspace_bytes(int seq, int d_model, int H) {
+    if (seq <= 0 || d_model <= 0 || H <= 0 || d_model % H != 0) return 0;
+    return mha_f32_scratch(seq, d_model, H).total;
+}
+
+int logos_gemm_f32(logos_ctx* ctx, const float* A, int lda, int64_t strideA, const float* B, int ldb,
+                   int64_t strideB, float* C, int ldc, int64_t strideC, int M, int N, int K, int batch) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    return logos::gemm_f32(ctx, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, M, N, K, batch);
+}
+
+int logos_mha_forward_f32(logos_ctx* ctx, const float* X, const float* W_Q, const float* W_K, const float* W_V,
+                          const float* W_O, const float* W_proj, float* out, int seq, int d_model, int H,
+                          const logos_attn_params* params, int kv_int8, void* scratch, size_t scratch_bytes) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!X || !W_Q || !W_K || !W_V || !W_O || !W_proj || !out || !scratch || seq <= 0 || d_model <= 0 || H <= 0)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward_f32: bad pointer or extent");
+    if (d_model % H != 0)     // the reference throws std::invalid_argument here (include/Attention.hpp:281-282)
+        return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward_f32: d_model must be divisible by num_heads");
+    if (!params_ok(params)) return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "mha_forward_f32: bad parameter block");
+    const int dk = d_model / H;
+    const mha_f32_layout l = mha_f32_scratch(seq, d_model, H);
+    if (scratch_bytes < l.total || (reinterpret_cast<uintptr_t>(scratch) & 255u))
+        return logos::fail(ctx, LOGOS_ERR_WORKSPACE, "mha_forward_f32: scratch of %zu bytes, 256-byte aligned, needed (%zu given)",
+                           l.total, scratch_bytes);
+    char* base = static_cast<char*>(scratch);
+    float *Q = (float*)(base + l.q), *K = (float*)(base + l.k), *V = (float*)(base + l.v), *O = (float*)(base + l.o);
+    float* concat = (float*)(base + l.concat);
+    const int64_t head = (int64_t)seq * dk, wqkv = (int64_t)d_model * dk;
+    const float* W[3] = {W_Q, W_K, W_V};
+    float* D3[3] = {Q, K, V};
+    for (int i = 0; i < 3; ++i) {      // [H] x ([seq][d_model] · [d_model][d_k]), X shared by the heads
+        int rc = logos::gemm_f32(ctx, X, d_model, 0, W[i], dk, wqkv, D3[i], dk, head, seq, dk, d_model, H);
+        if (rc != LOGOS_OK) return rc;
+    }
+    if (kv_int8) {
+        int8_t* k8 = (int8_t*)(base + l.k8);
+        int8_t* v8 = (int8_t*)(base + l.v8);
+        float* ks = (float*)(base + l.scales);
+        float* vs = ks + H;
+        int rc = logos::kv_quantize(ctx, LOGOS_F32, K, head, k8, head, ks, H, head);
+        if (rc == LOGOS_OK) rc = logos::kv_quantize(ctx, LOGOS_F32, V, head, v8, head, vs, H, head);
+        if (rc == LOGOS_OK) rc = logos::kv_dequantize(ctx, k8, head, ks, K, head, H, head);
+        if (rc == LOGOS_OK) rc = logos::kv_dequantize(ctx, v8, head, vs, V, head, H, head);
+        if (rc != LOGOS_OK) return rc;
+    }
+    int rc = logos_attention_fwd(ctx, LOGOS_F32, LOGOS_F32, Q, K, V, O, 1, H, seq, dk, params);
+    if (rc != LOGOS_OK) return rc;
+    // columns [0, d_k) of head_out_h · W_O[h] -> columns [h d_k, (h+1) d_k) of concat
+    rc = logos::gemm_f32(ctx, O, dk, head, W_O, d_model, (int64_t)dk * d_model, concat, d_model, dk, seq, dk, dk, H);
+    if (rc != LOGOS_OK) return rc;
+    return logos::gemm_f32(ctx, concat, d_model, 0, W_proj, d_model, 0, out, d_model, 0, seq, d_model, d_model, 1);
 }
 
 int logos_kv_quantize(logos_ctx* ctx, int src_dtype, const void* src, int64_t src_stride,

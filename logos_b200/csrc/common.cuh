@@ -191,6 +191,11 @@ int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*,
                 const float* absmax_known = nullptr);
 int project(logos_ctx*, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual, void* C,
             int M, int N, int K);
+int gemm_f32(logos_ctx*, const float* A, int lda, int64_t strideA, const float* B, int ldb, int64_t strideB, float* C,
+             int ldc, int64_t strideC, int M, int N, int K, int batch);
+int project_heads(logos_ctx*, int dtype, int out_dtype, const void* head_out, const void* Wt, const void* residual,
+                  void* C, int B, int S, int H, int N);
+int kv_dequantize16(logos_ctx*, int dst_dtype, const int8_t*, int64_t, const float*, void*, int64_t, int, int64_t);
 int qkv_project(logos_ctx*, int dtype, const void* X, const void* Wt, void* Q, void* K, void* V, int B, int S,
                 int H, int D, float* k_absmax, float* v_absmax);
 int kv_dequantize(logos_ctx*, const int8_t*, int64_t, const float*, float*, int64_t, int, int64_t);

@@ -45,6 +45,9 @@ struct GemmArgs {
     void* q; void* k; void* v;         // [B][H][S][64], 16-bit, operand dtype
     int S, H;
     unsigned* k_absmax; unsigned* v_absmax;   // [B][H] float bits (non-negative), atomicMax; may be null
+    // A given head-major, [B][a_heads][a_S][64] (the attention's output layout) with K = 64 a_heads: k block kb
+    // is head kb, so the tiles are fetched where they lie and nothing is permuted.  0: A is [M][K] row-major.
+    int a_heads, a_S;
     int* status;
 };
 
@@ -70,8 +73,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kGOffBar + (2 * kGStages + 1) * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kGN, m0 = blockIdx.y * kBM;
+    const int n0 = blockIdx.x * kGN;
     const int n_kb = (a.K + kGK - 1) / kGK;
+    // rows of this tile: m0 .. m0 + 127, below m_lim.  Head-major A: tiles never straddle two sequences.
+    int m0 = blockIdx.y * kBM, m_lim = a.M, a_row = m0, a_slab = 0;
+    if (a.a_heads) {
+        const int tiles = (a.a_S + kBM - 1) / kBM;
+        const int b = blockIdx.y / tiles;
+        a_row = (blockIdx.y - b * tiles) * kBM;
+        a_slab = b * a.a_heads;
+        m0 = b * a.a_S + a_row;
+        m_lim = (b + 1) * a.a_S;
+    }
 
     if (warp == 0 && lane == 0) {
         for (int s = 0; s < kGStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
@@ -94,7 +107,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 const int s = kb % kGStages;
                 if (kb >= kGStages && !mbar_wait(empty(s), ((kb / kGStages) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(full(s), 2 * kGTile);
-                tma_load_3d(sbase + (2 * s) * kGTile, &mapA, kb * kGK, m0, 0, full(s));
+                if (a.a_heads) tma_load_3d(sbase + (2 * s) * kGTile, &mapA, 0, a_row, a_slab + kb, full(s));
+                else           tma_load_3d(sbase + (2 * s) * kGTile, &mapA, kb * kGK, m0, 0, full(s));
                 tma_load_3d(sbase + (2 * s + 1) * kGTile, &mapW, kb * kGK, n0, 0, full(s));
             }
         }
@@ -135,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     tc_ld32(t_row + c0, v);
                     tc_wait_ld();
                     const int n = n0 + c0;
-                    if (m < a.M && n < a.N) {          // N is a multiple of 32
+                    if (m < m_lim && n < a.N) {        // N is a multiple of 32
                         const size_t off = (size_t)m * a.N + n;
                         if (a.c_is_f32) {
                             float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C) + off);
@@ -180,7 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const int which = hg / a.H, h = hg - which * a.H;
                     float amax = 0.0f;
                     unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.q : (which == 1 ? a.k : a.v));
-                    const bool live = m < a.M && which < 3;
+                    const bool live = m < m_lim && which < 3;
                     uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)b * a.H + h) * a.S + s) * 64);
 #pragma unroll 1
                     for (int hc = 0; hc < 2; ++hc) {
@@ -242,6 +256,19 @@ bool make_map_2d(CUtensorMap* m, const void* base, int rows, int K, bool f16) {
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// [slabs][S][64] 16-bit (one slab per (sequence, head)), box = 128 rows x 64, 128-byte swizzle
+bool make_map_slabs(CUtensorMap* m, const void* base, int S, int slabs, bool f16) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {64, (cuuint64_t)S, (cuuint64_t)slabs};
+    cuuint64_t strides[2] = {128, (cuuint64_t)S * 128};
+    cuuint32_t box[3] = {(cuuint32_t)kGK, (cuuint32_t)kBM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
     if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.K % 8) != 0 || (a.N % 64) != 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "projection: M, N, K = %d, %d, %d (K a multiple of 8, N of 64)", a.M, a.N, a.K);
@@ -249,11 +276,14 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
         return fail(ctx, LOGOS_ERR_ALIGNMENT, "projection: operands must be 16-byte aligned");
     if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "projection: status word missing");
     CUtensorMap ma, mw;
-    if (!make_map_2d(&ma, A, a.M, a.K, a.f16 != 0) || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0))
+    const bool a_ok = a.a_heads ? make_map_slabs(&ma, A, a.a_S, (a.M / a.a_S) * a.a_heads, a.f16 != 0)
+                                : make_map_2d(&ma, A, a.M, a.K, a.f16 != 0);
+    if (!a_ok || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0))
         return fail(ctx, LOGOS_ERR_CUDA, "projection: cuTensorMapEncodeTiled failed");
     a.status = ctx->tc_status;
     if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel, kGSmem)) return rc;
-    dim3 grid((a.N + kGN - 1) / kGN, (a.M + kBM - 1) / kBM);
+    dim3 grid((a.N + kGN - 1) / kGN,
+              a.a_heads ? (a.M / a.a_S) * ((a.a_S + kBM - 1) / kBM) : (a.M + kBM - 1) / kBM);
     gemm_tc_kernel<<<grid, kGThreads, kGSmem, ctx->stream>>>(ma, mw, a);
     LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
     return LOGOS_OK;
@@ -272,6 +302,21 @@ int project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void*
     a.M = M; a.N = N; a.K = K; a.f16 = dtype == LOGOS_F16; a.mode = 0;
     a.C = C; a.R = residual; a.c_is_f32 = out_dtype == LOGOS_F32;
     return launch_gemm(ctx, A, Wt, a);
+}
+
+int project_heads(logos_ctx* ctx, int dtype, int out_dtype, const void* head_out, const void* Wt, const void* residual,
+                  void* C, int B, int S, int H, int N) {
+    if (!head_out || !Wt || !C || B <= 0 || S <= 0 || H <= 0 || N <= 0)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "project_heads: bad pointer or extent");
+    if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project_heads: operands must be BF16 or FP16");
+    if (out_dtype != dtype && out_dtype != LOGOS_F32) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project_heads: output is the operand type or fp32");
+    if (!aligned16(C) || (residual && !aligned16(residual)) || (N % 64) != 0)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project_heads: C and the residual must be 16-byte aligned, N a multiple of 64");
+    GemmArgs a{};
+    a.M = B * S; a.N = N; a.K = H * 64; a.f16 = dtype == LOGOS_F16; a.mode = 0;
+    a.C = C; a.R = residual; a.c_is_f32 = out_dtype == LOGOS_F32;
+    a.a_heads = H; a.a_S = S;
+    return launch_gemm(ctx, head_out, Wt, a);
 }
 
 int qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt, void* Q, void* K, void* V, int B, int S,

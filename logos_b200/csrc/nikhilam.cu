@@ -118,6 +118,27 @@ quantize_kernel(const T* __restrict__ src, int64_t src_stride, int8_t* __restric
     }
 }
 
+// int8 -> 16-bit: the fp32 product q * scale (the reference's nikhilam_dequantize_kernel) rounded once to T
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+dequantize16_kernel(const int8_t* __restrict__ src, int64_t src_stride, const float* __restrict__ scales,
+                    T* __restrict__ dst, int64_t dst_stride, int64_t elems) {
+    const int8_t* q = src + (int64_t)blockIdx.y * src_stride;
+    T* x = dst + (int64_t)blockIdx.y * dst_stride;
+    const float scale = scales[blockIdx.y];
+    const int64_t nvec = elems >> 4;          // elems is a multiple of 16, both sides 16-byte aligned
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * kThreads) {
+        uint4 w = __ldg(reinterpret_cast<const uint4*>(q + (i << 4)));
+        const int8_t* b = reinterpret_cast<const int8_t*>(&w);
+        __align__(16) T o[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) o[k] = from_f32<T>((float)b[k] * scale);
+        uint4* dst4 = reinterpret_cast<uint4*>(x + (i << 4));
+        dst4[0] = reinterpret_cast<const uint4*>(o)[0];
+        dst4[1] = reinterpret_cast<const uint4*>(o)[1];
+    }
+}
+
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 dequantize_kernel(const int8_t* __restrict__ src, int64_t src_stride,
@@ -244,6 +265,25 @@ int kv_dequantize(logos_ctx* ctx, const int8_t* src, int64_t src_stride, const f
         dequantize_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, scales, dst,
                                                                      dst_stride, elems);
     LOGOS_LAUNCH_CHECK(ctx, "dequantize_kernel");
+    return LOGOS_OK;
+}
+
+int kv_dequantize16(logos_ctx* ctx, int dst_dtype, const int8_t* src, int64_t src_stride, const float* scales,
+                    void* dst, int64_t dst_stride, int n_tensors, int64_t elems) {
+    if (!src || !dst || !scales || n_tensors <= 0 || elems <= 0 || src_stride < elems || dst_stride < elems)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "kv_dequantize16: bad pointer, extent or stride");
+    if (dst_dtype != LOGOS_BF16 && dst_dtype != LOGOS_F16)
+        return fail(ctx, LOGOS_ERR_UNSUPPORTED, "kv_dequantize16: the destination is BF16 or FP16");
+    if (n_tensors > 65535)
+        return fail(ctx, LOGOS_ERR_UNSUPPORTED, "kv_dequantize16: more than 65535 tensors per call");
+    if ((elems % 16) != 0 || !aligned16(src) || !aligned16(dst) || (src_stride % 16) != 0 || (dst_stride % 8) != 0)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "kv_dequantize16: 16-byte aligned tensors of a multiple of 16 values");
+    dim3 grid(blocks_for(ctx, elems / 16, n_tensors), n_tensors);
+    if (dst_dtype == LOGOS_BF16)
+        dequantize16_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, scales, (__nv_bfloat16*)dst, dst_stride, elems);
+    else
+        dequantize16_kernel<__half><<<grid, kThreads, 0, ctx->stream>>>(src, src_stride, scales, (__half*)dst, dst_stride, elems);
+    LOGOS_LAUNCH_CHECK(ctx, "dequantize16_kernel");
     return LOGOS_OK;
 }
 

@@ -117,6 +117,54 @@ class Engine:
                                           _ptr(out), M, N, K))
         return out
 
+    def project_heads(self, head_out, Wt_o, residual=None, out_dtype=None, out=None):
+        """head_out: [B, H, S, 64] as the attention wrote it; Wt_o: [N, H*64] -> sum over heads of
+        head_out[b, h] · W_O[h] (+ residual), [B*S, N].  No per-token concatenation is made."""
+        B, H, S, DH = head_out.shape
+        N = Wt_o.shape[0]
+        assert DH == 64 and head_out.is_contiguous() and Wt_o.is_contiguous() and Wt_o.shape[1] == H * 64
+        out_dtype = out_dtype or head_out.dtype
+        if out is None:
+            out = torch.empty((B * S, N), dtype=out_dtype, device=head_out.device)
+        if residual is not None:
+            assert residual.dtype == out.dtype and residual.shape == out.shape and residual.is_contiguous()
+        self._check(self.lib.logos_project_heads(self.h, _DT[head_out.dtype], _DT[out.dtype], _ptr(head_out), _ptr(Wt_o),
+                                                _ptr(residual), _ptr(out), B, S, H, N))
+        return out
+
+    def mha_forward(self, X, Wt_qkv, Wt_o, Wt_proj, B, S, H, params: L.Params, residual=None, out_dtype=None,
+                    caches=None, attend_dequantized=False, scratch=None):
+        """MultiHeadAttention::forward for all heads and sequences in one call (logos_mha_forward).
+        X: [B*S, D] 16-bit; caches: (k_cache, v_cache, k_scale, v_scale) or None -> [B*S, D]."""
+        D = X.shape[1]
+        assert X.is_contiguous() and X.shape[0] == B * S and Wt_qkv.shape == (3 * H * 64, D)
+        assert Wt_o.shape == (D, H * 64) and Wt_proj.shape == (D, D)
+        assert Wt_qkv.is_contiguous() and Wt_o.is_contiguous() and Wt_proj.is_contiguous()
+        out = torch.empty((B * S, D), dtype=out_dtype or X.dtype, device=X.device)
+        if residual is not None:
+            assert residual.dtype == out.dtype and residual.shape == out.shape and residual.is_contiguous()
+        need = self.lib.logos_mha_workspace_bytes(B, S, H, D)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=X.device)
+        kc, vc, ks, vs = caches if caches is not None else (None, None, None, None)
+        S_max = kc.shape[-2] if kc is not None else 0
+        self._check(self.lib.logos_mha_forward(self.h, _DT[X.dtype], _DT[out.dtype], _ptr(X), _ptr(Wt_qkv), _ptr(Wt_o),
+                                              _ptr(Wt_proj), _ptr(residual), _ptr(out), B, S, H, D, C.byref(params),
+                                              _ptr(kc), _ptr(vc), _ptr(ks), _ptr(vs), S_max,
+                                              L.MHA_ATTEND_DEQUANTIZED if attend_dequantized else 0, _ptr(scratch),
+                                              scratch.numel()))
+        return out
+
+    def nikhilam_decompress16(self, q, scales, dtype, rows=None):
+        """q: [..., S_max, DH] int8, scales [...] -> BF16 / FP16 of rows [0, rows)."""
+        S_max, DH = q.shape[-2:]
+        rows = S_max if rows is None else rows
+        n = q.numel() // (S_max * DH)
+        out = torch.empty(q.shape[:-2] + (rows, DH), dtype=dtype, device=q.device)
+        self._check(self.lib.logos_kv_dequantize16(self.h, _DT[dtype], _ptr(q), S_max * DH, _ptr(scales), _ptr(out),
+                                                  rows * DH, n, rows * DH))
+        return out
+
     def nikhilam_compress_absmax(self, x, absmax, cache):
         """nikhilam_compress of x ([n..., S, DH]) into `cache` ([n, S_max, DH]) when max|x| per tensor is known."""
         S, DH = x.shape[-2:]

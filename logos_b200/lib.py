@@ -17,6 +17,7 @@ ERR_SCRATCH_LIMIT = 7
 ERR_KERNEL_TIMEOUT = 8
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
+MHA_ATTEND_DEQUANTIZED = 1
 OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK = 0, 1, 2, 3
 COMM_HANDLE_BYTES = 80
 
@@ -82,6 +83,14 @@ SIGNATURES = {
     "logos_kv_quantize_absmax": (_i, [_vp, _i, _vp, _i64, _vp, _i64, _vp, _vp, _i, _i64]),
     "logos_project": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "logos_qkv_project": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "logos_project_heads": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
+    "logos_kv_dequantize16": (_i, [_vp, _i, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
+    "logos_mha_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_mha_f32_workspace_bytes": (_sz, [_i, _i, _i]),
+    "logos_mha_forward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _PP, _i, _vp, _sz]),
+    "logos_gemm_f32": (_i, [_vp, _vp, _i, _i64, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _i]),
+    "logos_mha_forward": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp, _vp, _vp, _vp,
+                               _i, _i, _vp, _sz]),
     "logos_kv_dequantize": (_i, [_vp, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
     "logos_kv_append": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_decode_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),

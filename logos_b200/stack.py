@@ -114,8 +114,7 @@ class AttentionStack:
             O = eng.attention(Q, K, V, self.params)                        # [B, H_loc, S, 64]
             self.q_prev[l, :B].copy_(Q[:, :, S - 1].half())
             O = self._gather(O, (S, 64))
-            A = O.permute(0, 2, 1, 3).reshape(B * S, cfg.num_heads * 64)   # heads side by side per token
-            Y = eng.project(A.contiguous(), self.Wt_o[l])
+            Y = eng.project_heads(O.contiguous(), self.Wt_o[l])           # head-major operand: nothing is permuted
             X = eng.project(Y, self.Wt_proj[l], residual=X)
         self.cache.set_lens(S)
         last = X.view(B, S, cfg.d_model)[:, S - 1]

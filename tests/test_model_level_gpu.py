@@ -29,9 +29,9 @@ def mha_case(engine, seq, d_model, H, alpha, sparse, seed):
     mha = MultiHeadAttention(engine, dev(W["WQ"]), dev(W["WK"]), dev(W["WV"]), dev(W["WO"]), dev(W["Wp"]),
                              use_sparse=sparse, sparse_window=8, sparse_stride=4, use_navier_stokes=True,
                              ns_alpha=alpha, ns_eta=0.1, ns_nu=0.05, diffuse_mode=L.DIFFUSE_CENTRAL, kv_int8=True)
-    torch.backends.cuda.matmul.allow_tf32 = False
-    got = mha.forward(dev(X)).cpu().numpy()
+    got = mha.forward(dev(X)).cpu().numpy()          # logos_mha_forward_f32: every step in the engine
     assert_close(got, want, f"MHA seq={seq} d={d_model} alpha={alpha} sparse={sparse}")
+    return mha, X, W, cfg
 
 
 def test_mha_forward_small(engine):
@@ -43,6 +43,45 @@ def test_mha_forward_configuration_1(engine):
     # B=1, seq=512, d_model=1024, H=16, DH=64, fp32; X ~ N(0,1), weights ~ N(0,0.02); causal full
     # attention with Q-advection 0.1 and (central) V-diffusion 0.05; K/V through the INT8 round trip
     mha_case(engine, 512, 1024, 16, 1.0, False, 82)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_mha_forward16_configuration_1(engine, dtype):
+    """The same forward on the tensor cores (logos_mha_forward, one call): X and the weight shadows in 16 bits,
+    Q, K, V, the head outputs and concat stored in 16 bits, fp32 accumulation.  The CPU model gets the rounded
+    X and weights; what is left is the rounding of the four stored intermediates, each 2^-9 (BF16) or 2^-12
+    (FP16) relative per value: rel-L2 within 1e-2 / 2e-3 of the fp32 forward (5e-3 for FP16 through the INT8
+    round trip of K and V)."""
+    seq, d_model, H, seed = 512, 1024, 16, 82
+    dk = d_model // H
+    r16 = lambda a: torch.from_numpy(a).to(dtype).float().numpy()
+    X = r16(syn.normal((seq, d_model), seed, 1))
+    W = {k: r16(syn.normal(shape, seed, t, std=0.02)) for t, (k, shape) in enumerate(
+        dict(WQ=(H, d_model, dk), WK=(H, d_model, dk), WV=(H, d_model, dk), WO=(H, dk, d_model),
+             Wp=(d_model, d_model)).items(), start=2)}
+    dev = lambda a: torch.from_numpy(a).cuda()
+    lim = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    for kv_int8, mode in [(False, L.DIFFUSE_CAUSAL), (True, L.DIFFUSE_CENTRAL)]:
+        if mode == L.DIFFUSE_CENTRAL:      # the CPU classes' own stencil: the reference model as a whole
+            cfg = O.HeadCfg(0, 8, 4, 1, 1.0, 0.1, 0.05, int(kv_int8), O.lib().lo_max_threads())
+            want = np.empty((seq, d_model), np.float32)
+            O.lib().lo_mha_forward(X, W["WQ"], W["WK"], W["WV"], W["WO"], W["Wp"], seq, d_model, H, C.byref(cfg), want)
+        else:                              # the GPU model's causal stencil (tensor-core kernel): the model's steps
+            Xd = X.astype(np.float64)      # in fp64 around the oracle's attention
+            Q, K, V = (np.einsum("sd,hdc->hsc", Xd, W[k].astype(np.float64)).astype(np.float32) for k in ("WQ", "WK", "WV"))
+            p = O.attn_params(1.0 / np.sqrt(dk), True, 0, 0, 0.1, 0.05, 1.0, mode)
+            ho = O.attention_batched(Q[None], K[None], V[None], p)[0].astype(np.float64)       # [H, seq, dk]
+            concat = np.concatenate([ho[h] @ W["WO"][h].astype(np.float64)[:, :dk] for h in range(H)], axis=1)
+            want = (concat @ W["Wp"].astype(np.float64)).astype(np.float32)
+        mha = MultiHeadAttention(engine, dev(W["WQ"]), dev(W["WK"]), dev(W["WV"]), dev(W["WO"]), dev(W["Wp"]),
+                                 use_sparse=False, use_navier_stokes=True, ns_alpha=1.0, ns_eta=0.1, ns_nu=0.05,
+                                 diffuse_mode=mode, kv_int8=kv_int8)
+        got = mha.forward16(dev(X), dtype).cpu().numpy()
+        scale = float(np.abs(want).max())
+        # through the quantiser a K or V value that was rounded to 16 bits first can land on the neighbouring
+        # byte (1/127 of the tensor's range): FP16 then sees 3e-3 instead of 1e-3
+        lim_case = max(lim, 5e-3) if kv_int8 else lim
+        assert_close(got, want, f"MHA 16-bit {dtype} int8={kv_int8}", max_abs=3 * lim_case * scale, rel_l2=lim_case)
 
 
 def test_generation_loop_prefill_then_decode(engine):

@@ -77,3 +77,63 @@ def test_projection_argument_checks(engine):
     A32 = torch.zeros((4, 64), device="cuda")
     with pytest.raises(KeyError if False else L.LogosError):
         engine.project(A32, torch.zeros((64, 64), device="cuda"))       # fp32 operands are not taken
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,H,N", [(1, 128, 1, 64), (2, 256, 4, 256), (3, 200, 4, 512), (2, 77, 16, 1024), (1, 1, 2, 128)])
+def test_project_heads_reads_the_attention_layout(engine, dtype, B, S, H, N):
+    """C = sum over heads of head_out[b, h] · W_O[h] with head_out still [B, H, S, 64]: equal to the same
+    product on the per-token concatenation, sequences that are no multiple of the tile included."""
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + S + H)
+    O_ = torch.randn((B, H, S, 64), device="cuda", generator=g).to(dtype)
+    Wo = (torch.randn((H, 64, N), device="cuda", generator=g) * 0.05).to(dtype)
+    Wt_o = Wo.reshape(H * 64, N).t().contiguous()                      # [N][H*64]
+    want = torch.einsum("bhsc,hcn->bsn", O_.double(), Wo.double()).reshape(B * S, N).float()
+    got = engine.project_heads(O_, Wt_o, out_dtype=torch.float32)
+    engine.synchronize()
+    tol = 2e-5 * (H * 64) ** 0.5 * 3 + 1e-6
+    assert float((got - want).abs().max()) <= tol
+    # and bit-identical to the row-major GEMM on the concatenated operand (same tiles, same order of k)
+    A = O_.permute(0, 2, 1, 3).reshape(B * S, H * 64).contiguous()
+    same = engine.project(A, Wt_o, out_dtype=torch.float32)
+    engine.synchronize()
+    assert torch.equal(got, same)
+    R = torch.randn((B * S, N), device="cuda", generator=g).to(dtype)
+    got_r = engine.project_heads(O_, Wt_o, residual=R)
+    same_r = engine.project(A, Wt_o, residual=R)
+    engine.synchronize()
+    assert torch.equal(got_r, same_r)
+
+
+@pytest.mark.parametrize("M,N,K,batch", [(64, 64, 16, 1), (70, 33, 19, 3), (512, 64, 1024, 4), (1, 5, 7, 2), (130, 257, 64, 1)])
+def test_gemm_f32_strided_batched(engine, M, N, K, batch):
+    g = torch.Generator(device="cuda").manual_seed(M + 3 * N + 7 * K)
+    lda, ldb, ldc = K + 3, N + 2, N + 5
+    A = torch.randn((batch, M, lda), device="cuda", generator=g)
+    Bm = torch.randn((batch, K, ldb), device="cuda", generator=g)
+    Cm = torch.full((batch, M, ldc), -7.0, device="cuda")
+    from logos_b200.engine import _ptr
+    engine._check(engine.lib.logos_gemm_f32(engine.h, _ptr(A), lda, M * lda, _ptr(Bm), ldb, K * ldb, _ptr(Cm), ldc,
+                                            M * ldc, M, N, K, batch))
+    engine.synchronize()
+    want = (A[:, :, :K].double() @ Bm[:, :, :N].double()).float()
+    assert float((Cm[:, :, :N] - want).abs().max()) <= 1e-5 * K ** 0.5 + 1e-6
+    assert bool((Cm[:, :, N:] == -7.0).all())                     # the padding of C is not touched
+    # stride 0: one A for the whole batch
+    engine._check(engine.lib.logos_gemm_f32(engine.h, _ptr(A), lda, 0, _ptr(Bm), ldb, K * ldb, _ptr(Cm), ldc,
+                                            M * ldc, M, N, K, batch))
+    engine.synchronize()
+    want0 = (A[0:1, :, :K].double() @ Bm[:, :, :N].double()).float()
+    assert float((Cm[:, :, :N] - want0).abs().max()) <= 1e-5 * K ** 0.5 + 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_kv_dequantize16_is_the_rounded_fp32_product(engine, dtype):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    n, S_max, rows = 6, 96, 80
+    q = torch.randint(-127, 128, (n, S_max, 64), device="cuda", generator=g, dtype=torch.int8)
+    scales = torch.rand((n,), device="cuda", generator=g) * 0.05 + 1e-3
+    got = engine.nikhilam_decompress16(q, scales, dtype, rows=rows)
+    want32 = engine.nikhilam_decompress(q, scales, rows=rows)
+    engine.synchronize()
+    assert torch.equal(got, want32.to(dtype))
