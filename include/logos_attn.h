@@ -138,6 +138,21 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
                         const logos_attn_params* params);
 size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
 
+/* Attention backward: dQ, dK, dV of logos_attention_fwd's output with respect to its raw Q, K, V, for the
+ * gradient dO of that output; all tensors fp32 [B][H][S][DH], DH 32, 64 or 128, 16-byte aligned.
+ * Replaces, for all heads at once and without any seq x seq buffer, the per-head chain of
+ * run_backward (cuda/train_gpu.cu:657-748: recompute of the probabilities, attn_dV_kernel,
+ * attn_dAttnProbs_kernel, softmax_bwd_kernel, attn_dQ_kernel, attn_dK_kernel, :422-481) together with
+ * ns_diffuse_bwd_kernel and ns_advect_bwd_kernel (cuda/ModelGPU.cu:453-482).  `params` is the forward's:
+ * the mask that was applied in the forward is applied here (the reference's recompute uses the causal
+ * mask whatever the forward did), every diffuse_mode and 0 < ns_alpha < 1 included.  Sums have a fixed
+ * order: the result is reproducible bit for bit.  Workspace from the context
+ * (logos_attention_bwd_workspace_bytes / logos_ctx_reserve). */
+size_t logos_attention_bwd_workspace_bytes(int B, int H, int S, int DH);
+int logos_attention_bwd(logos_ctx* ctx, const float* Q, const float* K, const float* V, const float* dO,
+                        float* dQ, float* dK, float* dV, int B, int H, int S, int DH,
+                        const logos_attn_params* params);
+
 /* Prefill of one layer in one call: logos_attention_fwd, and before it -- when k_cache is non-NULL --
  * the layer's INT8 cache filled from the raw K and V.  This is the order of ModelGPU::forward, which
  * quantises a head's K and V (cuda/ModelGPU.cu:908) before the Navier-Stokes prologue and the attention

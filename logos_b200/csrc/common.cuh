@@ -191,6 +191,9 @@ int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*,
                 const float* absmax_known = nullptr);
 int project(logos_ctx*, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual, void* C,
             int M, int N, int K);
+size_t attention_bwd_workspace_bytes(int B, int H, int S, int DH);
+int attention_bwd(logos_ctx*, const float* Q, const float* K, const float* V, const float* dO, float* dQ, float* dK,
+                  float* dV, int B, int H, int S, int DH, const logos_attn_params*);
 int gemm_f32(logos_ctx*, const float* A, int lda, int64_t strideA, const float* B, int ldb, int64_t strideB, float* C,
              int ldc, int64_t strideC, int M, int N, int K, int batch);
 int project_heads(logos_ctx*, int dtype, int out_dtype, const void* head_out, const void* Wt, const void* residual,

@@ -117,6 +117,17 @@ class Engine:
                                           _ptr(out), M, N, K))
         return out
 
+    def attention_bwd(self, Q, K, V, dO, params: L.Params):
+        """Gradients (dQ, dK, dV) of attention(Q, K, V, params) for the output gradient dO; fp32 [B, H, S, DH]."""
+        B, H, S, DH = Q.shape
+        for t in (Q, K, V, dO):
+            assert t.dtype == torch.float32 and t.is_contiguous() and t.shape == Q.shape
+        self.reserve(self.lib.logos_attention_bwd_workspace_bytes(B, H, S, DH))
+        dQ, dK, dV = (torch.empty_like(Q) for _ in range(3))
+        self._check(self.lib.logos_attention_bwd(self.h, _ptr(Q), _ptr(K), _ptr(V), _ptr(dO), _ptr(dQ), _ptr(dK),
+                                                _ptr(dV), B, H, S, DH, C.byref(params)))
+        return dQ, dK, dV
+
     def project_heads(self, head_out, Wt_o, residual=None, out_dtype=None, out=None):
         """head_out: [B, H, S, 64] as the attention wrote it; Wt_o: [N, H*64] -> sum over heads of
         head_out[b, h] · W_O[h] (+ residual), [B*S, N].  No per-token concatenation is made."""

@@ -85,6 +85,8 @@ SIGNATURES = {
     "logos_qkv_project": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "logos_project_heads": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_kv_dequantize16": (_i, [_vp, _i, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
+    "logos_attention_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_mha_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_mha_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "logos_mha_forward_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _PP, _i, _vp, _sz]),

@@ -47,7 +47,7 @@ def build(force: bool = False) -> None:
         subprocess.check_call(["make", "-C", HERE, "oracle"], stdout=subprocess.DEVNULL)
     ref_tree = os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
     if os.path.isdir(os.path.join(ref_tree, "include")):
-        subprocess.check_call(["make", "-C", HERE, "ref", "refgpu"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", HERE, "ref", "refgpu", "refbwd"], stdout=subprocess.DEVNULL)
         if os.path.exists(os.path.join(HERE, "..", "logos_b200", "liblogos_attn_shim.so")):
             subprocess.check_call(["make", "-C", HERE, "refmodel"], stdout=subprocess.DEVNULL)
 
@@ -74,6 +74,8 @@ def lib() -> C.CDLL:
     L.lo_allowed.restype = C.c_int
     L.lo_attention_rows_f64.argtypes = [f32p, f32p, f32p, f32p, C.c_int, C.c_int, C.c_int,
                                         C.c_int, C.POINTER(AttnParams)]
+    L.lo_attention_bwd_f64.argtypes = [f32p, f32p, f32p, f32p, C.c_int, C.c_int, C.POINTER(AttnParams), f32p, f32p,
+                                       f32p]
     L.lo_absmax.argtypes = [f32p, C.c_long]
     L.lo_absmax.restype = C.c_float
     L.lo_nikhilam_scale.argtypes = [C.c_float]
@@ -229,3 +231,16 @@ def decode_int8_batch(q, q_prev, Kq, Vq, k_scale, v_scale, lens, p: AttnParams, 
                                np.ascontiguousarray(lens, np.int32), n, s_max, d, C.byref(p), out,
                                threads or lib().lo_max_threads())
     return out
+
+
+def attention_bwd(Q, K, V, dO, p: AttnParams):
+    """Gradients (dQ, dK, dV) of attention_batched's output with respect to Q, K, V ([B, H, S, d] fp32) for
+    a given dO, fp64 inside (lo_attention_bwd_f64)."""
+    Q, K, V, dO = (_f(a) for a in (Q, K, V, dO))
+    B, H, S, d = Q.shape
+    dQ, dK, dV = (np.empty_like(Q) for _ in range(3))
+    fn = lib().lo_attention_bwd_f64
+    for b in range(B):
+        for h in range(H):
+            fn(Q[b, h], K[b, h], V[b, h], dO[b, h], S, d, C.byref(p), dQ[b, h], dK[b, h], dV[b, h])
+    return dQ, dK, dV

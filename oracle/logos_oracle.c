@@ -317,6 +317,110 @@ void lo_attention_rows_f64(const float* Q, const float* K, const float* V, float
 }
 
 /* ------------------------------------------------------------------ */
+/* Attention backward: cuda/train_gpu.cu:657-748 (one head), with the    */
+/* adjoints of the prologue from cuda/ModelGPU.cu:453-482.               */
+
+/* One path (queries qx, values vx already advected / diffused), weight w on d_out:
+ *   p      = softmax over the allowed keys of scale * qx_i . k_j        (recompute, train_gpu.cu:671-701)
+ *   dvx_j += p_ij d_out_i                                                (attn_dV_kernel :422-432)
+ *   dp_ij  = d_out_i . vx_j                                              (attn_dAttnProbs_kernel :434-444)
+ *   ds_ij  = p_ij (dp_ij - sum_j p_ij dp_ij) scale                       (softmax_bwd_kernel :446-459)
+ *   dqx_i += ds_ij k_j ;  dk_j += ds_ij qx_i                             (attn_dQ_kernel, attn_dK_kernel :461-481)
+ * Unlike the reference's recompute, which applies the causal mask only, the mask is the one the
+ * forward used (Shunyam window and landmarks included): the gradient of the forward that was run. */
+static void bwd_path(const float* qx, const float* K, const float* vx, const float* dO, int seq, int d,
+                     const lo_attn_params* p, double w, double* dqx, double* dk, double* dvx) {
+    double* sc = (double*)malloc(sizeof(double) * (size_t)seq);
+    double* dp = (double*)malloc(sizeof(double) * (size_t)seq);
+    for (int i = 0; i < seq; ++i) {
+        const float* q = qx + (size_t)i * d;
+        const float* g = dO + (size_t)i * d;
+        double mx = -INFINITY;
+        for (int j = 0; j < seq; ++j) {
+            if (!lo_allowed(i, j, seq, p)) { sc[j] = -INFINITY; continue; }
+            double s = 0.0;
+            for (int c = 0; c < d; ++c) s += (double)q[c] * (double)K[(size_t)j * d + c];
+            sc[j] = s * (double)p->scale;
+            if (sc[j] > mx) mx = sc[j];
+        }
+        double l = 0.0;
+        for (int j = 0; j < seq; ++j) if (sc[j] != -INFINITY) { sc[j] = exp(sc[j] - mx); l += sc[j]; } else sc[j] = 0.0;
+        if (!(l > 1e-9)) continue;            /* the forward wrote zeros for this row */
+        double delta = 0.0;
+        for (int j = 0; j < seq; ++j) {
+            if (sc[j] == 0.0) { dp[j] = 0.0; continue; }
+            sc[j] /= l;
+            double t = 0.0;
+            for (int c = 0; c < d; ++c) t += w * (double)g[c] * (double)vx[(size_t)j * d + c];
+            dp[j] = t;
+            delta += sc[j] * t;
+        }
+        for (int j = 0; j < seq; ++j) {
+            if (sc[j] == 0.0) continue;
+            double ds = sc[j] * (dp[j] - delta) * (double)p->scale;
+            for (int c = 0; c < d; ++c) {
+                dvx[(size_t)j * d + c] += sc[j] * w * (double)g[c];
+                dqx[(size_t)i * d + c] += ds * (double)K[(size_t)j * d + c];
+                dk[(size_t)j * d + c] += ds * (double)q[c];
+            }
+        }
+    }
+    free(sc); free(dp);
+}
+
+void lo_attention_bwd_f64(const float* Q, const float* K, const float* V, const float* dO, int seq, int d,
+                          const lo_attn_params* p, float* dQ, float* dK, float* dV) {
+    size_t n = (size_t)seq * d;
+    int ns_on = (p->ns_alpha > 0.0f) && (p->ns_eta != 0.0f || p->diffuse_mode != LO_DIFFUSE_NONE);
+    int std_on = !ns_on || p->ns_alpha < 1.0f;
+    double* aq = (double*)calloc(n, sizeof(double));   /* gradients with respect to the raw Q, K, V */
+    double* ak = (double*)calloc(n, sizeof(double));
+    double* av = (double*)calloc(n, sizeof(double));
+    if (ns_on) {
+        float* qa = (float*)malloc(sizeof(float) * n);
+        float* vs = (float*)malloc(sizeof(float) * n);
+        double* dqa = (double*)calloc(n, sizeof(double));
+        double* dvs = (double*)calloc(n, sizeof(double));
+        lo_ns_advect(Q, qa, seq, d, p->ns_eta);
+        if (p->diffuse_mode == LO_DIFFUSE_CAUSAL) lo_ns_diffuse_causal(V, vs, seq, d, p->ns_nu);
+        else if (p->diffuse_mode == LO_DIFFUSE_CENTRAL) lo_ns_diffuse_central(V, vs, seq, d, p->ns_nu);
+        else memcpy(vs, V, sizeof(float) * n);
+        bwd_path(qa, K, vs, dO, seq, d, p, (double)p->ns_alpha, dqa, ak, dvs);
+        double eta = (double)p->ns_eta, nu = (double)p->ns_nu;
+        for (int i = 0; i < seq; ++i)
+            for (int c = 0; c < d; ++c) {
+                size_t x = (size_t)i * d + c;
+                /* ns_advect_bwd_kernel, cuda/ModelGPU.cu:453-461 */
+                double g = dqa[x] * ((i == 0) ? 1.0 : (1.0 + eta));
+                if (i + 1 < seq) g -= eta * dqa[x + d];
+                aq[x] += g;
+                if (p->diffuse_mode == LO_DIFFUSE_CAUSAL) {
+                    /* ns_diffuse_bwd_kernel, cuda/ModelGPU.cu:473-482 */
+                    double h = (1.0 - nu) * dvs[x];
+                    if (i + 1 < seq) h += nu * dvs[x + d];
+                    if (i == 0) h += nu * dvs[x];
+                    av[x] += h;
+                } else if (p->diffuse_mode == LO_DIFFUSE_CENTRAL) {
+                    /* transpose of the stencil of navier_stokes_attention (include/Attention.hpp:166-182):
+                     * row j reads max(j-1, 0) and min(j+1, seq-1) */
+                    double h = (1.0 - nu) * dvs[x];
+                    if (i + 1 < seq) h += 0.5 * nu * dvs[x + d];      /* row i+1 reads i as its left */
+                    if (i == 0) h += 0.5 * nu * dvs[x];               /* row 0 reads itself as its left */
+                    if (i > 0) h += 0.5 * nu * dvs[x - d];            /* row i-1 reads i as its right */
+                    if (i == seq - 1) h += 0.5 * nu * dvs[x];         /* the last row reads itself as its right */
+                    av[x] += h;
+                } else {
+                    av[x] += dvs[x];
+                }
+            }
+        free(qa); free(vs); free(dqa); free(dvs);
+    }
+    if (std_on) bwd_path(Q, K, V, dO, seq, d, p, ns_on ? 1.0 - (double)p->ns_alpha : 1.0, aq, ak, av);
+    for (size_t x = 0; x < n; ++x) { dQ[x] = (float)aq[x]; dK[x] = (float)ak[x]; dV[x] = (float)av[x]; }
+    free(aq); free(ak); free(av);
+}
+
+/* ------------------------------------------------------------------ */
 /* Nikhilam INT8: cuda/ModelGPU.cu:293-395                             */
 
 float lo_absmax(const float* x, long n) {

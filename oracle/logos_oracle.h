@@ -110,6 +110,12 @@ int lo_allowed(int i, int j, int seq, const lo_attn_params* p);
 void lo_attention_rows_f64(const float* Q, const float* K, const float* V, float* out,
                            int seq, int d, int row0, int row1, const lo_attn_params* p);
 
+/* Gradients of one head's attention (the function above, all rows) with respect to the raw Q, K, V for a
+ * given d_out [seq x d]: the chain of cuda/train_gpu.cu:657-748 (dV, dP, softmax backward, dQ, dK) and the
+ * adjoints of the prologue, cuda/ModelGPU.cu:453-482, in fp64; the mask is the forward's own. */
+void lo_attention_bwd_f64(const float* Q, const float* K, const float* V, const float* dO, int seq, int d,
+                          const lo_attn_params* p, float* dQ, float* dK, float* dV);
+
 /* ---- Nikhilam INT8 KV: cuda/ModelGPU.cu:293-395 ---- */
 
 float lo_absmax(const float* x, long n);                 /* absmax_kernel :308-326 */

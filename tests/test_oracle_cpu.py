@@ -218,3 +218,26 @@ def test_decode_composition_matches_last_row():
             full = O.attention_rows(Q, O.nikhilam_dequantize(Kq, ks), O.nikhilam_dequantize(Vq, vs), p)
             got = O.decode_int8_batch(Q[-1:], Q[-2:-1], Kq[None], Vq[None], [ks], [vs], [n], p)
             assert np.abs(got[0] - full[-1]).max() < 1e-6
+
+
+def test_backward_oracle_is_the_gradient_of_the_forward_oracle():
+    """lo_attention_bwd_f64 pinned by central differences of the (reference-pinned) forward oracle: every
+    diffusion stencil, the blend, the Shunyam mask with and without landmarks, and no causal mask."""
+    rng = np.random.default_rng(7)
+    S, d = 20, 8
+    cases = [(0, 0, 0.0, 0.0, 1.0, 0, True), (0, 0, 0.1, 0.05, 1.0, 1, True), (0, 0, 0.1, 0.05, 1.0, 2, True),
+             (6, 4, 0.1, 0.05, 0.3, 1, True), (6, 0, 0.2, 0.1, 0.6, 2, True), (0, 0, 0.1, 0.05, 1.0, 1, False)]
+    for (w, st, eta, nu, alpha, mode, causal) in cases:
+        p = O.attn_params(0.35, causal, w, st, eta, nu, alpha, mode)
+        Q, K, V, dO = (rng.standard_normal((1, 1, S, d)).astype(np.float32) for _ in range(4))
+        dQ, dK, dV = O.attention_bwd(Q, K, V, dO, p)
+        f = lambda: float((O.attention_batched(Q, K, V, p).astype(np.float64) * dO).sum())
+        for X, G in ((Q, dQ), (K, dK), (V, dV)):
+            for _ in range(8):
+                i = tuple(int(rng.integers(0, n)) for n in X.shape)
+                old, h = X[i], 1e-2
+                X[i] = old + h; fp = f()
+                X[i] = old - h; fm = f()
+                X[i] = old
+                num = (fp - fm) / (2 * h)
+                assert abs(num - G[i]) <= 2e-3 * (abs(num) + 1e-2), (w, st, mode, alpha, i, num, G[i])
