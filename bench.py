@@ -438,6 +438,69 @@ def measure_projection(eng, dev, batch, steps, warmup) -> dict:
             "max_abs_err_vs_fp64_product": float((got - want).abs().max())}
 
 
+def measure_backward(eng, dev, steps, warmup) -> dict:
+    """Attention backward at the prefill configuration's shape (B 4, H 16, S 4096, DH 64, fp32, causal with the
+    Navier-Stokes prologue): dQ, dK, dV for a given dO.  Flops counted as the five products of the chain over the
+    causal half (2.5 x the forward's); checked against the fp64 backward oracle on one short head first."""
+    import numpy as np
+    import torch
+    import oracle as O
+    from logos_b200 import lib as L
+    p = L.Params.make(0.125, True, 0, 0, ETA, NU, 1.0, L.DIFFUSE_CAUSAL)
+    g = torch.Generator(device=dev).manual_seed(91)
+    small = [torch.randn((1, 1, 384, DH), device=dev, generator=g) for _ in range(4)]
+    got = eng.attention_bwd(*small, p)
+    want = O.attention_bwd(*(t.cpu().numpy() for t in small), O.attn_params(0.125, True, 0, 0, ETA, NU, 1.0, 1))
+    err = max(float(np.abs(a.cpu().numpy() - b).max()) for a, b in zip(got, want))
+    Bq, S = 4, 4096
+    Q, K, V, dO = (torch.randn((Bq, H, S, DH), device=dev, generator=g) for _ in range(4))
+    for _ in range(warmup):
+        eng.attention_bwd(Q, K, V, dO, p)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(steps):
+        eng.attention_bwd(Q, K, V, dO, p)
+    ev[1].record()
+    eng.synchronize()
+    ms = ev[0].elapsed_time(ev[1]) / steps
+    flops = 2.5 * 4.0 * Bq * H * S * S * DH / 2
+    out = {"workload": f"attention_bwd_b{Bq}_h{H}_s{S}_dh{DH}_f32", "ms_per_step": ms,
+           "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (causal-halved, 5 products)", "bound": "fp32 FMA pipe",
+           "max_abs_err_vs_oracle": err,
+           "note": "exact fp32 arithmetic on the FMA pipe (no tensor cores): a first path for a row outside the forward hot path"}
+    # the reference's own chain for one head at a length its seq x seq buffers allow
+    path = os.path.join(os.path.dirname(os.path.abspath(O.__file__)), "_ref", "liblogos_refbwd.so")
+    if os.path.exists(path):
+        import ctypes as C
+        ref = C.CDLL(path)
+        ref.refbwd_attention_head.argtypes = [C.c_void_p] * 7 + [C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p, C.c_int]
+        Sr = 2048
+        q, k, v, do = (t[0, 0, :Sr].contiguous() for t in (Q, K, V, dO))
+        dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+        scratch = torch.empty(3 * Sr * Sr + 3 * Sr * DH, dtype=torch.float32, device=dev)
+        vp = lambda t: C.c_void_p(t.data_ptr())
+        call = lambda: ref.refbwd_attention_head(vp(q), vp(k), vp(v), vp(do), vp(dq), vp(dk), vp(dv), Sr, DH, ETA, NU,
+                                                 vp(scratch), 1)
+        torch.cuda.synchronize()
+        call()
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(3):
+            call()
+        ev[1].record()
+        torch.cuda.synchronize()
+        ref_ms = ev[0].elapsed_time(ev[1]) / 3
+        one = [t[:1, :1, :Sr].contiguous() for t in (Q, K, V, dO)]
+        eng.attention_bwd(*one, p)
+        ev[0].record()
+        for _ in range(3):
+            eng.attention_bwd(*one, p)
+        ev[1].record()
+        eng.synchronize()
+        out["one_head_s2048"] = {"reference_backward_chain_ms": ref_ms, "engine_ms": ev[0].elapsed_time(ev[1]) / 3}
+    return out
+
+
 def reference_gpu_kernels(eng, dev) -> list:
     """One head of the prefill and of the window configuration through the reference's own CUDA path
     (ns_advect_kernel + ns_diffuse_kernel + cuda_flash_attention_fwd, compiled unmodified for sm_100a)
@@ -557,6 +620,14 @@ def run_ours(args) -> None:
                           "max_abs_err_vs_fp64_product": r["max_abs_err_vs_fp64_product"],
                           "roofline": {"bound": "tensor", "achieved": r["value"], "peak": r["peak"], "peak_kind": r["peak_kind"],
                                        "frac": r["frac"], "traffic": None}, "gpu_launches": args.steps}))
+        finish()
+        return
+
+    if args.workload == "bwd":
+        r = measure_backward(eng, dev, max(3, args.steps // 4), 3)
+        print(json.dumps({"metric": r["workload"], "value": r["value"], "unit": r["unit"], "n_gpus": 1, "higher_is_better": True,
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": r["workload"]},
+                          "detail": r}))
         finish()
         return
 
@@ -728,6 +799,7 @@ def run_ours(args) -> None:
         line["stack"] = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
         if world == 1:
             line["secondary"].append(measure_projection(eng, dev, 32, 5, 3))
+            line["secondary"].append(measure_backward(eng, dev, 3, 2))
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["baselines"] = {"reference_gpu_kernels_on_this_gpu": reference_gpu_kernels(eng, dev),
                              "configuration_1_reference_cpu_forward": configuration1_cpu_baseline()}
@@ -747,7 +819,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU legs and the reference's GPU kernels")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack", "qkv"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack", "qkv", "bwd"],
                     help="decode is the benchmark; the others time one attention kernel alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")

@@ -216,7 +216,10 @@ int logos_kv_append(logos_ctx* ctx, int dtype, const void* k_new, const void* v_
  * [B][H][DH] (q_prev = the previous token's query, needed by the advection term;
  * may be NULL when ns_eta == 0).  out: FP32 [B][H][DH].  Replaces the full
  * re-forward per generated token of cuda/train_gpu.cu:2037-2046; numerically it
- * is nikhilam_decompress + ns kernels + the last row of cuda_flash_attention_fwd. */
+ * is nikhilam_decompress + ns kernels + the last row of cuda_flash_attention_fwd.
+ * DH = 64 (the model's) runs the split-K kernels; any other multiple of 16 up to 128 (the reference's
+ * attention takes DH <= 128, cuda/VedicGEMM.cu:899) runs a general fp32 kernel, one CTA per (b,h), with
+ * the context bounded by shared memory (S_max <= about 50 000, half of that when 0 < ns_alpha < 1). */
 int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
                       const int8_t* v_cache, const float* k_scale, const float* v_scale,
                       const int32_t* len, int B, int H, int S_max, int DH,

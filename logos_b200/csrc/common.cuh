@@ -191,6 +191,8 @@ int kv_quantize(logos_ctx*, int, const void*, int64_t, int8_t*, int64_t, float*,
                 const float* absmax_known = nullptr);
 int project(logos_ctx*, int dtype, int out_dtype, const void* A, const void* Wt, const void* residual, void* C,
             int M, int N, int K);
+int decode_generic(logos_ctx*, const void* q, const void* q_prev, const int8_t*, const int8_t*, const float*,
+                   const float*, const int32_t* len, int B, int H, int S_max, int DH, const logos_attn_params*, float* out);
 size_t attention_bwd_workspace_bytes(int B, int H, int S, int DH);
 int attention_bwd(logos_ctx*, const float* Q, const float* K, const float* V, const float* dO, float* dQ, float* dK,
                   float* dV, int B, int H, int S, int DH, const logos_attn_params*);

@@ -773,13 +773,14 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
     if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || (!out && !peer) || !p || B <= 0 ||
         H <= 0 || S_max <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad pointer or extent");
-    if (DH != kDH) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: DH must be 64, got %d", DH);
     if (!aligned16(k_cache) || !aligned16(v_cache))
         return fail(ctx, LOGOS_ERR_ALIGNMENT, "decode_int8: caches must be 16-byte aligned");
     if (p->diffuse_mode < 0 || p->diffuse_mode > 2)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad diffuse_mode");
     if (p->ns_eta != 0.0f && p->ns_alpha > 0.0f && !q_prev)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: q_prev is required when ns_eta != 0");
+    if (DH != kDH)       // the head dimensions the model does not use: the general kernel
+        return decode_generic(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, p, out);
     const int BH = B * H;
     if ((size_t)BH * sizeof(unsigned int) > kCounterBytes)
         return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: more than 16384 (b,h) pairs");

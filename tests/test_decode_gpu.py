@@ -14,9 +14,8 @@ pytestmark = pytest.mark.gpu
 MODES = [L.DIFFUSE_NONE, L.DIFFUSE_CAUSAL, L.DIFFUSE_CENTRAL]
 
 
-def make_cache(B, H, S_max, lens, seed):
+def make_cache(B, H, S_max, lens, seed, DH=64):
     """Pre-quantization K/V ~ N(0,1) with 1 % x8 outliers, quantized per (b,h) over the valid rows."""
-    DH = 64
     k = syn.normal_with_outliers((B, H, S_max, DH), seed, 1)
     v = syn.normal_with_outliers((B, H, S_max, DH), seed, 2)
     kq = np.zeros((B, H, S_max, DH), np.int8)
@@ -31,10 +30,9 @@ def make_cache(B, H, S_max, lens, seed):
     return kq, vq, ks, vs
 
 
-def run_case(engine, B, H, S_max, lens, params, seed, tight=2e-5):
-    DH = 64
+def run_case(engine, B, H, S_max, lens, params, seed, tight=2e-5, DH=64):
     lens = np.asarray(lens, np.int32)
-    kq, vq, ks, vs = make_cache(B, H, S_max, lens, seed)
+    kq, vq, ks, vs = make_cache(B, H, S_max, lens, seed, DH)
     q = syn.normal((B, H, DH), seed, 3).astype(np.float16)
     qp = syn.normal((B, H, DH), seed, 4).astype(np.float16)
     engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
@@ -166,10 +164,24 @@ def test_argument_errors(engine):
     bad = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, 7)
     with pytest.raises(L.LogosError):
         engine.decode_int8(q, q, z8, z8, one, one, lens, bad)
-    z8_32 = torch.zeros((B, H, S, 32), dtype=torch.int8, device="cuda")
+    z8_24 = torch.zeros((B, H, S, 24), dtype=torch.int8, device="cuda")     # not a multiple of 16
     with pytest.raises(L.LogosError) as e:
-        engine.decode_int8(q, q, z8_32, z8_32, one, one, lens, p)
+        engine.decode_int8(q[..., :24].contiguous(), q[..., :24].contiguous(), z8_24, z8_24, one, one, lens, p)
     assert e.value.status == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("DH", [16, 32, 96, 128])
+def test_other_head_dimensions(engine, DH):
+    """Head dimensions the model does not use (the reference's attention takes any DH <= 128): the general
+    kernel, every switch, ragged lengths, against the same oracle."""
+    sc = 1.0 / np.sqrt(DH)
+    for mode in MODES:
+        p = L.Params.make(sc, True, 0, 0, 0.1, 0.05, 1.0, mode)
+        run_case(engine, 3, 2, 300, [1, 2, 300], p, seed=400 + DH + mode, DH=DH)
+    run_case(engine, 2, 2, 700, [700, 333], L.Params.make(sc, True, 0, 0, 0.1, 0.05, 0.3, L.DIFFUSE_CENTRAL), seed=410 + DH, DH=DH)
+    run_case(engine, 2, 2, 600, [600, 64], L.Params.make(sc, True, 64, 16, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL), seed=420 + DH, DH=DH)
+    run_case(engine, 1, 2, 600, [599], L.Params.make(sc, True, 32, 0, 0.1, 0.05, 0.6, L.DIFFUSE_CAUSAL), seed=430 + DH, DH=DH)
+    run_case(engine, 1, 1, 4096, [4096], L.Params.make(sc, True, 0, 0, 0.0, 0.0, 1.0, L.DIFFUSE_NONE), seed=440 + DH, DH=DH)
 
 
 def test_decode_step_replayed_as_cuda_graph(engine):
