@@ -111,9 +111,12 @@ const char* logos_last_error(const logos_ctx* ctx);
  *   LOGOS_OPT_WORKSPACE_LOCK 1: logos_ctx_reserve / logos_ctx_set_workspace calls that would replace
  *                            the workspace fail with LOGOS_ERR_WORKSPACE.  A CUDA graph captured from
  *                            decode calls holds the workspace's address: lock it for as long as such
- *                            a graph can still be launched. */
+ *                            a graph can still be launched.
+ *   LOGOS_OPT_GEMM_NARROW    1: the projections always take the 128 x 128-tile kernel; 0 (default): the
+ *                            persistent 128 x 256-tile kernel whenever the problem fills the device.
+ *                            The two give bit-identical results (same products, same order of k). */
 typedef enum { LOGOS_OPT_FORCE_GENERAL = 0, LOGOS_OPT_DECODE_CHUNK = 1, LOGOS_OPT_PEER_WAIT_MS = 2,
-               LOGOS_OPT_WORKSPACE_LOCK = 3 } logos_option;
+               LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4 } logos_option;
 int logos_ctx_set_option(logos_ctx* ctx, int option, int value);
 
 /* ---- attention ---------------------------------------------------------- */

@@ -238,6 +238,9 @@ int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
         case LOGOS_OPT_WORKSPACE_LOCK:
             ctx->workspace_locked = value != 0;
             return LOGOS_OK;
+        case LOGOS_OPT_GEMM_NARROW:
+            ctx->gemm_narrow = value != 0;
+            return LOGOS_OK;
     }
     return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: unknown option %d", option);
 }

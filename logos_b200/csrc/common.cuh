@@ -26,6 +26,7 @@ struct logos_ctx {
     int decode_chunk = 0;             // LOGOS_OPT_DECODE_CHUNK: 0 = chosen from the problem size
     int peer_wait_ms = 2000;          // LOGOS_OPT_PEER_WAIT_MS
     bool workspace_locked = false;    // LOGOS_OPT_WORKSPACE_LOCK
+    bool gemm_narrow = false;         // LOGOS_OPT_GEMM_NARROW
     logos_alloc_fn alloc_fn = nullptr;   // caller's allocator for the workspace (null: cudaMalloc / cudaFree)
     logos_free_fn free_fn = nullptr;
     void* alloc_user = nullptr;

@@ -19,6 +19,8 @@
 //   warp 1    MMA issuer (one elected lane): four M128 N128 K16 MMAs per stage into 128 TMEM columns;
 //   warps 2-5 epilogue: one thread per output row reads its 128 accumulator columns from TMEM.
 // Every mbarrier wait is bounded; a wait that runs out raises the context's status word.
+#include <algorithm>
+
 #include "tcgen05_ptx.cuh"
 
 namespace logos {
@@ -58,6 +60,96 @@ __device__ __forceinline__ uint32_t pack16(float x, float y, bool f16) {
 }
 __device__ __forceinline__ float round16(float x, bool f16) {
     return f16 ? __half2float(__float2half_rn(x)) : __bfloat162float(__float2bfloat16_rn(x));
+}
+
+// ---- epilogue pieces, shared by the two kernels; the calling thread owns output row m ----
+
+// 32 accumulator columns starting at TMEM address t_addr -> C[m][n .. n+31] (+ residual)
+__device__ __forceinline__ void store_c_chunk(const GemmArgs& a, uint32_t t_addr, int m, int n, bool live) {
+    const bool f16 = a.f16 != 0;
+    float v[32];
+    tc_ld32(t_addr, v);
+    tc_wait_ld();
+    if (!live || n >= a.N) return;                 // N is a multiple of 32
+    const size_t off = (size_t)m * a.N + n;
+    if (a.c_is_f32) {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C) + off);
+        const float4* res = a.R ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.R) + off) : nullptr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float4 r4 = res ? res[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+            dst[j] = make_float4(v[4 * j] + r4.x, v[4 * j + 1] + r4.y, v[4 * j + 2] + r4.z, v[4 * j + 3] + r4.w);
+        }
+    } else {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.C) + off);
+        const uint4* res = a.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.R) + off) : nullptr;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+            uint4 r4 = res ? res[j] : make_uint4(0, 0, 0, 0);
+            const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
+                if (res) {
+                    if (f16) {
+                        float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
+                        x += rr.x; y += rr.y;
+                    } else {
+                        x += __uint_as_float(rw[e] << 16); y += __uint_as_float(rw[e] & 0xffff0000u);
+                    }
+                }
+                w[e] = pack16(x, y, f16);
+            }
+            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// 64 accumulator columns = one (projection, head) slice: scatter into Q, K or V [B][H][S][64] and reduce
+// max|x| of the stored (rounded) K or V values per (sequence, head) tensor
+__device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t_addr, int m, int n, bool row_live,
+                                                   int lane) {
+    const bool f16 = a.f16 != 0;
+    const int b = m / a.S, s = m - b * a.S;
+    const int hg = n / 64;                           // head slot among 3 H
+    const int which = hg / a.H, h = hg - which * a.H;
+    float amax = 0.0f;
+    unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.q : (which == 1 ? a.k : a.v));
+    const bool live = row_live && which < 3;
+    uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)b * a.H + h) * a.S + s) * 64);
+#pragma unroll 1
+    for (int hc = 0; hc < 2; ++hc) {
+        float v[32];
+        tc_ld32(t_addr + 32 * hc, v);
+        tc_wait_ld();
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
+                    w[e] = pack16(x, y, f16);
+                    amax = fmaxf(amax, fmaxf(fabsf(round16(x, f16)), fabsf(round16(y, f16))));
+                }
+                dst[4 * hc + j] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    // one atomic per warp when its 32 rows lie in one sequence, else one per row; non-negative floats order
+    // like integers
+    unsigned* tgt = which == 1 ? a.k_absmax : (which == 2 ? a.v_absmax : nullptr);
+    if (tgt) {
+        const int b_first = __shfl_sync(0xffffffffu, b, 0), b_last = __shfl_sync(0xffffffffu, b, 31);
+        const bool all_live = __all_sync(0xffffffffu, live);
+        if (b_first == b_last && all_live) {
+            amax = warp_max(amax);
+            if (lane == 0) atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
+        } else if (live) {
+            atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kGThreads, 2)
@@ -139,96 +231,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane, m = m0 + row;
         const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16);
-        const bool f16 = a.f16 != 0;
         if (mbar_wait(acc_full, 0, abort_flag)) {
             tc_fence_after();
             if (a.mode == 0) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < kGN; c0 += 32) {
-                    float v[32];
-                    tc_ld32(t_row + c0, v);
-                    tc_wait_ld();
-                    const int n = n0 + c0;
-                    if (m < m_lim && n < a.N) {        // N is a multiple of 32
-                        const size_t off = (size_t)m * a.N + n;
-                        if (a.c_is_f32) {
-                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C) + off);
-                            const float4* res = a.R ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.R) + off) : nullptr;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                float4 r4 = res ? res[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-                                dst[j] = make_float4(v[4 * j] + r4.x, v[4 * j + 1] + r4.y, v[4 * j + 2] + r4.z, v[4 * j + 3] + r4.w);
-                            }
-                        } else {
-                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.C) + off);
-                            const uint4* res = a.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.R) + off) : nullptr;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint32_t w[4];
-                                uint4 r4 = res ? res[j] : make_uint4(0, 0, 0, 0);
-                                const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r4);
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
-                                    if (res) {
-                                        if (f16) {
-                                            float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
-                                            x += rr.x; y += rr.y;
-                                        } else {
-                                            x += __uint_as_float(rw[e] << 16); y += __uint_as_float(rw[e] & 0xffff0000u);
-                                        }
-                                    }
-                                    w[e] = pack16(x, y, f16);
-                                }
-                                dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        }
-                    }
-                }
+                for (int c0 = 0; c0 < kGN; c0 += 32) store_c_chunk(a, t_row + c0, m, n0 + c0, m < m_lim);
             } else {
-                // Q, K, V scatter: the tile's two 64-column groups are two (projection, head) slices
-                const int b = m / a.S, s = m - b * a.S;
 #pragma unroll 1
-                for (int gi = 0; gi < 2; ++gi) {
-                    const int hg = (n0 + 64 * gi) / 64;              // head slot among 3 H
-                    const int which = hg / a.H, h = hg - which * a.H;
-                    float amax = 0.0f;
-                    unsigned short* base = reinterpret_cast<unsigned short*>(which == 0 ? a.q : (which == 1 ? a.k : a.v));
-                    const bool live = m < m_lim && which < 3;
-                    uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)b * a.H + h) * a.S + s) * 64);
-#pragma unroll 1
-                    for (int hc = 0; hc < 2; ++hc) {
-                        float v[32];
-                        tc_ld32(t_row + 64 * gi + 32 * hc, v);
-                        tc_wait_ld();
-                        if (live) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
-                                    w[e] = pack16(x, y, f16);
-                                    amax = fmaxf(amax, fmaxf(fabsf(round16(x, f16)), fabsf(round16(y, f16))));
-                                }
-                                dst[4 * hc + j] = make_uint4(w[0], w[1], w[2], w[3]);
-                            }
-                        }
-                    }
-                    // max|x| of the stored (rounded) values per (sequence, head) tensor: one atomic per warp when
-                    // its 32 rows lie in one sequence, else one per row; non-negative floats order like integers
-                    unsigned* tgt = which == 1 ? a.k_absmax : (which == 2 ? a.v_absmax : nullptr);
-                    if (tgt) {
-                        const int b_first = __shfl_sync(0xffffffffu, b, 0), b_last = __shfl_sync(0xffffffffu, b, 31);
-                        const bool all_live = __all_sync(0xffffffffu, live);
-                        if (b_first == b_last && all_live) {
-                            amax = warp_max(amax);
-                            if (lane == 0) atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
-                        } else if (live) {
-                            atomicMax(tgt + (size_t)b * a.H + h, __float_as_uint(amax));
-                        }
-                    }
-                }
+                for (int gi = 0; gi < 2; ++gi) scatter_head_slice(a, t_row + 64 * gi, m, n0 + 64 * gi, m < m_lim, lane);
             }
             tc_fence_before();
         }
@@ -243,13 +253,159 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
 }
 
+// ---- the wide kernel: persistent CTAs, 128 x 256 tiles, two accumulators ----
+//
+// A 128 x 128 MMA reads 8 KiB of operands from shared memory for 64 cycles of tensor-pipe work: that is the
+// whole shared-memory bandwidth of an SM, and it is what holds the kernel above near half of the pipe's
+// peak.  With N = 256 the same A tile feeds twice the columns (12 KiB per 128 cycles).  One CTA per SM walks
+// the tiles (n fastest, so the CTAs running together share A rows and the whole weight stays in L2); the
+// accumulator is double-buffered in tensor memory (2 x 256 columns), so the epilogue warps drain tile t while
+// the MMA warp fills tile t + 1; four stages of 48 KiB keep TMA ahead of the MMAs.
+constexpr int kWN = 256;
+constexpr int kWStages = 4;
+constexpr int kWTileB = kWN * kGK * 2;            // 32 KiB
+constexpr int kWStage = kGTile + kWTileB;         // 48 KiB
+constexpr int kWOffBar = kWStages * kWStage;
+constexpr int kWSmem = kWOffBar + (2 * kWStages + 4) * 8 + 64 + 1024;
+
+__global__ void __launch_bounds__(kGThreads, 1)
+gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const GemmArgs a,
+                    int m_tiles, int n_tiles) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar0 = sbase + kWOffBar;
+    auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(kWStages + s); };
+    auto acc_full = [&](int t) { return bar0 + 8u * (uint32_t)(2 * kWStages + t); };
+    auto acc_empty = [&](int t) { return bar0 + 8u * (uint32_t)(2 * kWStages + 2 + t); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kWOffBar + (2 * kWStages + 4) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kWOffBar + (2 * kWStages + 4) * 8 + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_kb = (a.K + kGK - 1) / kGK;
+    const int total = m_tiles * n_tiles;
+
+    if (warp == 0 && lane == 0) {
+        for (int s = 0; s < kWStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (int t = 0; t < 2; ++t) { mbar_init(acc_full(t), 1); mbar_init(acc_empty(t), 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // rows of m tile mt: m0 .. m0 + 127 below m_lim; head-major A: (row in the sequence, first slab)
+    auto tile_rows = [&](int mt, int& m0, int& m_lim, int& a_row, int& a_slab) {
+        m0 = mt * kBM; m_lim = a.M; a_row = m0; a_slab = 0;
+        if (a.a_heads) {
+            const int tiles = (a.a_S + kBM - 1) / kBM;
+            const int b = mt / tiles;
+            a_row = (mt - b * tiles) * kBM;
+            a_slab = b * a.a_heads;
+            m0 = b * a.a_S + a_row;
+            m_lim = (b + 1) * a.a_S;
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;                                   // k blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+                const int mt = tile / n_tiles, n0 = (tile - mt * n_tiles) * kWN;
+                int m0, m_lim, a_row, a_slab;
+                tile_rows(mt, m0, m_lim, a_row, a_slab);
+                bool ok = true;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % kWStages;
+                    if (!mbar_wait(empty(s), ((it / kWStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(full(s), kWStage);
+                    const uint32_t dst = sbase + s * kWStage;
+                    if (a.a_heads) tma_load_3d(dst, &mapA, 0, a_row, a_slab + kb, full(s));
+                    else           tma_load_3d(dst, &mapA, kb * kGK, m0, 0, full(s));
+                    tma_load_3d(dst + kGTile, &mapW, kb * kGK, n0, 0, full(s));
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        uint32_t elected;
+        asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(elected));
+        const bool leader = elected != 0;
+        const int fmt = a.f16 ? 0 : 1;
+        const uint32_t idesc = instr_desc(fmt, fmt, 0, kWN);
+        uint32_t it = 0, lt = 0;                               // k blocks and tiles done by this CTA
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x, ++lt) {
+            const int acc = lt & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(acc_empty(acc), ((lt >> 1) & 1) ^ 1, abort_flag)) != 0;
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d = tmem + (uint32_t)(acc * kWN);
+            for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                const int s = it % kWStages;
+                ok = __all_sync(0xffffffffu, mbar_wait(full(s), (it / kWStages) & 1, abort_flag)) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                if (leader) {
+                    const uint32_t sa = sbase + s * kWStage, sw = sa + kGTile;
+#pragma unroll
+                    for (int kk = 0; kk < kGK / 16; ++kk)
+                        tc_mma_f16(d, smem_desc(sa + 32 * kk), smem_desc(sw + 32 * kk), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    tc_commit(empty(s));
+                    if (kb == n_kb - 1) tc_commit(acc_full(acc));
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---- epilogue: thread = output row, TMEM lane quarter = warp % 4 ----
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        uint32_t lt = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++lt) {
+            const int mt = tile / n_tiles, n0 = (tile - mt * n_tiles) * kWN;
+            int m0, m_lim, a_row, a_slab;
+            tile_rows(mt, m0, m_lim, a_row, a_slab);
+            const int m = m0 + row, acc = lt & 1;
+            if (!mbar_wait(acc_full(acc), (lt >> 1) & 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16) + (uint32_t)(acc * kWN);
+            if (a.mode == 0) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < kWN; c0 += 32) store_c_chunk(a, t_row + c0, m, n0 + c0, m < m_lim);
+            } else {
+#pragma unroll 1
+                for (int gi = 0; gi < kWN / 64; ++gi)
+                    scatter_head_slice(a, t_row + 64 * gi, m, n0 + 64 * gi, m < m_lim && n0 + 64 * gi < a.N, lane);
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty(acc));               // this accumulator may be overwritten
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // [rows][K] 16-bit row-major matrix, box = 128 rows x 64 k, 128-byte swizzle
-bool make_map_2d(CUtensorMap* m, const void* base, int rows, int K, bool f16) {
+bool make_map_2d(CUtensorMap* m, const void* base, int rows, int K, bool f16, int box_rows = kBM) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, 1};
     cuuint64_t strides[2] = {(cuuint64_t)K * 2, (cuuint64_t)rows * K * 2};
-    cuuint32_t box[3] = {(cuuint32_t)kGK, (cuuint32_t)kBM, 1};
+    cuuint32_t box[3] = {(cuuint32_t)kGK, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
               dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -276,14 +432,25 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
         return fail(ctx, LOGOS_ERR_ALIGNMENT, "projection: operands must be 16-byte aligned");
     if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "projection: status word missing");
     CUtensorMap ma, mw;
+    const int m_tiles = a.a_heads ? (a.M / a.a_S) * ((a.a_S + kBM - 1) / kBM) : (a.M + kBM - 1) / kBM;
+    const int n_wide = (a.N + kWN - 1) / kWN;
+    // enough 128 x 256 tiles to give every SM one: the persistent wide kernel; otherwise the 128 x 128 kernel,
+    // which has twice the CTAs for a small problem
+    const bool wide = (int64_t)m_tiles * n_wide >= ctx->sm_count && !ctx->gemm_narrow;
     const bool a_ok = a.a_heads ? make_map_slabs(&ma, A, a.a_S, (a.M / a.a_S) * a.a_heads, a.f16 != 0)
                                 : make_map_2d(&ma, A, a.M, a.K, a.f16 != 0);
-    if (!a_ok || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0))
+    if (!a_ok || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0, wide ? kWN : kBM))
         return fail(ctx, LOGOS_ERR_CUDA, "projection: cuTensorMapEncodeTiled failed");
     a.status = ctx->tc_status;
+    if (wide) {
+        if (int rc = ensure_smem_limit(ctx, gemm_tc_wide_kernel, kWSmem)) return rc;
+        const int ctas = (int)std::min<int64_t>((int64_t)m_tiles * n_wide, ctx->sm_count);
+        gemm_tc_wide_kernel<<<ctas, kGThreads, kWSmem, ctx->stream>>>(ma, mw, a, m_tiles, n_wide);
+        LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_wide_kernel");
+        return LOGOS_OK;
+    }
     if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel, kGSmem)) return rc;
-    dim3 grid((a.N + kGN - 1) / kGN,
-              a.a_heads ? (a.M / a.a_S) * ((a.a_S + kBM - 1) / kBM) : (a.M + kBM - 1) / kBM);
+    dim3 grid((a.N + kGN - 1) / kGN, m_tiles);
     gemm_tc_kernel<<<grid, kGThreads, kGSmem, ctx->stream>>>(ma, mw, a);
     LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
     return LOGOS_OK;

@@ -137,3 +137,52 @@ def test_kv_dequantize16_is_the_rounded_fp32_product(engine, dtype):
     want32 = engine.nikhilam_decompress(q, scales, rows=rows)
     engine.synchronize()
     assert torch.equal(got, want32.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(148 * 128, 256, 64), (20000, 320, 136), (9000, 3072, 1024), (65536, 1024, 1024)])
+def test_wide_kernel_equals_the_narrow_one(engine, dtype, M, N, K):
+    """Problems that fill the device take the persistent 128 x 256-tile kernel: bit-identical to the 128 x 128
+    kernel (same products in the same order), ragged M, N no multiple of 256, several tiles per CTA, and the
+    fp64 product as the outside witness."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    A = torch.randn((M, K), device="cuda", generator=g).to(dtype)
+    W = (torch.randn((K, N), device="cuda", generator=g) * 0.02).to(dtype)
+    Wt = W.t().contiguous()
+    R = torch.randn((M, N), device="cuda", generator=g).to(dtype)
+    wide32 = engine.project(A, Wt, out_dtype=torch.float32)
+    wide16 = engine.project(A, Wt, residual=R)
+    engine.set_option(L.OPT_GEMM_NARROW, 1)
+    try:
+        narrow32 = engine.project(A, Wt, out_dtype=torch.float32)
+        narrow16 = engine.project(A, Wt, residual=R)
+    finally:
+        engine.set_option(L.OPT_GEMM_NARROW, 0)
+    engine.synchronize()
+    assert torch.equal(wide32, narrow32) and torch.equal(wide16, narrow16)
+    rows = torch.randint(0, M, (64,), device="cuda", generator=g)
+    want = (A[rows].double() @ W.double()).float()
+    assert float((wide32[rows] - want).abs().max()) <= 2e-5 * K ** 0.5 + 1e-6
+
+
+def test_wide_kernel_qkv_scatter_and_heads(engine):
+    """The wide kernel's other two forms: the Q/K/V scatter with max|x| (four head slices per tile) and the
+    head-major A operand, both against the narrow kernel."""
+    B, S, H, D = 16, 1280, 4, 512            # 160 m tiles x 3 n tiles: wide; S no multiple of 128 x anything special
+    g = torch.Generator(device="cuda").manual_seed(99)
+    X = torch.randn((B * S, D), device="cuda", generator=g).bfloat16()
+    Wt = (torch.randn((3 * H * 64, D), device="cuda", generator=g) * 0.05).bfloat16()
+    outs = engine.qkv_project(X, Wt, B, S, H, absmax=True)
+    O_ = torch.randn((B, H, S, 64), device="cuda", generator=g).bfloat16()
+    Wt_o = (torch.randn((512, H * 64), device="cuda", generator=g) * 0.05).bfloat16()
+    y = engine.project_heads(O_, Wt_o)
+    engine.set_option(L.OPT_GEMM_NARROW, 1)
+    try:
+        outs_n = engine.qkv_project(X, Wt, B, S, H, absmax=True)
+        y_n = engine.project_heads(O_, Wt_o)
+    finally:
+        engine.set_option(L.OPT_GEMM_NARROW, 0)
+    engine.synchronize()
+    for a_, b_ in zip(outs, outs_n):
+        assert torch.equal(a_, b_)
+    assert torch.equal(y, y_n)
