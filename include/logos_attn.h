@@ -103,7 +103,7 @@ const char* logos_last_error(const logos_ctx* ctx);
  * (cuda/ModelGPU.cuh:67-82) and are never read from the environment.
  *   LOGOS_OPT_FORCE_GENERAL  1: every attention call takes the exact fp32 kernel (tests compare the
  *                            tensor-core kernels with it); 0 (default): normal dispatch.
- *   LOGOS_OPT_DECODE_CHUNK   keys per split of the dense decode kernel: 128, 256, 512 or 1024;
+ *   LOGOS_OPT_DECODE_CHUNK   keys per split of the dense decode kernel: a multiple of 64 from 128 to 1024;
  *                            0 (default) = chosen from the problem size.  Results of two calls are
  *                            bit-identical only when they use the same chunk.
  *   LOGOS_OPT_PEER_WAIT_MS   longest time a kernel waits for the other GPUs of a logos_comm before it

@@ -226,8 +226,8 @@ int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
             ctx->force_general = value != 0;
             return LOGOS_OK;
         case LOGOS_OPT_DECODE_CHUNK:
-            if (value != 0 && value != 128 && value != 256 && value != 512 && value != 1024)
-                return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: decode chunk must be 0, 128, 256, 512 or 1024");
+            if (value != 0 && (value < 128 || value > 1024 || (value % 64) != 0))
+                return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: decode chunk must be 0 or a multiple of 64 in [128, 1024]");
             ctx->decode_chunk = value;
             return LOGOS_OK;
         case LOGOS_OPT_PEER_WAIT_MS:

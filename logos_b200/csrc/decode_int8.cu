@@ -737,16 +737,25 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     emit_row(a, bh, tid, r);
 }
 
-// Keys per split of the dense kernel, the one rule of both entry points: the largest chunk that
-// still gives every SM about four CTAs.  Measured at 8192 keys with 128 to 1024 (sequence, head)
-// pairs, the largest chunk is the fastest or within 3 % of it at every size (33 / 62 / 99 / 187 us
-// against 42 / 72 / 131 / 245 us with 256-key chunks): a warp's fixed cost -- query digits, softmax,
-// partial record, merge -- outweighs a ragged last wave, so the chunk only shrinks for very few
-// pairs.  `forced` != 0 (LOGOS_OPT_DECODE_CHUNK) overrides the rule.
+// Keys per split of the dense kernel, the one rule of both entry points.  A warp's fixed cost -- query digits,
+// softmax, partial record, merge -- outweighs finer splitting: measured at 8192 keys, the largest chunk
+// (1024) is the fastest whenever the launch is more than two waves of CTAs (ten 64-thread CTAs fit an SM) or
+// less than one (187 us at 1024 pairs, 99 at 512, 33 at 128; 256-key chunks: 245 / 131 / 42).  Between one
+// and two waves the second wave is mostly empty, so the chunk shrinks (in steps of 64 keys) until the CTAs
+// just fill two: 58 us instead of 62 at 256 pairs.  For very few pairs the chunk shrinks until every SM has
+// about four CTAs.  `forced` != 0 (LOGOS_OPT_DECODE_CHUNK) overrides the rule.
 int pick_chunk(int sm_count, int forced, int64_t BH, int S_max) {
     if (forced) return forced;
     int chunk = kMaxChunk;
     while (chunk > 128 && BH * ((S_max + chunk - 1) / chunk) < (int64_t)sm_count * 4) chunk >>= 1;
+    const int64_t slots = (int64_t)sm_count * 10;
+    const int64_t ctas = BH * ((S_max + chunk - 1) / chunk);
+    if (chunk == kMaxChunk && ctas > slots && ctas < 2 * slots) {
+        const int64_t per_pair = (2 * slots) / BH;                       // splits per pair that two waves hold
+        int c = (int)(((S_max + per_pair - 1) / per_pair + 63) / 64 * 64);
+        while (c < kMaxChunk && BH * ((S_max + c - 1) / c) > 2 * slots) c += 64;
+        if (c >= 128 && c < kMaxChunk) chunk = c;
+    }
     return chunk;
 }
 

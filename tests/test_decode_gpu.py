@@ -236,7 +236,7 @@ def test_dense_decode_rejects_viscosity_outside_unit_interval(engine):
     engine.synchronize()
 
 
-@pytest.mark.parametrize("chunk", [128, 256, 512, 1024])
+@pytest.mark.parametrize("chunk", [128, 192, 256, 512, 768, 960, 1024])
 def test_every_split_size_against_the_oracle(engine, chunk):
     p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
     engine.set_option(L.OPT_DECODE_CHUNK, chunk)
