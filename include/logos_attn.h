@@ -114,9 +114,12 @@ const char* logos_last_error(const logos_ctx* ctx);
  *                            a graph can still be launched.
  *   LOGOS_OPT_GEMM_NARROW    1: the projections always take the 128 x 128-tile kernel; 0 (default): the
  *                            persistent 128 x 256-tile kernel whenever the problem fills the device.
- *                            The two give bit-identical results (same products, same order of k). */
+ *                            The two give bit-identical results (same products, same order of k).
+ *   LOGOS_OPT_DECODE_DEPTH   tiles of 32 keys a warp of the dense decode kernel holds at once: 2 or 4;
+ *                            0 (default) = 4 when the launch is a single wave of CTAs, else 2.  The
+ *                            arithmetic and its order do not depend on it. */
 typedef enum { LOGOS_OPT_FORCE_GENERAL = 0, LOGOS_OPT_DECODE_CHUNK = 1, LOGOS_OPT_PEER_WAIT_MS = 2,
-               LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4 } logos_option;
+               LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4, LOGOS_OPT_DECODE_DEPTH = 5 } logos_option;
 int logos_ctx_set_option(logos_ctx* ctx, int option, int value);
 
 /* ---- attention ---------------------------------------------------------- */

@@ -241,6 +241,11 @@ int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
         case LOGOS_OPT_GEMM_NARROW:
             ctx->gemm_narrow = value != 0;
             return LOGOS_OK;
+        case LOGOS_OPT_DECODE_DEPTH:
+            if (value != 0 && value != 2 && value != 4)
+                return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: decode depth must be 0, 2 or 4");
+            ctx->decode_depth = value;
+            return LOGOS_OK;
     }
     return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: unknown option %d", option);
 }

@@ -27,6 +27,7 @@ struct logos_ctx {
     int peer_wait_ms = 2000;          // LOGOS_OPT_PEER_WAIT_MS
     bool workspace_locked = false;    // LOGOS_OPT_WORKSPACE_LOCK
     bool gemm_narrow = false;         // LOGOS_OPT_GEMM_NARROW
+    int decode_depth = 0;             // LOGOS_OPT_DECODE_DEPTH
     logos_alloc_fn alloc_fn = nullptr;   // caller's allocator for the workspace (null: cudaMalloc / cudaFree)
     logos_free_fn free_fn = nullptr;
     void* alloc_user = nullptr;

@@ -264,8 +264,12 @@ constexpr float kWGrid = 8388608.0f;            // 2^23 levels per unit weight
 // only meets the other warps of the CTA once, to merge (max, sum, output).  Inside
 // the passes there is no block-wide barrier, and the next 32-key tile is always in
 // flight while the current one is consumed.
-template <bool BLEND>
-__global__ void __launch_bounds__(kDenseThreads, 10)
+// NB = tiles of a pass held in registers at once (the one being used and NB - 1 on their way).  Two keep ten
+// CTAs on an SM: right when the launch is several waves deep, where the memory system is already full.  Four
+// (eight CTAs per SM) are for launches of a single wave, where a warp's chain of load latencies is the whole
+// run time and more loads in flight per warp shorten it.
+template <bool BLEND, int NB>
+__global__ void __launch_bounds__(kDenseThreads, NB == 2 ? 10 : 8)
 decode_dense_kernel(const DecodeArgs a) {
     constexpr int PATHS = BLEND ? 2 : 1;
     constexpr int ND = 3 * PATHS;                                   // digit rows / columns in use
@@ -301,7 +305,7 @@ decode_dense_kernel(const DecodeArgs a) {
 
     if (nw > 0) {
         // first K tile goes out before any arithmetic
-        uint4 ka[4], kb[4];
+        uint4 kt[NB][4];
         auto load_k = [&](uint4 (&buf)[4], int r0) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -309,7 +313,8 @@ decode_dense_kernel(const DecodeArgs a) {
                 buf[u] = (r < nw) ? ld_stream(kbase + (int64_t)r * kDH + 16 * t) : make_uint4(0, 0, 0, 0);
             }
         };
-        load_k(ka, 0);
+#pragma unroll
+        for (int u = 0; u < NB - 1; ++u) load_k(kt[u], 32 * u);
 
         // ---- query digits: lane (g,t) holds digit g of channels 16t..16t+15 ----
         uint32_t qb[4];
@@ -388,15 +393,16 @@ decode_dense_kernel(const DecodeArgs a) {
                 }
             }
         };
-        for (int r0 = 0; r0 < nw; r0 += 64) {
-            load_k(kb, r0 + 32);
-            score_tile(ka, r0);
-            load_k(ka, r0 + 64);
-            if (r0 + 32 < nw) score_tile(kb, r0 + 32);   // warp-uniform
+        for (int r0 = 0; r0 < nw; r0 += 32 * NB) {
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                load_k(kt[(u + NB - 1) % NB], r0 + 32 * (u + NB - 1));
+                if (r0 + 32 * u < nw) score_tile(kt[u], r0 + 32 * u);   // warp-uniform
+            }
         }
 
         // first V tile goes out before the softmax
-        uint2 va[8], vb[8];
+        uint2 vt[NB][8];
         auto load_v = [&](uint2 (&buf)[8], int r0) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -404,7 +410,8 @@ decode_dense_kernel(const DecodeArgs a) {
                 buf[u] = (r < nw) ? ld_stream8(vbase + (int64_t)r * kDH + 8 * g) : make_uint2(0, 0);
             }
         };
-        load_v(va, 0);
+#pragma unroll
+        for (int u = 0; u < NB - 1; ++u) load_v(vt[u], 32 * u);
         if (lane == 0) { p_ns[0] = 0.0f; p_ns[1 + nw] = 0.0f; }
         __syncwarp();
 
@@ -481,11 +488,12 @@ decode_dense_kernel(const DecodeArgs a) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) mma_u8s8(acc[j], a0, 0u, a2, 0u, blo[j], bhi[j]);
         };
-        for (int r0 = 0; r0 < nw; r0 += 64) {
-            load_v(vb, r0 + 32);
-            value_tile(va, r0);
-            load_v(va, r0 + 64);
-            if (r0 + 32 < nw) value_tile(vb, r0 + 32);   // warp-uniform
+        for (int r0 = 0; r0 < nw; r0 += 32 * NB) {
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                load_v(vt[(u + NB - 1) % NB], r0 + 32 * (u + NB - 1));
+                if (r0 + 32 * u < nw) value_tile(vt[u], r0 + 32 * u);   // warp-uniform
+            }
         }
         // halo rows in fp32 (lanes 0-3, 16 channels each): the row before the range takes
         // cR * p(first key), the row after it takes cL * p(last key)
@@ -854,13 +862,17 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
         a.counters = nullptr; a.partials = nullptr;
     }
     dim3 grid(n_splits, BH);
+    // a single wave of CTAs (eight per SM): the deep-prefetch form
+    const int depth = ctx->decode_depth ? ctx->decode_depth
+                                        : ((int64_t)n_splits * BH <= (int64_t)ctx->sm_count * 8 ? 4 : 2);
+    void (*kernel)(const DecodeArgs) =
+        depth == 4 ? (blend ? decode_dense_kernel<true, 4> : decode_dense_kernel<false, 4>)
+                   : (blend ? decode_dense_kernel<true, 2> : decode_dense_kernel<false, 2>);
     if (follows_append) {      // the kernel before this one on the stream is the engine's append of row len - 1
-        if (blend) LOGOS_CUDA_TRY(ctx, launch_overlapped(decode_dense_kernel<true>, grid, dim3(kDenseThreads), 0, ctx->stream, a));
-        else       LOGOS_CUDA_TRY(ctx, launch_overlapped(decode_dense_kernel<false>, grid, dim3(kDenseThreads), 0, ctx->stream, a));
+        LOGOS_CUDA_TRY(ctx, launch_overlapped(kernel, grid, dim3(kDenseThreads), 0, ctx->stream, a));
         return LOGOS_OK;
     }
-    if (blend) decode_dense_kernel<true><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
-    else       decode_dense_kernel<false><<<grid, kDenseThreads, 0, ctx->stream>>>(a);
+    kernel<<<grid, kDenseThreads, 0, ctx->stream>>>(a);
     LOGOS_LAUNCH_CHECK(ctx, "decode_dense_kernel");
     return LOGOS_OK;
 }
@@ -977,7 +989,7 @@ extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const
         return LOGOS_ERR_CUDA;
     }
     dim3 grid(n_splits, (unsigned)BH);
-    if (blend) decode_dense_kernel<true><<<grid, kDenseThreads, 0, st>>>(a);
-    else       decode_dense_kernel<false><<<grid, kDenseThreads, 0, st>>>(a);
+    if (blend) decode_dense_kernel<true, 2><<<grid, kDenseThreads, 0, st>>>(a);
+    else       decode_dense_kernel<false, 2><<<grid, kDenseThreads, 0, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? LOGOS_OK : LOGOS_ERR_CUDA;
 }

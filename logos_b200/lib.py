@@ -18,7 +18,7 @@ ERR_KERNEL_TIMEOUT = 8
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
 MHA_ATTEND_DEQUANTIZED = 1
-OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK, OPT_GEMM_NARROW = 0, 1, 2, 3, 4
+OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK, OPT_GEMM_NARROW, OPT_DECODE_DEPTH = 0, 1, 2, 3, 4, 5
 COMM_HANDLE_BYTES = 80
 
 

@@ -246,3 +246,19 @@ def test_every_split_size_against_the_oracle(engine, chunk):
         engine.set_option(L.OPT_DECODE_CHUNK, 0)
     with pytest.raises(L.LogosError):
         engine.set_option(L.OPT_DECODE_CHUNK, 300)
+
+
+def test_prefetch_depth_does_not_change_the_bits(engine):
+    """LOGOS_OPT_DECODE_DEPTH only changes how many tiles a warp has in flight: same arithmetic, same order."""
+    outs = []
+    for depth in (2, 4):
+        engine.set_option(L.OPT_DECODE_DEPTH, depth)
+        try:
+            outs.append([run_case(engine, 3, 2, 2048, [2048, 1, 777], L.Params.make(0.125, True, 0, 0, 0.1, 0.05, a, m), seed=33)
+                         for a, m in ((1.0, L.DIFFUSE_CAUSAL), (0.4, L.DIFFUSE_CENTRAL))])
+        finally:
+            engine.set_option(L.OPT_DECODE_DEPTH, 0)
+    for x, y in zip(*outs):
+        assert np.array_equal(x, y)
+    with pytest.raises(L.LogosError):
+        engine.set_option(L.OPT_DECODE_DEPTH, 3)
