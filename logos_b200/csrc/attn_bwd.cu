@@ -412,7 +412,7 @@ size_t attention_bwd_workspace_bytes(int B, int H, int S, int DH) {
     if (B <= 0 || H <= 0 || S <= 0 || DH <= 0) return 0;
     const size_t t = ((size_t)B * H * S * DH * sizeof(float) + 255) & ~(size_t)255;
     const size_t r = ((size_t)B * H * S * sizeof(float) + 255) & ~(size_t)255;
-    return 4 * t + 2 * r;     // Q_adv, V_s, dQ_adv, dV_s; log-sum-exp, delta
+    return kWorkspaceCounterBytes + 4 * t + 2 * r;     // (decode's counters,) Q_adv, V_s, dQ_adv, dV_s; log-sum-exp, delta
 }
 
 int attention_bwd(logos_ctx* ctx, const float* Q, const float* K, const float* V, const float* dO, float* dQ, float* dK,
@@ -433,7 +433,7 @@ int attention_bwd(logos_ctx* ctx, const float* Q, const float* K, const float* V
     const int64_t total = (int64_t)BH * S * DH;
     const size_t t = ((size_t)total * sizeof(float) + 255) & ~(size_t)255;
     const size_t r = ((size_t)BH * S * sizeof(float) + 255) & ~(size_t)255;
-    char* ws = static_cast<char*>(ctx->workspace);
+    char* ws = static_cast<char*>(ctx->workspace) + kWorkspaceCounterBytes;
     float *Qa = (float*)ws, *Vs = (float*)(ws + t), *dQa = (float*)(ws + 2 * t), *dVs = (float*)(ws + 3 * t);
     float *lse = (float*)(ws + 4 * t), *delta = (float*)(ws + 4 * t + r);
 

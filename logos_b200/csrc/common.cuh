@@ -140,6 +140,11 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The first 64 KiB of a context's workspace are the split-K arrival counters of the decode kernel.  They are
+// zero whenever no decode kernel is running (cleared when the block is attached, put back to zero by the
+// kernel itself); every other user of the workspace starts beyond them.
+constexpr size_t kWorkspaceCounterBytes = 64 * 1024;
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline size_t dtype_size(int dt) { return dt == LOGOS_F32 ? 4 : 2; }

@@ -38,7 +38,7 @@ constexpr int kRowsPerIter = kWarps * kRowsPerWarp;  // 64
 constexpr int kUnroll = 4;       // 16-byte loads in flight per lane
 constexpr int kMaxChunk = 1024;  // keys per CTA in the dense kernel
 constexpr int kPartial = 2 + kDH;  // (max, sum, acc[64]) per split
-constexpr size_t kCounterBytes = 64 * 1024;  // head of the workspace: arrival counters
+constexpr size_t kCounterBytes = kWorkspaceCounterBytes;  // head of the workspace: arrival counters
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeArgs {

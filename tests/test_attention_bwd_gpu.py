@@ -68,6 +68,15 @@ def test_bwd_is_reproducible_bit_for_bit(engine):
         assert torch.equal(x, y)
 
 
+def test_bwd_leaves_the_decode_counters_alone(engine):
+    """Backward and decode share the context's workspace: a split-K decode right after a backward must still find
+    its arrival counters at zero."""
+    Q, K, V, dO = (torch.from_numpy(a).cuda() for a in _case(1, 2, 256, 64, 345))
+    engine.attention_bwd(Q, K, V, dO, L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL))
+    from test_decode_gpu import run_case
+    run_case(engine, 2, 2, 4096, [4096, 1500], L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL), seed=346)
+
+
 def test_bwd_matches_autograd_of_the_forward_at_length(engine):
     """S = 1024, 8 heads: torch autograd through an fp64 restatement of the forward (advection, causal
     diffusion, masked softmax) as a third, independent witness at a size the C oracle takes long for."""
