@@ -295,6 +295,8 @@ int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const void* q_pr
  *   column c of W_Q[h] (which 0), W_K[h] (1) or W_V[h] (2), i.e. Wt_qkv[n][k] = W[k][c].  With k_absmax /
  *   v_absmax (float [B][H], both or neither) the epilogue also leaves max|x| of every stored K and V
  *   tensor there, ready for logos_kv_quantize_absmax.  DH is 64; D_model a multiple of 8.
+ *   Operands 16-byte aligned; outputs (Q, K, V, C) and the residual 32-byte aligned (they are written and read 32
+ *   bytes per thread and instruction).
  *
  * logos_project -- C [M][N] = A [M][K] · W (+ residual [M][N]), A and the K-major shadow Wt [N][K] in
  *   one 16-bit dtype, C and the residual in out_dtype (that dtype or LOGOS_F32).  With the heads'

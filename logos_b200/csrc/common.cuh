@@ -146,6 +146,7 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
 constexpr size_t kWorkspaceCounterBytes = 64 * 1024;
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 inline size_t dtype_size(int dt) { return dt == LOGOS_F32 ? 4 : 2; }
 inline bool dtype_ok(int dt) { return dt == LOGOS_F32 || dt == LOGOS_BF16 || dt == LOGOS_F16; }

@@ -64,45 +64,96 @@ __device__ __forceinline__ float round16(float x, bool f16) {
 
 // ---- epilogue pieces, shared by the two kernels; the calling thread owns output row m ----
 
-// 32 accumulator columns starting at TMEM address t_addr -> C[m][n .. n+31] (+ residual)
-__device__ __forceinline__ void store_c_chunk(const GemmArgs& a, uint32_t t_addr, int m, int n, bool live) {
+// 32-byte global accesses (one full sector per thread and instruction); the address is 32-byte aligned
+__device__ __forceinline__ void ld_nc_32B(const void* p, uint4& lo, uint4& hi) {
+    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_32B(void* p, const uint4& lo, const uint4& hi) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+}
+
+// The residual of 32 output columns of row m (64 or 128 bytes), fetched ahead of the accumulator so that its
+// latency is not part of the epilogue's chain.  Zeros when there is no residual or the chunk is not live.
+struct ResChunk { uint4 v[8]; };
+__device__ __forceinline__ void load_residual_chunk(const GemmArgs& a, int m, int n, bool live, ResChunk& r) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r.v[j] = make_uint4(0, 0, 0, 0);
+    if (!a.R || !live || n >= a.N) return;
+    const size_t off = (size_t)m * a.N + n;
+    if (a.c_is_f32) {
+        const uint4* res = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.R) + off);
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) ld_nc_32B(res + j, r.v[j], r.v[j + 1]);
+    } else {
+        const uint4* res = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.R) + off);
+#pragma unroll
+        for (int j = 0; j < 4; j += 2) ld_nc_32B(res + j, r.v[j], r.v[j + 1]);
+    }
+}
+
+// 32 accumulator columns (already in registers) plus their residual -> C[m][n .. n+31]
+__device__ __forceinline__ void write_c_chunk(const GemmArgs& a, const float (&v)[32], int m, int n, bool live,
+                                              const ResChunk& r) {
     const bool f16 = a.f16 != 0;
-    float v[32];
-    tc_ld32(t_addr, v);
-    tc_wait_ld();
     if (!live || n >= a.N) return;                 // N is a multiple of 32
     const size_t off = (size_t)m * a.N + n;
     if (a.c_is_f32) {
-        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.C) + off);
-        const float4* res = a.R ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.R) + off) : nullptr;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<float*>(a.C) + off);
+        uint4 o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            float4 r4 = res ? res[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-            dst[j] = make_float4(v[4 * j] + r4.x, v[4 * j + 1] + r4.y, v[4 * j + 2] + r4.z, v[4 * j + 3] + r4.w);
+            const float4 r4 = *reinterpret_cast<const float4*>(&r.v[j]);
+            const float4 f = make_float4(v[4 * j] + r4.x, v[4 * j + 1] + r4.y, v[4 * j + 2] + r4.z, v[4 * j + 3] + r4.w);
+            o[j] = *reinterpret_cast<const uint4*>(&f);
         }
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) st_32B(dst + j, o[j], o[j + 1]);
     } else {
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.C) + off);
-        const uint4* res = a.R ? reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(a.R) + off) : nullptr;
+        uint4 o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             uint32_t w[4];
-            uint4 r4 = res ? res[j] : make_uint4(0, 0, 0, 0);
-            const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r4);
+            const uint32_t* rw = reinterpret_cast<const uint32_t*>(&r.v[j]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float x = v[8 * j + 2 * e], y = v[8 * j + 2 * e + 1];
-                if (res) {
-                    if (f16) {
-                        float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
-                        x += rr.x; y += rr.y;
-                    } else {
-                        x += __uint_as_float(rw[e] << 16); y += __uint_as_float(rw[e] & 0xffff0000u);
-                    }
+                if (f16) {
+                    float2 rr = __half22float2(*reinterpret_cast<const __half2*>(&rw[e]));
+                    x += rr.x; y += rr.y;
+                } else {
+                    x += __uint_as_float(rw[e] << 16); y += __uint_as_float(rw[e] & 0xffff0000u);
                 }
                 w[e] = pack16(x, y, f16);
             }
-            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+            o[j] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        st_32B(dst, o[0], o[1]);
+        st_32B(dst + 2, o[2], o[3]);
+    }
+}
+
+// One output row's columns [n0, n0 + cols) from the accumulator at t_row, the residual of chunk c + 1 on its way
+// while chunk c is written.  `first` was fetched by the caller (before it waited for the accumulator); cols is a
+// multiple of 64.  (Having the next chunk's accumulator columns in flight as well measured no faster.)
+__device__ __forceinline__ void store_c_row(const GemmArgs& a, uint32_t t_row, int m, int n0, int cols, bool live,
+                                            ResChunk& first) {
+    ResChunk next;
+    float v[32];
+#pragma unroll 1
+    for (int c0 = 0; c0 < cols; c0 += 64) {
+        load_residual_chunk(a, m, n0 + c0 + 32, live, next);
+        tc_ld32(t_row + c0, v);
+        tc_wait_ld();
+        write_c_chunk(a, v, m, n0 + c0, live, first);
+        load_residual_chunk(a, m, n0 + c0 + 64, live && c0 + 64 < cols, first);
+        tc_ld32(t_row + c0 + 32, v);
+        tc_wait_ld();
+        write_c_chunk(a, v, m, n0 + c0 + 32, live, next);
     }
 }
 
@@ -124,6 +175,7 @@ __device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t
         tc_ld32(t_addr + 32 * hc, v);
         tc_wait_ld();
         if (live) {
+            uint4 o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint32_t w[4];
@@ -133,8 +185,10 @@ __device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t
                     w[e] = pack16(x, y, f16);
                     amax = fmaxf(amax, fmaxf(fabsf(round16(x, f16)), fabsf(round16(y, f16))));
                 }
-                dst[4 * hc + j] = make_uint4(w[0], w[1], w[2], w[3]);
+                o[j] = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            st_32B(dst + 4 * hc, o[0], o[1]);
+            st_32B(dst + 4 * hc + 2, o[2], o[3]);
         }
     }
     // one atomic per warp when its 32 rows lie in one sequence, else one per row; non-negative floats order
@@ -231,11 +285,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane, m = m0 + row;
         const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16);
+        ResChunk res0;
+        if (a.mode == 0) load_residual_chunk(a, m, n0, m < m_lim, res0);
         if (mbar_wait(acc_full, 0, abort_flag)) {
             tc_fence_after();
             if (a.mode == 0) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < kGN; c0 += 32) store_c_chunk(a, t_row + c0, m, n0 + c0, m < m_lim);
+                store_c_row(a, t_row, m, n0, kGN, m < m_lim, res0);
             } else {
 #pragma unroll 1
                 for (int gi = 0; gi < 2; ++gi) scatter_head_slice(a, t_row + 64 * gi, m, n0 + 64 * gi, m < m_lim, lane);
@@ -374,12 +429,13 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             int m0, m_lim, a_row, a_slab;
             tile_rows(mt, m0, m_lim, a_row, a_slab);
             const int m = m0 + row, acc = lt & 1;
+            ResChunk res0;
+            if (a.mode == 0) load_residual_chunk(a, m, n0, m < m_lim, res0);
             if (!mbar_wait(acc_full(acc), (lt >> 1) & 1, abort_flag)) break;
             tc_fence_after();
             const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16) + (uint32_t)(acc * kWN);
             if (a.mode == 0) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < kWN; c0 += 32) store_c_chunk(a, t_row + c0, m, n0 + c0, m < m_lim);
+                store_c_row(a, t_row, m, n0, kWN, m < m_lim, res0);
             } else {
 #pragma unroll 1
                 for (int gi = 0; gi < kWN / 64; ++gi)
@@ -463,8 +519,8 @@ int project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const void*
     if (!A || !Wt || !C) return fail(ctx, LOGOS_ERR_INVALID_ARG, "project: null pointer");
     if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project: operands must be BF16 or FP16");
     if (out_dtype != dtype && out_dtype != LOGOS_F32) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project: output is the operand type or fp32");
-    if (!aligned16(C) || (residual && !aligned16(residual)) || (N % 64) != 0)
-        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project: C and the residual must be 16-byte aligned, N a multiple of 64");
+    if (!aligned32(C) || (residual && !aligned32(residual)) || (N % 64) != 0)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project: C and the residual must be 32-byte aligned, N a multiple of 64");
     GemmArgs a{};
     a.M = M; a.N = N; a.K = K; a.f16 = dtype == LOGOS_F16; a.mode = 0;
     a.C = C; a.R = residual; a.c_is_f32 = out_dtype == LOGOS_F32;
@@ -477,8 +533,8 @@ int project_heads(logos_ctx* ctx, int dtype, int out_dtype, const void* head_out
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "project_heads: bad pointer or extent");
     if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project_heads: operands must be BF16 or FP16");
     if (out_dtype != dtype && out_dtype != LOGOS_F32) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "project_heads: output is the operand type or fp32");
-    if (!aligned16(C) || (residual && !aligned16(residual)) || (N % 64) != 0)
-        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project_heads: C and the residual must be 16-byte aligned, N a multiple of 64");
+    if (!aligned32(C) || (residual && !aligned32(residual)) || (N % 64) != 0)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "project_heads: C and the residual must be 32-byte aligned, N a multiple of 64");
     GemmArgs a{};
     a.M = B * S; a.N = N; a.K = H * 64; a.f16 = dtype == LOGOS_F16; a.mode = 0;
     a.C = C; a.R = residual; a.c_is_f32 = out_dtype == LOGOS_F32;
@@ -491,7 +547,7 @@ int qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt, void* 
     if (!X || !Wt || !Q || !K || !V || B <= 0 || S <= 0 || H <= 0 || D <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "qkv_project: bad pointer or extent");
     if (dtype != LOGOS_BF16 && dtype != LOGOS_F16) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "qkv_project: operands must be BF16 or FP16");
-    if (!aligned16(Q) || !aligned16(K) || !aligned16(V)) return fail(ctx, LOGOS_ERR_ALIGNMENT, "qkv_project: outputs must be 16-byte aligned");
+    if (!aligned32(Q) || !aligned32(K) || !aligned32(V)) return fail(ctx, LOGOS_ERR_ALIGNMENT, "qkv_project: outputs must be 32-byte aligned");
     if ((k_absmax == nullptr) != (v_absmax == nullptr))
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "qkv_project: the two absmax tables are given together or not at all");
     if (k_absmax) {
