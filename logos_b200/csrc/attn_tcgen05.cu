@@ -98,6 +98,7 @@ static_assert(B_NUM <= kNumBars, "barrier count");
 struct TcArgs {
     void* O;
     int S, out_is_f32, in_is_f16;
+    int o_al32;                 // O is 32-byte aligned: rows are stored 32 bytes at a time
     float c;            // scale * log2(e)
     float eta, nu;
     int diffuse;        // 0 none, 1 causal
@@ -761,20 +762,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     tc_wait_ld();
                     if (i_glob < S) {
                         const size_t row = ((size_t)bh * S + i_glob) * kD + hc * 32;
+                        // 32 bytes per store when the output allows it: a full sector per thread and instruction
                         if (a.out_is_f32) {
-                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.O) + row);
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<float*>(a.O) + row);
+                            uint4 w4[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                dst[j] = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+                            for (int j = 0; j < 8; ++j) {
+                                const float4 f = make_float4(o[4 * j] * inv, o[4 * j + 1] * inv, o[4 * j + 2] * inv, o[4 * j + 3] * inv);
+                                w4[j] = *reinterpret_cast<const uint4*>(&f);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; j += 2) {
+                                if (a.o_al32) st_32B(dst + j, w4[j], w4[j + 1]);
+                                else { dst[j] = w4[j]; dst[j + 1] = w4[j + 1]; }
+                            }
                         } else {
                             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(a.O) + row);
+                            uint4 w4[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 uint32_t w[4];
 #pragma unroll
                                 for (int e = 0; e < 4; ++e)
                                     w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
-                                dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                                w4[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; j += 2) {
+                                if (a.o_al32) st_32B(dst + j, w4[j], w4[j + 1]);
+                                else { dst[j] = w4[j]; dst[j + 1] = w4[j + 1]; }
                             }
                         }
                     }
@@ -983,6 +999,7 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     TcArgs a;
     a.O = O; a.S = S;
     a.out_is_f32 = out_dtype == LOGOS_F32;
+    a.o_al32 = aligned32(O) ? 1 : 0;
     a.in_is_f16 = f16;
     a.c = p->scale * 1.4426950408889634f;
     a.eta = ns_any ? p->ns_eta : 0.0f;

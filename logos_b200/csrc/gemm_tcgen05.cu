@@ -64,18 +64,6 @@ __device__ __forceinline__ float round16(float x, bool f16) {
 
 // ---- epilogue pieces, shared by the two kernels; the calling thread owns output row m ----
 
-// 32-byte global accesses (one full sector per thread and instruction); the address is 32-byte aligned
-__device__ __forceinline__ void ld_nc_32B(const void* p, uint4& lo, uint4& hi) {
-    asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
-                 : "l"(p));
-}
-__device__ __forceinline__ void st_32B(void* p, const uint4& lo, const uint4& hi) {
-    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                 ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-                 : "memory");
-}
-
 // The residual of 32 output columns of row m (64 or 128 bytes), fetched ahead of the accumulator so that its
 // latency is not part of the epilogue's chain.  Zeros when there is no residual or the chunk is not live.
 struct ResChunk { uint4 v[8]; };
