@@ -144,6 +144,19 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
                         const logos_attn_params* params);
 size_t logos_attention_workspace_bytes(int B, int H, int S, int DH);
 
+/* logos_attention_fwd on tensors that are not packed [B][H][S][DH]: element strides between two sequences,
+ * two heads and two rows; the DH values of a row are contiguous.  `qkv` describes Q, K and V (one layout for
+ * the three, as one projection writes them), `out` describes O; NULL = packed.  Examples: token-major
+ * [B][S][H][DH] is {S*H*DH, DH, H*DH}; one head of a packed tensor is the packed strides with a shifted base.
+ * Same kernels, same results bit for bit as the packed call on the same values.  For 16-bit tensors every row
+ * must start on a 16-byte boundary (strides multiples of 8 elements); when the sequences' slabs are not evenly
+ * spaced (batch != H * head, B > 1) the tensor-core kernel is launched once per sequence. */
+typedef struct { int64_t batch, head, row; } logos_strides;
+int logos_attention_fwd_strided(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                                const void* V, void* O, int B, int H, int S, int DH,
+                                const logos_strides* qkv, const logos_strides* out,
+                                const logos_attn_params* params);
+
 /* Attention backward: dQ, dK, dV of logos_attention_fwd's output with respect to its raw Q, K, V, for the
  * gradient dO of that output; all tensors fp32 [B][H][S][DH], DH 32, 64 or 128, 16-byte aligned.
  * Replaces, for all heads at once and without any seq x seq buffer, the per-head chain of

@@ -287,7 +287,18 @@ size_t logos_attention_workspace_bytes(int B, int H, int S, int DH) {
 int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
                         const void* V, void* O, int B, int H, int S, int DH,
                         const logos_attn_params* params) {
+    return logos_attention_fwd_strided(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, nullptr, nullptr, params);
+}
+
+int logos_attention_fwd_strided(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
+                                const void* V, void* O, int B, int H, int S, int DH,
+                                const logos_strides* qkv, const logos_strides* out,
+                                const logos_attn_params* params) {
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    for (const logos_strides* st : {qkv, out})
+        if (st && (st->row < DH || st->head < 0 || st->batch < 0))
+            return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: a row stride below DH or a negative stride");
+    const bool strided = qkv != nullptr || out != nullptr;
     if (!Q || !K || !V || !O || B <= 0 || H <= 0 || S <= 0 || DH <= 0)
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_fwd: bad pointer or extent");
     if (!params_ok(params))
@@ -297,10 +308,10 @@ int logos_attention_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void*
     // What the tensor-core kernel takes (causal, Shunyam window with or without landmarks) goes there; the
     // gather kernel keeps the Shunyam shapes it declines (viscosity above 1/2); everything else is fp32 SIMT.
     if (!ctx->force_general && logos::attention_tc_eligible(in_dtype, out_dtype, DH, params, S))
-        return logos::attention_tc(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
-    if (!ctx->force_general && logos::attention_window_eligible(in_dtype, out_dtype, DH, params, S))
+        return logos::attention_tc(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params, qkv, out);
+    if (!strided && !ctx->force_general && logos::attention_window_eligible(in_dtype, out_dtype, DH, params, S))
         return logos::attention_window(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
-    return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params);
+    return logos::attention_simt(ctx, in_dtype, out_dtype, Q, K, V, O, B, H, S, DH, params, qkv, out);
 }
 
 size_t logos_attention_bwd_workspace_bytes(int B, int H, int S, int DH) {

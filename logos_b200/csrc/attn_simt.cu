@@ -30,7 +30,9 @@ constexpr int kMaxCh = kMaxDH / 16;  // output channels per lane
 
 struct SimtArgs {
     const void* Q; const void* K; const void* V; void* O;
-    int S, DH;
+    int S, DH, H;
+    // elements between two sequences, two heads and two rows of Q / K / V (one layout for the three) and of O
+    long long i_batch, i_head, i_row, o_batch, o_head, o_row;
     float scale, eta, nu, alpha;
     int causal, shunyam, window, stride, diffuse_mode;
 };
@@ -48,11 +50,13 @@ attention_simt_kernel(const SimtArgs a) {
     float* sP = sVr + (BLEND ? BN * DH : 0);         // [BM][BN]
     float* sP2 = sP + BM * BN;                       // [BM][BN]   (BLEND)
 
-    const int64_t head_off = (int64_t)blockIdx.y * S * DH;
+    const int b_idx = (int)blockIdx.y / a.H, h_idx = (int)blockIdx.y - b_idx * a.H;
+    const int64_t head_off = (int64_t)b_idx * a.i_batch + (int64_t)h_idx * a.i_head;
+    const int64_t RS = a.i_row;                       // row pitch of Q, K, V
     const TIn* Q = (const TIn*)a.Q + head_off;
     const TIn* K = (const TIn*)a.K + head_off;
     const TIn* V = (const TIn*)a.V + head_off;
-    TOut* O = (TOut*)a.O + head_off;
+    TOut* O = (TOut*)a.O + (int64_t)b_idx * a.o_batch + (int64_t)h_idx * a.o_head;
 
     const int tid = threadIdx.x;
     const int grp = tid >> 4, lc = tid & 15;
@@ -64,8 +68,8 @@ attention_simt_kernel(const SimtArgs a) {
         int r = e / DH, d = e - r * DH, i = q0 + r;
         float q = 0.0f, qa = 0.0f;
         if (i < S) {
-            q = to_f32<TIn>(Q[(int64_t)i * DH + d]);
-            float qp = (i > 0) ? to_f32<TIn>(Q[(int64_t)(i - 1) * DH + d]) : q;
+            q = to_f32<TIn>(Q[(int64_t)i * RS + d]);
+            float qp = (i > 0) ? to_f32<TIn>(Q[(int64_t)(i - 1) * RS + d]) : q;
             qa = q + a.eta * (q - qp);
         }
         sQa[e] = qa;
@@ -101,15 +105,15 @@ attention_simt_kernel(const SimtArgs a) {
             int r = e / DH, d = e - r * DH, j = k0 + r;
             float kv = 0.0f, v = 0.0f, vs = 0.0f;
             if (j < S) {
-                kv = to_f32<TIn>(K[(int64_t)j * DH + d]);
-                v = to_f32<TIn>(V[(int64_t)j * DH + d]);
+                kv = to_f32<TIn>(K[(int64_t)j * RS + d]);
+                v = to_f32<TIn>(V[(int64_t)j * RS + d]);
                 if (a.diffuse_mode == LOGOS_DIFFUSE_CAUSAL) {
-                    float vp = (j > 0) ? to_f32<TIn>(V[(int64_t)(j - 1) * DH + d]) : v;
+                    float vp = (j > 0) ? to_f32<TIn>(V[(int64_t)(j - 1) * RS + d]) : v;
                     vs = (1.0f - a.nu) * v + a.nu * vp;
                 } else if (a.diffuse_mode == LOGOS_DIFFUSE_CENTRAL) {
                     int jl = (j > 0) ? j - 1 : 0, jr = (j < S - 1) ? j + 1 : S - 1;
-                    float vl = to_f32<TIn>(V[(int64_t)jl * DH + d]);
-                    float vr = to_f32<TIn>(V[(int64_t)jr * DH + d]);
+                    float vl = to_f32<TIn>(V[(int64_t)jl * RS + d]);
+                    float vr = to_f32<TIn>(V[(int64_t)jr * RS + d]);
                     vs = (1.0f - a.nu) * v + (a.nu * 0.5f) * (vl + vr);
                 } else {
                     vs = v;
@@ -215,7 +219,7 @@ attention_simt_kernel(const SimtArgs a) {
             if (d < DH) {
                 float r = o1[rr][c] * inv1;
                 if (BLEND) r = (1.0f - a.alpha) * (o2[rr][c] * inv2) + a.alpha * r;
-                O[(int64_t)i * DH + d] = from_f32<TOut>(r);
+                O[(int64_t)i * a.o_row + d] = from_f32<TOut>(r);
             }
         }
     }
@@ -248,13 +252,17 @@ int launch(logos_ctx* ctx, const SimtArgs& a, int BH, bool blend) {
 
 int attention_simt(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
-                   const logos_attn_params* p) {
+                   const logos_attn_params* p, const logos_strides* in, const logos_strides* out) {
     if (DH > kMaxDH)
         return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention: DH=%d exceeds %d", DH, kMaxDH);
     if ((int64_t)B * H > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention: B*H > 65535");
     SimtArgs a;
     a.Q = Q; a.K = K; a.V = V; a.O = O;
-    a.S = S; a.DH = DH;
+    a.S = S; a.DH = DH; a.H = H;
+    a.i_batch = in ? in->batch : (int64_t)H * S * DH; a.i_head = in ? in->head : (int64_t)S * DH; a.i_row = in ? in->row : DH;
+    a.o_batch = out ? out->batch : (int64_t)H * S * DH; a.o_head = out ? out->head : (int64_t)S * DH; a.o_row = out ? out->row : DH;
+    if (a.i_row < DH || a.o_row < DH)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "attention: a row stride is smaller than DH");
     a.scale = p->scale;
     a.causal = p->causal;
     a.shunyam = shunyam_active(p->window, S) ? 1 : 0;

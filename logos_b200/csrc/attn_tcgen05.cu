@@ -97,6 +97,7 @@ static_assert(B_NUM <= kNumBars, "barrier count");
 
 struct TcArgs {
     void* O;
+    long long o_row, o_slab;    // elements between the rows of a head's output and between two (sequence, head) outputs
     int S, out_is_f32, in_is_f16;
     int o_al32;                 // O is 32-byte aligned: rows are stored 32 bytes at a time
     float c;            // scale * log2(e)
@@ -761,7 +762,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     tc_ld32(tmem_O + 32 * hc, o);
                     tc_wait_ld();
                     if (i_glob < S) {
-                        const size_t row = ((size_t)bh * S + i_glob) * kD + hc * 32;
+                        const size_t row = (size_t)bh * a.o_slab + (size_t)i_glob * a.o_row + hc * 32;
                         // 32 bytes per store when the output allows it: a full sector per thread and instruction
                         if (a.out_is_f32) {
                             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<float*>(a.O) + row);
@@ -930,11 +931,15 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
 // [BH][S][64] 16-bit tensor, box = 128 rows x 64 channels of one head, 128-byte swizzle
 // `rows` rows per head taken every `pitch` rows from `base` (pitch 1: the plain tensor; pitch = the landmark
 // stride: the strided view whose row m is key m * stride of the head)
-bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16, int rows = -1, int pitch = 1) {
+// row_elems / slab_elems: elements between two rows of a head and between two (sequence, head) slabs (0: contiguous)
+bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16, int rows = -1, int pitch = 1,
+              int64_t row_elems = 0, int64_t slab_elems = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
+    if (row_elems == 0) row_elems = kD;
+    if (slab_elems == 0) slab_elems = (int64_t)S * kD;
     cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)(rows < 0 ? S : rows), (cuuint64_t)BH};
-    cuuint64_t strides[2] = {(cuuint64_t)kD * 2 * pitch, (cuuint64_t)S * kD * 2};
+    cuuint64_t strides[2] = {(cuuint64_t)row_elems * 2 * pitch, (cuuint64_t)slab_elems * 2};
     cuuint32_t box[3] = {(cuuint32_t)kD, (cuuint32_t)kBM, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
@@ -973,8 +978,29 @@ bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn
     return true;
 }
 
+// in / out: element strides of Q, K, V and of O (NULL: contiguous [B][H][S][64]).  One launch covers every
+// (sequence, head) when the slabs are evenly spaced (batch stride = H x head stride); otherwise one launch per sequence.
 int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
-                 void* O, int B, int H, int S, int DH, const logos_attn_params* p) {
+                 void* O, int B, int H, int S, int DH, const logos_attn_params* p, const logos_strides* in,
+                 const logos_strides* out) {
+    logos_strides si{(int64_t)H * S * kD, (int64_t)S * kD, kD}, so = si;
+    if (in) si = *in;
+    if (out) so = *out;
+    const int esz_o = out_dtype == LOGOS_F32 ? 4 : 2;
+    if (si.row < kD || (si.row % 8) || (si.head % 8) || (si.batch % 8) || so.row < kD || (so.row * esz_o) % 16 ||
+        (so.head * esz_o) % 16 || (so.batch * esz_o) % 16)
+        return fail(ctx, LOGOS_ERR_ALIGNMENT, "attention: strides must keep every row 16-byte aligned");
+    if (B > 1 && (si.batch != (int64_t)H * si.head || so.batch != (int64_t)H * so.head)) {
+        for (int b = 0; b < B; ++b) {     // slabs not evenly spaced over (sequence, head): one sequence at a time
+            logos_strides s1 = si, s2 = so;
+            s1.batch = (int64_t)H * si.head; s2.batch = (int64_t)H * so.head;
+            const size_t ib = (size_t)b * si.batch * 2, ob = (size_t)b * so.batch * esz_o;
+            int rc = attention_tc(ctx, in_dtype, out_dtype, (const char*)Q + ib, (const char*)K + ib, (const char*)V + ib,
+                                  (char*)O + ob, 1, H, S, DH, p, &s1, &s2);
+            if (rc != LOGOS_OK) return rc;
+        }
+        return LOGOS_OK;
+    }
     (void)DH;
     const int BH = B * H;
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O))
@@ -982,7 +1008,8 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "attention: status word missing");
     const bool f16 = in_dtype == LOGOS_F16;
     CUtensorMap mq, mk, mv, mkl, mvl, mvp;
-    if (!make_map(&mq, Q, BH, S, f16) || !make_map(&mk, K, BH, S, f16) || !make_map(&mv, V, BH, S, f16))
+    if (!make_map(&mq, Q, BH, S, f16, -1, 1, si.row, si.head) || !make_map(&mk, K, BH, S, f16, -1, 1, si.row, si.head) ||
+        !make_map(&mv, V, BH, S, f16, -1, 1, si.row, si.head))
         return fail(ctx, LOGOS_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed");
     // Shunyam landmarks: strided views of K and V (row m = key m * stride) and of V one row earlier
     // (row m = key (m + 1) * stride - 1, read at m - 1); each view ends inside its head's rows
@@ -990,14 +1017,16 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     mkl = mk; mvl = mv; mvp = mv;
     if (lm_stride) {
         const int n_lm = (S + lm_stride - 1) / lm_stride, n_prev = S / lm_stride;
-        const unsigned char* v_prev = reinterpret_cast<const unsigned char*>(V) + (size_t)(lm_stride - 1) * kD * 2;
-        if (!make_map(&mkl, K, BH, S, f16, n_lm, lm_stride) || !make_map(&mvl, V, BH, S, f16, n_lm, lm_stride) ||
-            !make_map(&mvp, n_prev > 0 ? v_prev : V, BH, S, f16, n_prev > 0 ? n_prev : 1, lm_stride))
+        const unsigned char* v_prev = reinterpret_cast<const unsigned char*>(V) + (size_t)(lm_stride - 1) * si.row * 2;
+        if (!make_map(&mkl, K, BH, S, f16, n_lm, lm_stride, si.row, si.head) ||
+            !make_map(&mvl, V, BH, S, f16, n_lm, lm_stride, si.row, si.head) ||
+            !make_map(&mvp, n_prev > 0 ? v_prev : V, BH, S, f16, n_prev > 0 ? n_prev : 1, lm_stride, si.row, si.head))
             return fail(ctx, LOGOS_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed for the landmark views");
     }
     const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
     TcArgs a;
     a.O = O; a.S = S;
+    a.o_row = so.row; a.o_slab = so.head;
     a.out_is_f32 = out_dtype == LOGOS_F32;
     a.o_al32 = aligned32(O) ? 1 : 0;
     a.in_is_f16 = f16;

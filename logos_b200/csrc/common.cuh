@@ -221,14 +221,15 @@ int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_
 size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
-                   const logos_attn_params*);
+                   const logos_attn_params*, const logos_strides* in = nullptr, const logos_strides* out = nullptr);
 bool attention_window_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
 int attention_window(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
                      void* O, int B, int H, int S, int DH, const logos_attn_params*);
 int umma_selftest(logos_ctx*, int mode, int dtype, const void* A, const void* B, float* D);
 bool attention_tc_eligible(int in_dtype, int out_dtype, int DH, const logos_attn_params* p, int S);
 int attention_tc(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K, const void* V,
-                 void* O, int B, int H, int S, int DH, const logos_attn_params*);
+                 void* O, int B, int H, int S, int DH, const logos_attn_params*, const logos_strides* in = nullptr,
+                 const logos_strides* out = nullptr);
 void comm_peer_epilogue(const logos_comm* c, int H_local, PeerEpilogue* out);
 int comm_wait(logos_ctx*, logos_comm*, void* gathered, size_t bytes);
 int comm_collect_rows(logos_ctx*, logos_comm*, float* gathered, int B, int H_total, int DH,

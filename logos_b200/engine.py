@@ -90,6 +90,21 @@ class Engine:
                                                 _ptr(V), _ptr(out), B, H, S, DH, C.byref(params)))
         return out
 
+    def attention_strided(self, Q, K, V, params: L.Params, out=None, out_dtype=None):
+        """Q, K, V: views of shape [B, H, S, DH] with any batch / head / row strides (the last dimension
+        contiguous, one layout for the three); `out`: such a view too, or None for a packed tensor."""
+        B, H, S, DH = Q.shape
+        assert Q.stride() == K.stride() == V.stride() and Q.stride(3) == 1
+        if out is None:
+            out = torch.empty((B, H, S, DH), dtype=out_dtype or Q.dtype, device=Q.device)
+        assert out.shape == Q.shape and out.stride(3) == 1
+        si = L.Strides(Q.stride(0), Q.stride(1), Q.stride(2))
+        so = L.Strides(out.stride(0), out.stride(1), out.stride(2))
+        self._check(self.lib.logos_attention_fwd_strided(self.h, _DT[Q.dtype], _DT[out.dtype], _ptr(Q), _ptr(K), _ptr(V),
+                                                        _ptr(out), B, H, S, DH, C.byref(si), C.byref(so),
+                                                        C.byref(params)))
+        return out
+
     # ---- projections -----------------------------------------------------------
     def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False):
         """X: [B*S, D] 16-bit; Wt_qkv: [3*H*64, D] (K-major shadow of the stacked W_Q | W_K | W_V) ->

@@ -17,6 +17,11 @@ ERR_SCRATCH_LIMIT = 7
 ERR_KERNEL_TIMEOUT = 8
 F32, BF16, F16 = 0, 1, 2
 DIFFUSE_NONE, DIFFUSE_CAUSAL, DIFFUSE_CENTRAL = 0, 1, 2
+class Strides(C.Structure):
+    """logos_strides: elements between two sequences, two heads, two rows."""
+    _fields_ = [("batch", C.c_int64), ("head", C.c_int64), ("row", C.c_int64)]
+
+
 MHA_ATTEND_DEQUANTIZED = 1
 OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK, OPT_GEMM_NARROW, OPT_DECODE_DEPTH = 0, 1, 2, 3, 4, 5
 COMM_HANDLE_BYTES = 80
@@ -85,6 +90,7 @@ SIGNATURES = {
     "logos_qkv_project": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "logos_project_heads": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_kv_dequantize16": (_i, [_vp, _i, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
+    "logos_attention_fwd_strided": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _PP]),
     "logos_attention_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_mha_workspace_bytes": (_sz, [_i, _i, _i, _i]),
