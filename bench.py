@@ -681,9 +681,12 @@ def run_ours(args) -> None:
         decoders.append(ShardedDecoder(eng, kc, vc, ks, vs, params, rank, world, gather="peer", comm=comm))
     torch.cuda.synchronize()
 
-    q, qp, kn, vn = (torch.randn((B, Hl, DH), device=dev, generator=g).half() for _ in range(4))
+    dblock = torch.randn((4, B, Hl, DH), device=dev, generator=g).half()     # q | q_prev | k_new | v_new
+    q, qp, kn, vn = dblock[0], dblock[1], dblock[2], dblock[3]
     lens = torch.full((B,), S_MAX, dtype=torch.int32, device=dev)
-    hq, hqp, hkn, hvn = (t.cpu().pin_memory() for t in (q, qp, kn, vn))
+    # the step's four host tensors in one pinned block, one after the other: the entry point sends them as one copy
+    hblock = dblock.cpu().pin_memory()
+    hq, hqp, hkn, hvn = hblock[0], hblock[1], hblock[2], hblock[3]
     hlens = lens.cpu().pin_memory()
     hout = torch.empty((B, H, DH), dtype=torch.float32).pin_memory()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -749,8 +752,8 @@ def run_ours(args) -> None:
         e2e_how = "logos_decode_step_int8_host: copies, append, decode, copy back, synchronise"
     elif not args.no_graph:
         def e2e_fn(i):
-            for dst, src in zip((q, qp, kn, vn, lens), (hq, hqp, hkn, hvn, hlens)):
-                dst.copy_(src, non_blocking=True)
+            dblock.copy_(hblock, non_blocking=True)
+            lens.copy_(hlens, non_blocking=True)
             hout.copy_(decoders[i % n_sets].replay(), non_blocking=True)
             torch.cuda.current_stream().synchronize()
         e2e_how = "pinned-host copies in, the step's graph, copy of the gathered rows back, synchronise"

@@ -125,10 +125,11 @@ def test_full_size_benchmark_shape(engine):
     assert np.abs(a - b_).max() < 1e-5
 
 
-@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("pinned", [True, False, "one block"])
 def test_host_step_entry_point(engine, pinned):
     """logos_decode_step_int8_host == append + decode on device tensors, with page-locked host
-    buffers (new K/V rows and the output are not staged) and with pageable ones (everything is)."""
+    buffers (separate allocations, which may be neighbours in address space but must not be copied as one),
+    with pageable ones, and with the four tensors in one page-locked block (sent as one copy)."""
     B, H, S_max, DH = 4, 4, 512, 64
     lens0 = np.array([10, 100, 300, 511], np.int32)
     kq, vq, ks, vs = make_cache(B, H, S_max, lens0, 21)
@@ -136,10 +137,14 @@ def test_host_step_entry_point(engine, pinned):
     kc, vc, ksd, vsd = dev(kq), dev(vq), dev(ks), dev(vs)
     kc2, vc2 = kc.clone(), vc.clone()
     host = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
-    q = host(torch.randn(B, H, DH).half())
-    qp = host(torch.randn(B, H, DH).half())
-    kn = host(torch.randn(B, H, DH).half())
-    vn = host(torch.randn(B, H, DH).half())
+    if pinned == "one block":
+        block = torch.randn(4, B, H, DH).half().pin_memory()
+        q, qp, kn, vn = block[0], block[1], block[2], block[3]
+    else:
+        q = host(torch.randn(B, H, DH).half())
+        qp = host(torch.randn(B, H, DH).half())
+        kn = host(torch.randn(B, H, DH).half())
+        vn = host(torch.randn(B, H, DH).half())
     lens = host(torch.from_numpy(lens0 + 1))
     out = host(torch.full((B, H, DH), float("nan")))
     p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
