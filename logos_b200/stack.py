@@ -76,6 +76,7 @@ class AttentionStack:
         self.Wt_lm = sh(w["lm_head"].t())                                                          # [V, D]
         self.embed = w["embed"].to(dtype)
         self.ln_g, self.ln_b = w["ln_gamma"].float(), w["ln_beta"].float()
+        self.ln_g16, self.ln_b16 = self.ln_g.to(dtype), self.ln_b.to(dtype)
         self.cache = KVCache(cfg.num_layers, batch, self.Hl, cfg.max_seq_len, 64, device=self.embed.device)
         self.q_prev = torch.zeros((cfg.num_layers, batch, self.Hl, 64), dtype=torch.float16, device=self.embed.device)
         self.batch = batch
@@ -88,7 +89,8 @@ class AttentionStack:
 
     # ---- pieces ------------------------------------------------------------------------------
     def _norm(self, X, l):
-        return F.layer_norm(X.float(), (self.cfg.d_model,), self.ln_g[l], self.ln_b[l], 1e-5).to(self.dtype)
+        # one kernel: 16-bit in and out, fp32 statistics inside
+        return F.layer_norm(X, (self.cfg.d_model,), self.ln_g16[l], self.ln_b16[l], 1e-5)
 
     def _gather(self, local, shape_tail):
         """[B, H_loc, ...] -> [B, H, ...] on every rank."""
@@ -129,8 +131,8 @@ class AttentionStack:
         lens = self.cache.lens
         for l in range(cfg.num_layers):
             xn = self._norm(x, l)
-            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl)
-            q, k, v = (t.view(B, self.Hl, 64).half() for t in (q, k, v))
+            # the decode entry points take FP16: Q, K, V come as one block and are converted as one
+            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True).half().view(3, B, self.Hl, 64).unbind(0)
             kc, vc, ks, vs = self.cache.layer(l)
             if self.world == 1:
                 o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params)
