@@ -347,9 +347,11 @@ int logos_kv_dequantize16(logos_ctx* ctx, int dst_dtype, const int8_t* src, int6
  *   concat   = sum_h head_out_h · W_O[h]
  *   out      = concat · W_proj (+ residual)
  * X: [B*S][D_model] in `dtype` (BF16 or FP16); Wt_qkv [3*H*64][D_model], Wt_o [D_model][H*64], Wt_proj
- * [D_model][D_model]: K-major 16-bit shadows of the weights in the same dtype (INTEGRATION.md gives the
- * index maps; for the CPU classes, which keep columns [h*64, h*64+64) of head_out_h · W_O[h], Wt_o is block
- * diagonal).  out, residual: [B*S][D_model] in out_dtype (`dtype` or LOGOS_F32); residual may be NULL.
+ * [D_model][D_model]: K-major 16-bit shadows of the weights in the same dtype,
+ *   Wt_qkv[(which*H + h)*64 + c][k] = W_which[h][k][c]   (which = 0, 1, 2 for Q, K, V),
+ *   Wt_o[n][h*64 + c] = W_O[h][c][n],   Wt_proj[n][k] = W_proj[k][n];
+ * for the CPU classes, which keep columns [h*64, h*64+64) of head_out_h · W_O[h], Wt_o is block diagonal
+ * (Wt_o[h*64 + j][h*64 + c] = W_O[h][c][j], zero elsewhere).  out, residual: [B*S][D_model] in out_dtype (`dtype` or LOGOS_F32); residual may be NULL.
  * k_cache, v_cache: int8 [B][H][S_max][64], k_scale, v_scale: float [B][H]; the four together or all NULL.
  * scratch: device memory of logos_mha_workspace_bytes(B, S, H, D_model) bytes, 256-byte aligned, owned by
  * the caller and free again when the call's work on the stream has finished.  H * 64 need not equal D_model. */
