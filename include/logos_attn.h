@@ -172,6 +172,16 @@ int logos_attention_bwd(logos_ctx* ctx, const float* Q, const float* K, const fl
                         float* dQ, float* dK, float* dV, int B, int H, int S, int DH,
                         const logos_attn_params* params);
 
+/* The same gradients on the tensor cores: Q, K, V, dO in `dtype` (BF16 or FP16) [B][H][S][64], dQ, dK, dV
+ * fp32; every product a tcgen05 MMA with fp32 accumulation, the probabilities recomputed per 128 x 128 tile
+ * and handed to the next product as 16-bit operands (so results carry the 16-bit rounding of the weights:
+ * about 1e-2 of the largest gradient in BF16, 2e-3 in FP16).  Same `params` rules as logos_attention_bwd.
+ * Workspace from the context (logos_attention_bwd16_workspace_bytes / logos_ctx_reserve). */
+size_t logos_attention_bwd16_workspace_bytes(int B, int H, int S, int DH);
+int logos_attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, const void* V, const void* dO,
+                          float* dQ, float* dK, float* dV, int B, int H, int S, int DH,
+                          const logos_attn_params* params);
+
 /* Prefill of one layer in one call: logos_attention_fwd, and before it -- when k_cache is non-NULL --
  * the layer's INT8 cache filled from the raw K and V.  This is the order of ModelGPU::forward, which
  * quantises a head's K and V (cuda/ModelGPU.cu:908) before the Navier-Stokes prologue and the attention

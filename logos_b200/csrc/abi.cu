@@ -326,6 +326,18 @@ int logos_attention_bwd(logos_ctx* ctx, const float* Q, const float* K, const fl
     return logos::attention_bwd(ctx, Q, K, V, dO, dQ, dK, dV, B, H, S, DH, params);
 }
 
+size_t logos_attention_bwd16_workspace_bytes(int B, int H, int S, int DH) {
+    return logos::attention_bwd16_workspace_bytes(B, H, S, DH);
+}
+
+int logos_attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, const void* V, const void* dO,
+                          float* dQ, float* dK, float* dV, int B, int H, int S, int DH,
+                          const logos_attn_params* params) {
+    if (!ctx) return LOGOS_ERR_INVALID_ARG;
+    if (!params_ok(params)) return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_bwd16: bad parameter block");
+    return logos::attention_bwd16(ctx, dtype, Q, K, V, dO, dQ, dK, dV, B, H, S, DH, params);
+}
+
 int logos_prefill_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, const void* K,
                       const void* V, void* O, int B, int H, int S, int DH,
                       const logos_attn_params* params, int8_t* k_cache, int8_t* v_cache,

@@ -408,6 +408,15 @@ int run_path(logos_ctx* ctx, BwdArgs& a, int BH) {
 
 }  // namespace
 
+// dQ, dV (+)= the transposed stencils applied to a path's dQ_adv, dV_s (shared with the tensor-core backward)
+int attention_bwd_adjoint(logos_ctx* ctx, const float* dQa, const float* dVs, float* dQ, float* dV, int S, int DH,
+                          float eta, float nu, int mode, int ns, int accumulate, int64_t total) {
+    const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->sm_count * 16);
+    bwd_adjoint_kernel<<<blocks, 256, 0, ctx->stream>>>(dQa, dVs, dQ, dV, S, DH, eta, nu, mode, ns, accumulate, total);
+    LOGOS_LAUNCH_CHECK(ctx, "bwd_adjoint_kernel");
+    return LOGOS_OK;
+}
+
 size_t attention_bwd_workspace_bytes(int B, int H, int S, int DH) {
     if (B <= 0 || H <= 0 || S <= 0 || DH <= 0) return 0;
     const size_t t = ((size_t)B * H * S * DH * sizeof(float) + 255) & ~(size_t)255;

@@ -1,0 +1,612 @@
+// attn_bwd_tc.cu -- attention backward on the tensor cores (tcgen05), 16-bit operands, fp32 accumulation.
+//
+// The same mathematics as attn_bwd.cu (the chain of cuda/train_gpu.cu:657-748 without any seq x seq buffer, the
+// forward's own mask), with every product on tcgen05.mma and the operands staged by TMA:
+//
+//   bwd_tc_rows_kernel   one CTA per 128 query rows, one pass over the visible key tiles with a running maximum:
+//       S = Qx K^T, dP = dO Vx^T                         (two M128 N128 products into tensor memory)
+//       e = 2^(c S - m), l += sum e, D += sum e dP       (one thread per row; m moves lazily, as in the forward)
+//       A += (e dP) K,  B += e K                         (weights written back to tensor memory as 16-bit A operands)
+//     and at the end  delta = D / l,  dQx = scale (A - delta B) / l,  lse = m + log2 l.
+//   bwd_tc_keys_kernel   one CTA per 128 keys, over the query tiles that see them, transposed so that a thread
+//     owns a key:  S^T = K Qx^T, dP^T = Vx dO^T,  P^T = 2^(c S^T - lse_i),  dS^T = P^T (dP^T - delta_i) scale,
+//       dVx += P^T dO,  dK += dS^T Qx.
+//
+// Qx, Vx are the advected queries and diffused values (16-bit, made by a prologue kernel when the Navier-Stokes
+// terms are on); the transposed stencils and the blend are handled around the kernels as in attn_bwd.cu.
+// Tensor memory: 512 columns per CTA (two 128-column products, two 64-column weight operands, two 64-column
+// accumulators), so one CTA per SM.  Every mbarrier wait is bounded; a wait that runs out raises the context's
+// status word (LOGOS_ERR_KERNEL_TIMEOUT) and the CTA winds down.
+#include <algorithm>
+
+#include "tcgen05_ptx.cuh"
+
+namespace logos {
+namespace {
+
+using namespace tc;
+
+constexpr int kBT = 128;                     // rows of a tile (queries or keys)
+constexpr int kBD = 64;                      // head dimension
+constexpr int kBTile = kBT * kBD * 2;        // 16 KiB
+constexpr int kBwdTcThreads = 160;           // four softmax warps + one control warp
+constexpr float kLazy = 4.0f;                // the running maximum moves when it would grow by more than 2^4
+
+struct BwdTcArgs {
+    float* dQx; float* dK; float* dVx;       // [BH][S][64] fp32
+    float* lse; float* delta;                // [BH][S]: log2-domain log-sum-exp (c folded in) and delta
+    int S;
+    float c, scale, w;                       // c = scale * log2(e); w multiplies the results (share of a blend)
+    int causal, shunyam, window, stride, f16, accumulate_dk;
+    int* status;
+};
+
+// does key tile [k0, k0 + 128) show anything to query rows [q0, q_last]?
+__device__ __forceinline__ bool tile_visible(const BwdTcArgs& a, int q0, int q_last, int k0) {
+    if (k0 >= a.S) return false;
+    if (a.causal && k0 > q_last) return false;
+    if (!a.shunyam) return true;
+    const bool in_win = (k0 + kBT - 1 >= q0 - a.window) && (k0 <= q_last);
+    bool has_land = false;
+    if (a.stride > 0) {
+        const int first = ((k0 + a.stride - 1) / a.stride) * a.stride;
+        has_land = first < k0 + kBT && first < a.S;
+    }
+    return in_win || has_land;
+}
+
+__device__ __forceinline__ uint32_t pack2(float x, float y, bool f16) { return f32_to_16(x, f16) | (f32_to_16(y, f16) << 16); }
+
+// MN-major B operand: a [128 rows (the k dimension)][64] tile as TMA wrote it, 16 rows (2048 bytes) per k step
+__device__ __forceinline__ uint64_t desc_rows(uint32_t tile, int kk) { return smem_desc(tile + (uint32_t)kk * 2048u); }
+// K-major operand: 16 of the 64 channels (32 bytes) per k step
+__device__ __forceinline__ uint64_t desc_chan(uint32_t tile, int kk) { return smem_desc(tile + (uint32_t)kk * 32u); }
+
+// 32 fp32 values -> 16 packed words written to tensor memory columns [col, col + 16)
+__device__ __forceinline__ void st_packed32(uint32_t taddr, const float* v, bool f16) {
+    uint32_t pk[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pk[e] = pack2(v[16 * h + 2 * e], v[16 * h + 2 * e + 1], f16);
+        tc_st8(taddr + 8u * (uint32_t)h, pk);
+    }
+}
+
+enum { RB_QG = 0, RB_KVFULL0, RB_KVFULL1, RB_KVEMPTY0, RB_KVEMPTY1, RB_SFULL, RB_SEMPTY, RB_WFULL, RB_ACC, RB_NUM };
+constexpr int kRowsSmem = 6 * kBTile + RB_NUM * 8 + 64 + 1024;
+
+__global__ void __launch_bounds__(kBwdTcThreads, 1)
+bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t sQ = sbase, sG = sbase + kBTile, sK = sbase + 2 * kBTile, sV = sbase + 4 * kBTile;
+    const uint32_t bar0 = sbase + 6 * kBTile;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBTile + RB_NUM * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 6 * kBTile + RB_NUM * 8 + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = a.S, bh = blockIdx.y;
+    const int q0 = blockIdx.x * kBT, q_last = min(S, q0 + kBT) - 1;
+    const int kt_end = (S + kBT - 1) / kBT;
+    const bool f16 = a.f16 != 0;
+
+    if (warp == 4 && lane == 0) {
+        mbar_init(bar(RB_QG), 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(RB_KVFULL0 + s), 1); mbar_init(bar(RB_KVEMPTY0 + s), 1); }
+        mbar_init(bar(RB_SFULL), 1);
+        mbar_init(bar(RB_SEMPTY), 128);
+        mbar_init(bar(RB_WFULL), 128);
+        mbar_init(bar(RB_ACC), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    // columns: S 0, dP 128, W1 = e dP 256, W2 = e 320, A 384, B 448
+    constexpr uint32_t cS = 0, cP = 128, cW1 = 256, cW2 = 320, cA = 384, cB = 448;
+
+    auto next_visible = [&](int kt) {        // first visible key tile at or after kt (kt_end: none)
+        while (kt < kt_end && !tile_visible(a, q0, q_last, kt * kBT)) ++kt;
+        return kt;
+    };
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const int fmt = f16 ? 0 : 1;
+            const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
+            mbar_expect_tx(bar(RB_QG), 2 * kBTile);
+            tma_load_3d(sQ, &mapQ, 0, q0, bh, bar(RB_QG));
+            tma_load_3d(sG, &mapG, 0, q0, bh, bar(RB_QG));
+            int kt_load = next_visible(0), n_load = 0;
+            bool ok = true;
+            auto load_next = [&]() {         // the next visible tile into the stage that is (or becomes) free
+                if (kt_load >= kt_end) return;
+                const int st = n_load & 1;
+                if (n_load >= 2 && !mbar_wait(bar(RB_KVEMPTY0 + st), ((n_load >> 1) - 1) & 1, abort_flag)) { ok = false; return; }
+                mbar_expect_tx(bar(RB_KVFULL0 + st), 2 * kBTile);
+                tma_load_3d(sK + st * kBTile, &mapK, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
+                tma_load_3d(sV + st * kBTile, &mapV, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
+                ++n_load;
+                kt_load = next_visible(kt_load + 1);
+            };
+            auto issue_scores = [&](int n) {  // S = Qx K^T, dP = dO Vx^T of the n-th visible tile
+                const int st = n & 1;
+                if (n == 0 && !mbar_wait(bar(RB_QG), 0, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(bar(RB_KVFULL0 + st), (n >> 1) & 1, abort_flag)) { ok = false; return; }
+                if (n > 0 && !mbar_wait(bar(RB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBD / 16; ++kk) {
+                    tc_mma_f16(tmem + cS, desc_chan(sQ, kk), desc_chan(sK + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma_f16(tmem + cP, desc_chan(sG, kk), desc_chan(sV + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(RB_SFULL));
+            };
+            load_next();
+            load_next();
+            int kt = next_visible(0), n = 0;
+            if (ok && kt < kt_end) issue_scores(0);
+            while (ok && kt < kt_end) {
+                const int st = n & 1;
+                const int kt_next = next_visible(kt + 1);
+                if (!mbar_wait(bar(RB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBT / 16; ++kk) {
+                    const uint64_t bd = desc_rows(sK + st * kBTile, kk);
+                    const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
+                    tc_mma_f16_ta(tmem + cA, tmem + cW1 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
+                    tc_mma_f16_ta(tmem + cB, tmem + cW2 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
+                }
+                tc_commit(bar(RB_ACC));
+                tc_commit(bar(RB_KVEMPTY0 + st));
+                if (kt_next < kt_end) issue_scores(n + 1);
+                if (ok) load_next();
+                kt = kt_next;
+                ++n;
+            }
+        }
+    } else {
+        // ================= one thread per query row =================
+        const int r = warp * 32 + lane, i = q0 + r;
+        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        const bool causal = a.causal != 0, shun = a.shunyam != 0;
+        float m_run = -INFINITY, l_run = 0.0f, d_run = 0.0f;
+        bool ok = true;
+        int n = 0;
+        for (int kt = next_visible(0); ok && kt < kt_end; kt = next_visible(kt + 1), ++n) {
+            const int k0 = kt * kBT;
+            if (!mbar_wait(bar(RB_SFULL), n & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            float s[kBT];
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) tc_ld32(tmem + lane_addr + cS + 32 * cb, s + 32 * cb);
+            tc_wait_ld();
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kBT; ++j) {
+                const bool okj = i < S && k0 + j < S && key_allowed(i, k0 + j, causal, shun, a.window, a.stride);
+                s[j] = okj ? s[j] * a.c : -INFINITY;
+                mx = fmaxf(mx, s[j]);
+            }
+            // lazy running maximum: a warp-wide decision, because the correction is a warp-collective access
+            const bool want = (mx > m_run + kLazy) || (m_run == -INFINITY && mx > -INFINITY);
+            const bool any = __any_sync(0xffffffffu, want && n > 0 && m_run > -INFINITY);
+            float m_new = want ? mx : m_run;
+            if (any && m_new < mx) m_new = mx;       // correcting anyway: take the exact maximum
+            if (n > 0) {       // the accumulators and the weight columns are in use until the previous products are done
+                if (!mbar_wait(bar(RB_ACC), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+            }
+            if (any) {
+                const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
+#pragma unroll
+                for (int hc = 0; hc < 4; ++hc) {       // A and B are neighbours: 128 columns from cA
+                    float o[32];
+                    tc_ld32(tmem + lane_addr + cA + 32 * hc, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= f;
+                    tc_st32(tmem + lane_addr + cA + 32 * hc, o);
+                }
+                l_run *= f;
+                d_run *= f;
+            }
+            // without `any`, a lane only moves its maximum while its sums are still empty (first tile, or nothing seen yet)
+            m_run = m_new;
+            const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
+            float lsum = 0.0f, dsum = 0.0f;
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                float dp[32], w1[32];
+                tc_ld32(tmem + lane_addr + cP + 32 * cb, dp);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float e = ex2(s[32 * cb + j] + neg_m);      // -inf gives 0
+                    s[32 * cb + j] = e;
+                    lsum += e;
+                    w1[j] = e * dp[j];
+                    dsum += w1[j];
+                }
+                st_packed32(tmem + lane_addr + cW1 + 16 * cb, w1, f16);
+                st_packed32(tmem + lane_addr + cW2 + 16 * cb, s + 32 * cb, f16);
+            }
+            l_run += lsum;
+            d_run += dsum;
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(RB_SEMPTY));      // S and dP have been read
+            mbar_arrive(bar(RB_WFULL));       // the weights are in place
+        }
+        if (ok && n > 0) ok = mbar_wait(bar(RB_ACC), (n - 1) & 1, abort_flag);
+        if (ok) {
+            tc_fence_after();
+            const bool live = n > 0 && l_run > 1e-9f;     // a row that saw nothing was written as zeros by the forward
+            const float inv = live ? 1.0f / l_run : 0.0f;
+            const float dlt = d_run * inv;
+            if (i < S) {
+                a.lse[(size_t)bh * S + i] = live ? m_run + log2f(l_run) : INFINITY;
+                a.delta[(size_t)bh * S + i] = dlt;
+            }
+            float* dst = a.dQx + ((size_t)bh * S + i) * kBD;
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+                float av[32], bv[32];
+                if (n > 0) {
+                    tc_ld32(tmem + lane_addr + cA + 32 * hc, av);
+                    tc_ld32(tmem + lane_addr + cB + 32 * hc, bv);
+                    tc_wait_ld();
+                }
+                if (i < S) {
+                    const float k1 = a.scale * inv * a.w;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (live) o4 = make_float4((av[j] - dlt * bv[j]) * k1, (av[j + 1] - dlt * bv[j + 1]) * k1,
+                                                   (av[j + 2] - dlt * bv[j + 2]) * k1, (av[j + 3] - dlt * bv[j + 3]) * k1);
+                        *reinterpret_cast<float4*>(dst + 32 * hc + j) = o4;
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+enum { KB_KV = 0, KB_QGFULL0, KB_QGFULL1, KB_QGEMPTY0, KB_QGEMPTY1, KB_SFULL, KB_SEMPTY, KB_WFULL, KB_ACC, KB_STAT, KB_NUM };
+constexpr int kKeysOffStat = 6 * kBTile;                       // [2][2][128] floats: lse, delta of two query tiles in turn
+constexpr int kKeysOffBar = kKeysOffStat + 2 * 2 * kBT * 4;
+constexpr int kKeysSmem = kKeysOffBar + KB_NUM * 8 + 64 + 1024;
+
+__global__ void __launch_bounds__(kBwdTcThreads, 1)
+bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t sK = sbase, sV = sbase + kBTile, sQ = sbase + 2 * kBTile, sG = sbase + 4 * kBTile;
+    float* stat = reinterpret_cast<float*>(smem + kKeysOffStat);
+    const uint32_t bar0 = sbase + kKeysOffBar;
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kKeysOffBar + KB_NUM * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kKeysOffBar + KB_NUM * 8 + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = a.S, bh = blockIdx.y;
+    const int k0 = blockIdx.x * kBT, k_last = min(S, k0 + kBT) - 1;
+    const bool f16 = a.f16 != 0;
+    // query tiles that can see these keys: from the diagonal on (causal); a pure window ends them early
+    const int qt_begin = a.causal ? k0 / kBT : 0;
+    int qt_end = (S + kBT - 1) / kBT;
+    if (a.shunyam && a.stride <= 0) qt_end = min(qt_end, (k_last + a.window) / kBT + 1);
+
+    if (warp == 4 && lane == 0) {
+        mbar_init(bar(KB_KV), 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(KB_QGFULL0 + s), 1); mbar_init(bar(KB_QGEMPTY0 + s), 1); }
+        mbar_init(bar(KB_SFULL), 1);
+        mbar_init(bar(KB_SEMPTY), 128);
+        mbar_init(bar(KB_WFULL), 128);
+        mbar_init(bar(KB_ACC), 1);
+        mbar_init(bar(KB_STAT), 128);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    // columns: S^T 0, dP^T 128, P^T 256, dS^T 320, dV 384, dK 448
+    constexpr uint32_t cS = 0, cP = 128, cW1 = 256, cW2 = 320, cV = 384, cK = 448;
+
+    auto next_visible = [&](int qt) {        // first query tile at or after qt that sees this key tile
+        while (qt < qt_end && !tile_visible(a, qt * kBT, min(S, qt * kBT + kBT) - 1, k0)) ++qt;
+        return qt;
+    };
+
+    if (warp == 4) {
+        if (lane == 0) {
+            const int fmt = f16 ? 0 : 1;
+            const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
+            mbar_expect_tx(bar(KB_KV), 2 * kBTile);
+            tma_load_3d(sK, &mapK, 0, k0, bh, bar(KB_KV));
+            tma_load_3d(sV, &mapV, 0, k0, bh, bar(KB_KV));
+            int qt_load = next_visible(qt_begin), n_load = 0;
+            bool ok = true;
+            auto load_next = [&]() {
+                if (qt_load >= qt_end) return;
+                const int st = n_load & 1;
+                if (n_load >= 2 && !mbar_wait(bar(KB_QGEMPTY0 + st), ((n_load >> 1) - 1) & 1, abort_flag)) { ok = false; return; }
+                mbar_expect_tx(bar(KB_QGFULL0 + st), 2 * kBTile);
+                tma_load_3d(sQ + st * kBTile, &mapQ, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
+                tma_load_3d(sG + st * kBTile, &mapG, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
+                ++n_load;
+                qt_load = next_visible(qt_load + 1);
+            };
+            auto issue_scores = [&](int n) {  // S^T = K Qx^T, dP^T = Vx dO^T of the n-th visible query tile
+                const int st = n & 1;
+                if (n == 0 && !mbar_wait(bar(KB_KV), 0, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(bar(KB_QGFULL0 + st), (n >> 1) & 1, abort_flag)) { ok = false; return; }
+                if (n > 0 && !mbar_wait(bar(KB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; return; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBD / 16; ++kk) {
+                    tc_mma_f16(tmem + cS, desc_chan(sK, kk), desc_chan(sQ + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma_f16(tmem + cP, desc_chan(sV, kk), desc_chan(sG + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(KB_SFULL));
+            };
+            load_next();
+            load_next();
+            int qt = next_visible(qt_begin), n = 0;
+            if (ok && qt < qt_end) issue_scores(0);
+            while (ok && qt < qt_end) {
+                const int st = n & 1;
+                const int qt_next = next_visible(qt + 1);
+                if (!mbar_wait(bar(KB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBT / 16; ++kk) {
+                    const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
+                    tc_mma_f16_ta(tmem + cV, tmem + cW1 + 8u * (uint32_t)kk, desc_rows(sG + st * kBTile, kk), idesc_acc, accu);
+                    tc_mma_f16_ta(tmem + cK, tmem + cW2 + 8u * (uint32_t)kk, desc_rows(sQ + st * kBTile, kk), idesc_acc, accu);
+                }
+                tc_commit(bar(KB_ACC));
+                tc_commit(bar(KB_QGEMPTY0 + st));
+                if (qt_next < qt_end) issue_scores(n + 1);
+                if (ok) load_next();
+                qt = qt_next;
+                ++n;
+            }
+        }
+    } else {
+        // ================= one thread per key =================
+        const int r = warp * 32 + lane, j = k0 + r;
+        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        const bool causal = a.causal != 0, shun = a.shunyam != 0;
+        bool ok = true;
+        int n = 0;
+        for (int qt = next_visible(qt_begin); ok && qt < qt_end; qt = next_visible(qt + 1), ++n) {
+            const int q0 = qt * kBT;
+            // the query tile's statistics: thread r fetches row r's into shared memory, all 128 threads then read all
+            // of them (broadcast reads).  Two buffers in turn: a thread can only write tile n + 2's after every
+            // thread has arrived for tile n + 1, i.e. has finished reading tile n's.  The hand-over is an mbarrier
+            // with a bounded wait, so a CTA that is winding down cannot get stuck in it.
+            float* st_lse = stat + (n & 1) * 2 * kBT;
+            float* st_dlt = st_lse + kBT;
+            st_lse[r] = (q0 + r < S) ? a.lse[(size_t)bh * S + q0 + r] : INFINITY;
+            st_dlt[r] = (q0 + r < S) ? a.delta[(size_t)bh * S + q0 + r] : 0.0f;
+            mbar_arrive(bar(KB_STAT));
+            if (!mbar_wait(bar(KB_STAT), n & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar(KB_SFULL), n & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            float s[kBT];
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) tc_ld32(tmem + lane_addr + cS + 32 * cb, s + 32 * cb);
+            tc_wait_ld();
+#pragma unroll
+            for (int q = 0; q < kBT; ++q) {
+                const bool okq = j < S && q0 + q < S && key_allowed(q0 + q, j, causal, shun, a.window, a.stride);
+                s[q] = okq ? ex2(s[q] * a.c - st_lse[q]) : 0.0f;           // p_ij; lse = +inf for a dead row gives 0
+            }
+            if (n > 0) {
+                if (!mbar_wait(bar(KB_ACC), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+            }
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) {
+                float dp[32];
+                tc_ld32(tmem + lane_addr + cP + 32 * cb, dp);
+                tc_wait_ld();
+#pragma unroll
+                for (int q = 0; q < 32; ++q) dp[q] = s[32 * cb + q] * (dp[q] - st_dlt[32 * cb + q]) * a.scale;   // ds_ij
+                st_packed32(tmem + lane_addr + cW1 + 16 * cb, s + 32 * cb, f16);
+                st_packed32(tmem + lane_addr + cW2 + 16 * cb, dp, f16);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(KB_SEMPTY));
+            mbar_arrive(bar(KB_WFULL));
+        }
+        if (ok && n > 0) ok = mbar_wait(bar(KB_ACC), (n - 1) & 1, abort_flag);
+        if (ok) {
+            tc_fence_after();
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                float* dst = (which == 0 ? a.dVx : a.dK) + ((size_t)bh * S + j) * kBD;
+                const bool acc_out = which == 1 && a.accumulate_dk;
+#pragma unroll
+                for (int hc = 0; hc < 2; ++hc) {
+                    float v[32];
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) v[q] = 0.0f;
+                    if (n > 0) {
+                        tc_ld32(tmem + lane_addr + (which == 0 ? cV : cK) + 32 * hc, v);
+                        tc_wait_ld();
+                    }
+                    if (j < S) {
+#pragma unroll
+                        for (int q = 0; q < 32; q += 4) {
+                            float4* p4 = reinterpret_cast<float4*>(dst + 32 * hc + q);
+                            float4 o4 = make_float4(v[q] * a.w, v[q + 1] * a.w, v[q + 2] * a.w, v[q + 3] * a.w);
+                            if (acc_out) { const float4 old = *p4; o4.x += old.x; o4.y += old.y; o4.z += old.z; o4.w += old.w; }
+                            *p4 = o4;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// Qx = advect(Q), Vx = diffuse(V) in the operand type (ns_advect_kernel, ns_diffuse_kernel, cuda/ModelGPU.cu:443-471;
+// the central stencil is navier_stokes_attention's, include/Attention.hpp:168-182), fp32 arithmetic, one rounding
+template <typename T>
+__global__ void bwd16_prologue_kernel(const T* __restrict__ Q, const T* __restrict__ V, T* __restrict__ Qa, T* __restrict__ Vs,
+                                      int S, float eta, float nu, int mode, int64_t total) {
+    for (int64_t x = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; x < total; x += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)((x / kBD) % S);
+        const float q = to_f32<T>(Q[x]), v = to_f32<T>(V[x]);
+        const float qp = i > 0 ? to_f32<T>(Q[x - kBD]) : q;
+        Qa[x] = from_f32<T>(q + eta * (q - qp));
+        float vs = v;
+        if (mode == LOGOS_DIFFUSE_CAUSAL) {
+            const float vp = i > 0 ? to_f32<T>(V[x - kBD]) : v;
+            vs = (1.0f - nu) * v + nu * vp;
+        } else if (mode == LOGOS_DIFFUSE_CENTRAL) {
+            const float vl = i > 0 ? to_f32<T>(V[x - kBD]) : v, vr = i < S - 1 ? to_f32<T>(V[x + kBD]) : v;
+            vs = (1.0f - nu) * v + (nu * 0.5f) * (vl + vr);
+        }
+        Vs[x] = from_f32<T>(vs);
+    }
+}
+
+// [BH][S][64] 16-bit tensor, box = 128 rows x 64 channels of one head, 128-byte swizzle
+bool make_map_bwd(CUtensorMap* m, const void* base, int BH, int S, bool f16) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)kBD, (cuuint64_t)S, (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)kBD * 2, (cuuint64_t)S * kBD * 2};
+    cuuint32_t box[3] = {(cuuint32_t)kBD, (cuuint32_t)kBT, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+size_t attention_bwd16_workspace_bytes(int B, int H, int S, int DH) {
+    if (B <= 0 || H <= 0 || S <= 0 || DH <= 0) return 0;
+    const size_t n = (size_t)B * H * S * DH;
+    const size_t t16 = (n * 2 + 255) & ~(size_t)255, t32 = (n * 4 + 255) & ~(size_t)255;
+    const size_t r = ((size_t)B * H * S * 4 + 255) & ~(size_t)255;
+    return kWorkspaceCounterBytes + 2 * t16 + 2 * t32 + 2 * r;     // Qx, Vx; dQx, dVx; log-sum-exp, delta
+}
+
+int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, const void* V, const void* dO, float* dQ,
+                    float* dK, float* dV, int B, int H, int S, int DH, const logos_attn_params* p) {
+    if (!Q || !K || !V || !dO || !dQ || !dK || !dV || B <= 0 || H <= 0 || S <= 0)
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_bwd16: bad pointer or extent");
+    if (dtype != LOGOS_BF16 && dtype != LOGOS_F16)
+        return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: operands are BF16 or FP16");
+    if (DH != kBD) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: DH must be 64, got %d", DH);
+    if ((int64_t)B * H > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: B*H > 65535");
+    if (!(p->scale > 0.0f)) return fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_bwd16: scale must be positive");
+    const void* ptrs[7] = {Q, K, V, dO, dQ, dK, dV};
+    for (const void* q : ptrs)
+        if (!aligned16(q)) return fail(ctx, LOGOS_ERR_ALIGNMENT, "attention_bwd16: tensors must be 16-byte aligned");
+    if (!ctx->tc_status) return fail(ctx, LOGOS_ERR_WORKSPACE, "attention_bwd16: status word missing");
+    const size_t need = attention_bwd16_workspace_bytes(B, H, S, DH);
+    if (!ctx->workspace || ctx->workspace_bytes < need)
+        return fail(ctx, LOGOS_ERR_WORKSPACE, "attention_bwd16: workspace of %zu bytes needed, %zu reserved "
+                    "(logos_attention_bwd16_workspace_bytes / logos_ctx_reserve)", need, ctx->workspace_bytes);
+    const int BH = B * H;
+    const int64_t total = (int64_t)BH * S * DH;
+    const size_t t16 = ((size_t)total * 2 + 255) & ~(size_t)255, t32 = ((size_t)total * 4 + 255) & ~(size_t)255;
+    const size_t r = ((size_t)BH * S * 4 + 255) & ~(size_t)255;
+    char* ws = static_cast<char*>(ctx->workspace) + kWorkspaceCounterBytes;
+    void* Qa = ws;
+    void* Vs = ws + t16;
+    float* dQa = (float*)(ws + 2 * t16);
+    float* dVs = (float*)(ws + 2 * t16 + t32);
+    float* lse = (float*)(ws + 2 * t16 + 2 * t32);
+    float* delta = (float*)(ws + 2 * t16 + 2 * t32 + r);
+
+    const bool f16 = dtype == LOGOS_F16;
+    const bool ns_any = p->ns_alpha > 0.0f && (p->ns_eta != 0.0f || p->diffuse_mode != LOGOS_DIFFUSE_NONE);
+    const bool std_on = !ns_any || p->ns_alpha < 1.0f;
+    const int mode = ns_any ? p->diffuse_mode : LOGOS_DIFFUSE_NONE;
+    const int ew_blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->sm_count * 16);
+
+    BwdTcArgs a{};
+    a.dQx = dQa; a.dK = dK; a.dVx = dVs; a.lse = lse; a.delta = delta;
+    a.S = S; a.scale = p->scale; a.c = p->scale * 1.4426950408889634f;
+    a.causal = p->causal; a.shunyam = shunyam_active(p->window, S) ? 1 : 0;
+    a.window = p->window; a.stride = p->stride; a.f16 = f16; a.status = ctx->tc_status;
+    if (int rc = ensure_smem_limit(ctx, bwd_tc_rows_kernel, kRowsSmem)) return rc;
+    if (int rc = ensure_smem_limit(ctx, bwd_tc_keys_kernel, kKeysSmem)) return rc;
+    CUtensorMap mk, mg;
+    if (!make_map_bwd(&mk, K, BH, S, f16) || !make_map_bwd(&mg, dO, BH, S, f16))
+        return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
+    dim3 grid((S + kBT - 1) / kBT, BH);
+    auto run = [&](const void* Qx, const void* Vx) -> int {
+        CUtensorMap mq, mv;
+        if (!make_map_bwd(&mq, Qx, BH, S, f16) || !make_map_bwd(&mv, Vx, BH, S, f16))
+            return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
+        bwd_tc_rows_kernel<<<grid, kBwdTcThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_rows_kernel");
+        bwd_tc_keys_kernel<<<grid, kBwdTcThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_keys_kernel");
+        return LOGOS_OK;
+    };
+    bool first = true;
+    if (ns_any) {
+        if (f16) bwd16_prologue_kernel<__half><<<ew_blocks, 256, 0, ctx->stream>>>((const __half*)Q, (const __half*)V, (__half*)Qa, (__half*)Vs, S, p->ns_eta, p->ns_nu, mode, total);
+        else bwd16_prologue_kernel<__nv_bfloat16><<<ew_blocks, 256, 0, ctx->stream>>>((const __nv_bfloat16*)Q, (const __nv_bfloat16*)V, (__nv_bfloat16*)Qa, (__nv_bfloat16*)Vs, S, p->ns_eta, p->ns_nu, mode, total);
+        LOGOS_LAUNCH_CHECK(ctx, "bwd16_prologue_kernel");
+        a.w = p->ns_alpha; a.accumulate_dk = 0;
+        if (int rc = run(Qa, Vs)) return rc;
+        if (int rc = attention_bwd_adjoint(ctx, dQa, dVs, dQ, dV, S, DH, p->ns_eta, p->ns_nu, mode, 1, 0, total)) return rc;
+        first = false;
+    }
+    if (std_on) {
+        a.w = ns_any ? 1.0f - p->ns_alpha : 1.0f; a.accumulate_dk = first ? 0 : 1;
+        if (int rc = run(Q, V)) return rc;
+        if (int rc = attention_bwd_adjoint(ctx, dQa, dVs, dQ, dV, S, DH, 0.0f, 0.0f, LOGOS_DIFFUSE_NONE, 0, first ? 0 : 1, total)) return rc;
+    }
+    return LOGOS_OK;
+}
+
+}  // namespace logos

@@ -201,6 +201,11 @@ int project(logos_ctx*, int dtype, int out_dtype, const void* A, const void* Wt,
             int M, int N, int K);
 int decode_generic(logos_ctx*, const void* q, const void* q_prev, const int8_t*, const int8_t*, const float*,
                    const float*, const int32_t* len, int B, int H, int S_max, int DH, const logos_attn_params*, float* out);
+int attention_bwd_adjoint(logos_ctx*, const float* dQa, const float* dVs, float* dQ, float* dV, int S, int DH, float eta,
+                          float nu, int mode, int ns, int accumulate, int64_t total);
+size_t attention_bwd16_workspace_bytes(int B, int H, int S, int DH);
+int attention_bwd16(logos_ctx*, int dtype, const void* Q, const void* K, const void* V, const void* dO, float* dQ, float* dK,
+                    float* dV, int B, int H, int S, int DH, const logos_attn_params*);
 size_t attention_bwd_workspace_bytes(int B, int H, int S, int DH);
 int attention_bwd(logos_ctx*, const float* Q, const float* K, const float* V, const float* dO, float* dQ, float* dK,
                   float* dV, int B, int H, int S, int DH, const logos_attn_params*);

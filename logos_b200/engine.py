@@ -136,6 +136,17 @@ class Engine:
                                           _ptr(out), M, N, K))
         return out
 
+    def attention_bwd16(self, Q, K, V, dO, params: L.Params):
+        """The gradients on the tensor cores: Q, K, V, dO BF16 or FP16 [B, H, S, 64] -> fp32 (dQ, dK, dV)."""
+        B, H, S, DH = Q.shape
+        for t in (Q, K, V, dO):
+            assert t.dtype == Q.dtype and t.is_contiguous() and t.shape == Q.shape
+        self.reserve(self.lib.logos_attention_bwd16_workspace_bytes(B, H, S, DH))
+        dQ, dK, dV = (torch.empty(Q.shape, dtype=torch.float32, device=Q.device) for _ in range(3))
+        self._check(self.lib.logos_attention_bwd16(self.h, _DT[Q.dtype], _ptr(Q), _ptr(K), _ptr(V), _ptr(dO), _ptr(dQ),
+                                                  _ptr(dK), _ptr(dV), B, H, S, DH, C.byref(params)))
+        return dQ, dK, dV
+
     def attention_bwd(self, Q, K, V, dO, params: L.Params):
         """Gradients (dQ, dK, dV) of attention(Q, K, V, params) for the output gradient dO; fp32 [B, H, S, DH]."""
         B, H, S, DH = Q.shape

@@ -91,6 +91,8 @@ SIGNATURES = {
     "logos_project_heads": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i]),
     "logos_kv_dequantize16": (_i, [_vp, _i, _vp, _i64, _vp, _vp, _i64, _i, _i64]),
     "logos_attention_fwd_strided": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _PP]),
+    "logos_attention_bwd16_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "logos_attention_bwd16": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_attention_bwd_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "logos_attention_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP]),
     "logos_mha_workspace_bytes": (_sz, [_i, _i, _i, _i]),
