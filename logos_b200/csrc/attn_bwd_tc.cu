@@ -193,11 +193,21 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             for (int cb = 0; cb < 4; ++cb) tc_ld32(tmem + lane_addr + cS + 32 * cb, s + 32 * cb);
             tc_wait_ld();
             float mx = -INFINITY;
+            // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
+            const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
+            if (full) {
 #pragma unroll
-            for (int j = 0; j < kBT; ++j) {
-                const bool okj = i < S && k0 + j < S && key_allowed(i, k0 + j, causal, shun, a.window, a.stride);
-                s[j] = okj ? s[j] * a.c : -INFINITY;
-                mx = fmaxf(mx, s[j]);
+                for (int j = 0; j < kBT; ++j) {
+                    s[j] *= a.c;
+                    mx = fmaxf(mx, s[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kBT; ++j) {
+                    const bool okj = i < S && k0 + j < S && key_allowed(i, k0 + j, causal, shun, a.window, a.stride);
+                    s[j] = okj ? s[j] * a.c : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
             }
             // lazy running maximum: a warp-wide decision, because the correction is a warp-collective access
             const bool want = (mx > m_run + kLazy) || (m_run == -INFINITY && mx > -INFINITY);
@@ -297,7 +307,12 @@ constexpr int kKeysOffStat = 6 * kBTile;                       // [2][2][128] fl
 constexpr int kKeysOffBar = kKeysOffStat + 2 * 2 * kBT * 4;
 constexpr int kKeysSmem = kKeysOffBar + KB_NUM * 8 + 64 + 1024;
 
-__global__ void __launch_bounds__(kBwdTcThreads, 1)
+// Eight weight warps here: a key row is shared by two threads (warps w and w + 4 own the same tensor-memory lanes),
+// each taking 64 of the tile's 128 queries -- no exchange is needed, the statistics come from the rows kernel.
+constexpr int kKeysThreads = 288;
+constexpr int kKeysCtrl = 8;
+
+__global__ void __launch_bounds__(kKeysThreads, 1)
 bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
     extern __shared__ unsigned char smem_raw[];
@@ -319,18 +334,18 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     int qt_end = (S + kBT - 1) / kBT;
     if (a.shunyam && a.stride <= 0) qt_end = min(qt_end, (k_last + a.window) / kBT + 1);
 
-    if (warp == 4 && lane == 0) {
+    if (warp == kKeysCtrl && lane == 0) {
         mbar_init(bar(KB_KV), 1);
         for (int s = 0; s < 2; ++s) { mbar_init(bar(KB_QGFULL0 + s), 1); mbar_init(bar(KB_QGEMPTY0 + s), 1); }
         mbar_init(bar(KB_SFULL), 1);
-        mbar_init(bar(KB_SEMPTY), 128);
-        mbar_init(bar(KB_WFULL), 128);
+        mbar_init(bar(KB_SEMPTY), 256);
+        mbar_init(bar(KB_WFULL), 256);
         mbar_init(bar(KB_ACC), 1);
-        mbar_init(bar(KB_STAT), 128);
+        mbar_init(bar(KB_STAT), 256);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == kKeysCtrl) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -346,7 +361,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         return qt;
     };
 
-    if (warp == 4) {
+    if (warp == kKeysCtrl) {
         if (lane == 0) {
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
@@ -402,48 +417,58 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
         }
     } else {
-        // ================= one thread per key =================
-        const int r = warp * 32 + lane, j = k0 + r;
-        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        // ================= two threads per key: (lane quarter, half of the query columns) =================
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane, j = k0 + r;
+        const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
+        const uint32_t col_s = (uint32_t)(64 * half), col_w = (uint32_t)(32 * half);
         const bool causal = a.causal != 0, shun = a.shunyam != 0;
         bool ok = true;
         int n = 0;
         for (int qt = next_visible(qt_begin); ok && qt < qt_end; qt = next_visible(qt + 1), ++n) {
-            const int q0 = qt * kBT;
-            // the query tile's statistics: thread r fetches row r's into shared memory, all 128 threads then read all
-            // of them (broadcast reads).  Two buffers in turn: a thread can only write tile n + 2's after every
-            // thread has arrived for tile n + 1, i.e. has finished reading tile n's.  The hand-over is an mbarrier
-            // with a bounded wait, so a CTA that is winding down cannot get stuck in it.
+            const int q0 = qt * kBT, qh = q0 + 64 * half;
+            // the query tile's statistics go through shared memory: the thread pair of row r fetches query r's
+            // log-sum-exp and delta, all threads then read all of them (broadcast reads).  Two buffers in turn: a
+            // thread can only write tile n + 2's after every thread has arrived for tile n + 1, i.e. has finished
+            // reading tile n's.  The hand-over is an mbarrier with a bounded wait, so a CTA that is winding down
+            // cannot get stuck in it.
             float* st_lse = stat + (n & 1) * 2 * kBT;
             float* st_dlt = st_lse + kBT;
-            st_lse[r] = (q0 + r < S) ? a.lse[(size_t)bh * S + q0 + r] : INFINITY;
-            st_dlt[r] = (q0 + r < S) ? a.delta[(size_t)bh * S + q0 + r] : 0.0f;
+            if (half == 0) st_lse[r] = (q0 + r < S) ? a.lse[(size_t)bh * S + q0 + r] : INFINITY;
+            else           st_dlt[r] = (q0 + r < S) ? a.delta[(size_t)bh * S + q0 + r] : 0.0f;
             mbar_arrive(bar(KB_STAT));
             if (!mbar_wait(bar(KB_STAT), n & 1, abort_flag)) { ok = false; break; }
             if (!mbar_wait(bar(KB_SFULL), n & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float s[kBT];
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) tc_ld32(tmem + lane_addr + cS + 32 * cb, s + 32 * cb);
+            float s[64];
+            tc_ld32(tmem + lane_addr + cS + col_s, s);
+            tc_ld32(tmem + lane_addr + cS + col_s + 32, s + 32);
             tc_wait_ld();
+            // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
+            const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
+            if (full) {
 #pragma unroll
-            for (int q = 0; q < kBT; ++q) {
-                const bool okq = j < S && q0 + q < S && key_allowed(q0 + q, j, causal, shun, a.window, a.stride);
-                s[q] = okq ? ex2(s[q] * a.c - st_lse[q]) : 0.0f;           // p_ij; lse = +inf for a dead row gives 0
+                for (int q = 0; q < 64; ++q) s[q] = ex2(s[q] * a.c - st_lse[64 * half + q]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 64; ++q) {
+                    const bool okq = j < S && qh + q < S && key_allowed(qh + q, j, causal, shun, a.window, a.stride);
+                    s[q] = okq ? ex2(s[q] * a.c - st_lse[64 * half + q]) : 0.0f;   // p_ij; lse = +inf for a dead row gives 0
+                }
             }
             if (n > 0) {
                 if (!mbar_wait(bar(KB_ACC), (n - 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
             }
 #pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
+            for (int cb = 0; cb < 2; ++cb) {
                 float dp[32];
-                tc_ld32(tmem + lane_addr + cP + 32 * cb, dp);
+                tc_ld32(tmem + lane_addr + cP + col_s + 32 * cb, dp);
                 tc_wait_ld();
 #pragma unroll
-                for (int q = 0; q < 32; ++q) dp[q] = s[32 * cb + q] * (dp[q] - st_dlt[32 * cb + q]) * a.scale;   // ds_ij
-                st_packed32(tmem + lane_addr + cW1 + 16 * cb, s + 32 * cb, f16);
-                st_packed32(tmem + lane_addr + cW2 + 16 * cb, dp, f16);
+                for (int q = 0; q < 32; ++q) dp[q] = s[32 * cb + q] * (dp[q] - st_dlt[64 * half + 32 * cb + q]) * a.scale;   // ds_ij
+                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, s + 32 * cb, f16);
+                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, dp, f16);
             }
             tc_wait_st();
             tc_fence_before();
@@ -453,27 +478,25 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (ok && n > 0) ok = mbar_wait(bar(KB_ACC), (n - 1) & 1, abort_flag);
         if (ok) {
             tc_fence_after();
+            // half 0 writes the key's dV row, half 1 its dK row
+            float* dst = (half == 0 ? a.dVx : a.dK) + ((size_t)bh * S + j) * kBD;
+            const bool acc_out = half == 1 && a.accumulate_dk;
 #pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                float* dst = (which == 0 ? a.dVx : a.dK) + ((size_t)bh * S + j) * kBD;
-                const bool acc_out = which == 1 && a.accumulate_dk;
+            for (int hc = 0; hc < 2; ++hc) {
+                float v[32];
 #pragma unroll
-                for (int hc = 0; hc < 2; ++hc) {
-                    float v[32];
+                for (int q = 0; q < 32; ++q) v[q] = 0.0f;
+                if (n > 0) {
+                    tc_ld32(tmem + lane_addr + (half == 0 ? cV : cK) + 32 * hc, v);
+                    tc_wait_ld();
+                }
+                if (j < S) {
 #pragma unroll
-                    for (int q = 0; q < 32; ++q) v[q] = 0.0f;
-                    if (n > 0) {
-                        tc_ld32(tmem + lane_addr + (which == 0 ? cV : cK) + 32 * hc, v);
-                        tc_wait_ld();
-                    }
-                    if (j < S) {
-#pragma unroll
-                        for (int q = 0; q < 32; q += 4) {
-                            float4* p4 = reinterpret_cast<float4*>(dst + 32 * hc + q);
-                            float4 o4 = make_float4(v[q] * a.w, v[q + 1] * a.w, v[q + 2] * a.w, v[q + 3] * a.w);
-                            if (acc_out) { const float4 old = *p4; o4.x += old.x; o4.y += old.y; o4.z += old.z; o4.w += old.w; }
-                            *p4 = o4;
-                        }
+                    for (int q = 0; q < 32; q += 4) {
+                        float4* p4 = reinterpret_cast<float4*>(dst + 32 * hc + q);
+                        float4 o4 = make_float4(v[q] * a.w, v[q + 1] * a.w, v[q + 2] * a.w, v[q + 3] * a.w);
+                        if (acc_out) { const float4 old = *p4; o4.x += old.x; o4.y += old.y; o4.z += old.z; o4.w += old.w; }
+                        *p4 = o4;
                     }
                 }
             }
@@ -484,7 +507,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
-    if (warp == 4) {
+    if (warp == kKeysCtrl) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -587,7 +610,7 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
             return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
         bwd_tc_rows_kernel<<<grid, kBwdTcThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_rows_kernel");
-        bwd_tc_keys_kernel<<<grid, kBwdTcThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        bwd_tc_keys_kernel<<<grid, kKeysThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_keys_kernel");
         return LOGOS_OK;
     };
