@@ -29,7 +29,6 @@ using namespace tc;
 constexpr int kBT = 128;                     // rows of a tile (queries or keys)
 constexpr int kBD = 64;                      // head dimension
 constexpr int kBTile = kBT * kBD * 2;        // 16 KiB
-constexpr int kBwdTcThreads = 160;           // four softmax warps + one control warp
 constexpr float kLazy = 4.0f;                // the running maximum moves when it would grow by more than 2^4
 
 struct BwdTcArgs {
@@ -73,20 +72,28 @@ __device__ __forceinline__ void st_packed32(uint32_t taddr, const float* v, bool
     }
 }
 
-enum { RB_QG = 0, RB_KVFULL0, RB_KVFULL1, RB_KVEMPTY0, RB_KVEMPTY1, RB_SFULL, RB_SEMPTY, RB_WFULL, RB_ACC, RB_NUM };
-constexpr int kRowsSmem = 6 * kBTile + RB_NUM * 8 + 64 + 1024;
+enum { RB_QG = 0, RB_KVFULL0, RB_KVFULL1, RB_KVEMPTY0, RB_KVEMPTY1, RB_SFULL, RB_SEMPTY, RB_WFULL, RB_ACC, RB_XCH, RB_NUM };
+constexpr int kRowsOffXch = 6 * kBTile;                       // [2][2][128] floats: the half rows' maxima (and, at the end, sums)
+constexpr int kRowsOffBar = kRowsOffXch + 2 * 2 * kBT * 4;
+constexpr int kRowsSmem = kRowsOffBar + RB_NUM * 8 + 64 + 1024;
+// Eight weight warps: a query row is shared by two threads (warps w and w + 4 own the same tensor-memory lanes), each
+// taking 64 of the tile's 128 keys.  They agree on the row's maximum through shared memory once per tile and keep
+// partial sums of their own until the end.
+constexpr int kRowsThreads = 288;
+constexpr int kRowsCtrl = 8;
 
-__global__ void __launch_bounds__(kBwdTcThreads, 1)
+__global__ void __launch_bounds__(kRowsThreads, 1)
 bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     const uint32_t sQ = sbase, sG = sbase + kBTile, sK = sbase + 2 * kBTile, sV = sbase + 4 * kBTile;
-    const uint32_t bar0 = sbase + 6 * kBTile;
+    float* xch = reinterpret_cast<float*>(smem + kRowsOffXch);
+    const uint32_t bar0 = sbase + kRowsOffBar;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 6 * kBTile + RB_NUM * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 6 * kBTile + RB_NUM * 8 + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kRowsOffBar + RB_NUM * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kRowsOffBar + RB_NUM * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = a.S, bh = blockIdx.y;
@@ -94,17 +101,18 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const int kt_end = (S + kBT - 1) / kBT;
     const bool f16 = a.f16 != 0;
 
-    if (warp == 4 && lane == 0) {
+    if (warp == kRowsCtrl && lane == 0) {
         mbar_init(bar(RB_QG), 1);
         for (int s = 0; s < 2; ++s) { mbar_init(bar(RB_KVFULL0 + s), 1); mbar_init(bar(RB_KVEMPTY0 + s), 1); }
         mbar_init(bar(RB_SFULL), 1);
-        mbar_init(bar(RB_SEMPTY), 128);
-        mbar_init(bar(RB_WFULL), 128);
+        mbar_init(bar(RB_SEMPTY), 256);
+        mbar_init(bar(RB_WFULL), 256);
         mbar_init(bar(RB_ACC), 1);
+        mbar_init(bar(RB_XCH), 256);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == kRowsCtrl) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -120,7 +128,7 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         return kt;
     };
 
-    if (warp == 4) {
+    if (warp == kRowsCtrl) {
         if (lane == 0) {
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
@@ -177,39 +185,59 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
         }
     } else {
-        // ================= one thread per query row =================
-        const int r = warp * 32 + lane, i = q0 + r;
-        const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
+        // ================= two threads per query row: (lane quarter, half of the key columns) =================
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane, i = q0 + r;
+        const uint32_t lane_addr = ((uint32_t)(quarter * 32)) << 16;
+        const uint32_t col_s = (uint32_t)(64 * half), col_w = (uint32_t)(32 * half);
         const bool causal = a.causal != 0, shun = a.shunyam != 0;
-        float m_run = -INFINITY, l_run = 0.0f, d_run = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f, d_run = 0.0f;      // l, d: this thread's half of the row's sums
         bool ok = true;
-        int n = 0;
+        int n = 0;                // visible tiles done
+        int nx = 0;               // exchanges done (one per tile, one more at the end)
+        // both halves of a row publish a value and read each other's; two buffers in turn (a thread can only write
+        // exchange x + 2 after everyone has arrived for exchange x + 1, i.e. has read exchange x); bounded wait
+        auto exchange = [&](float mine, float& other) {
+            float* buf = xch + (nx & 1) * 2 * kBT;
+            buf[half * kBT + r] = mine;
+            mbar_arrive(bar(RB_XCH));
+            const bool fine = mbar_wait(bar(RB_XCH), nx & 1, abort_flag);
+            other = buf[(half ^ 1) * kBT + r];
+            ++nx;
+            return fine;
+        };
         for (int kt = next_visible(0); ok && kt < kt_end; kt = next_visible(kt + 1), ++n) {
-            const int k0 = kt * kBT;
+            const int k0 = kt * kBT, kh = k0 + 64 * half;
             if (!mbar_wait(bar(RB_SFULL), n & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float s[kBT];
-#pragma unroll
-            for (int cb = 0; cb < 4; ++cb) tc_ld32(tmem + lane_addr + cS + 32 * cb, s + 32 * cb);
+            float s[64];
+            tc_ld32(tmem + lane_addr + cS + col_s, s);
+            tc_ld32(tmem + lane_addr + cS + col_s + 32, s + 32);
             tc_wait_ld();
             float mx = -INFINITY;
             // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
             const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
             if (full) {
 #pragma unroll
-                for (int j = 0; j < kBT; ++j) {
+                for (int j = 0; j < 64; ++j) {
                     s[j] *= a.c;
                     mx = fmaxf(mx, s[j]);
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < kBT; ++j) {
-                    const bool okj = i < S && k0 + j < S && key_allowed(i, k0 + j, causal, shun, a.window, a.stride);
+                for (int j = 0; j < 64; ++j) {
+                    const bool okj = i < S && kh + j < S && key_allowed(i, kh + j, causal, shun, a.window, a.stride);
                     s[j] = okj ? s[j] * a.c : -INFINITY;
                     mx = fmaxf(mx, s[j]);
                 }
             }
-            // lazy running maximum: a warp-wide decision, because the correction is a warp-collective access
+            {
+                float other;
+                if (!exchange(mx, other)) { ok = false; break; }
+                mx = fmaxf(mx, other);           // the row's maximum over the whole tile: the same in both threads
+            }
+            // lazy running maximum: a warp-wide decision, because the correction is a warp-collective access; the two
+            // warps of a row see the same maxima and decide alike
             const bool want = (mx > m_run + kLazy) || (m_run == -INFINITY && mx > -INFINITY);
             const bool any = __any_sync(0xffffffffu, want && n > 0 && m_run > -INFINITY);
             float m_new = want ? mx : m_run;
@@ -221,13 +249,14 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             if (any) {
                 const float f = (m_run == -INFINITY) ? 0.0f : ex2(m_run - m_new);
 #pragma unroll
-                for (int hc = 0; hc < 4; ++hc) {       // A and B are neighbours: 128 columns from cA
+                for (int hc = 0; hc < 2; ++hc) {       // half 0 corrects A, half 1 corrects B (64 columns each)
                     float o[32];
-                    tc_ld32(tmem + lane_addr + cA + 32 * hc, o);
+                    const uint32_t col = (half == 0 ? cA : cB) + 32u * (uint32_t)hc;
+                    tc_ld32(tmem + lane_addr + col, o);
                     tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] *= f;
-                    tc_st32(tmem + lane_addr + cA + 32 * hc, o);
+                    tc_st32(tmem + lane_addr + col, o);
                 }
                 l_run *= f;
                 d_run *= f;
@@ -237,9 +266,9 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
             float lsum = 0.0f, dsum = 0.0f;
 #pragma unroll
-            for (int cb = 0; cb < 4; ++cb) {
+            for (int cb = 0; cb < 2; ++cb) {
                 float dp[32], w1[32];
-                tc_ld32(tmem + lane_addr + cP + 32 * cb, dp);
+                tc_ld32(tmem + lane_addr + cP + col_s + 32 * cb, dp);
                 tc_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -249,8 +278,8 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                     w1[j] = e * dp[j];
                     dsum += w1[j];
                 }
-                st_packed32(tmem + lane_addr + cW1 + 16 * cb, w1, f16);
-                st_packed32(tmem + lane_addr + cW2 + 16 * cb, s + 32 * cb, f16);
+                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, w1, f16);
+                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, s + 32 * cb, f16);
             }
             l_run += lsum;
             d_run += dsum;
@@ -259,34 +288,42 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             mbar_arrive(bar(RB_SEMPTY));      // S and dP have been read
             mbar_arrive(bar(RB_WFULL));       // the weights are in place
         }
+        // the row's sums: this half's plus the other's
+        if (ok) {
+            float other;
+            ok = exchange(l_run, other);
+            l_run += other;
+            if (ok) {
+                ok = exchange(d_run, other);
+                d_run += other;
+            }
+        }
         if (ok && n > 0) ok = mbar_wait(bar(RB_ACC), (n - 1) & 1, abort_flag);
         if (ok) {
             tc_fence_after();
             const bool live = n > 0 && l_run > 1e-9f;     // a row that saw nothing was written as zeros by the forward
             const float inv = live ? 1.0f / l_run : 0.0f;
             const float dlt = d_run * inv;
-            if (i < S) {
+            if (i < S && half == 0) {
                 a.lse[(size_t)bh * S + i] = live ? m_run + log2f(l_run) : INFINITY;
                 a.delta[(size_t)bh * S + i] = dlt;
             }
-            float* dst = a.dQx + ((size_t)bh * S + i) * kBD;
+            // each half writes 32 of the row's 64 channels
+            float* dst = a.dQx + ((size_t)bh * S + i) * kBD + 32 * half;
+            float av[32], bv[32];
+            if (n > 0) {
+                tc_ld32(tmem + lane_addr + cA + col_w, av);
+                tc_ld32(tmem + lane_addr + cB + col_w, bv);
+                tc_wait_ld();
+            }
+            if (i < S) {
+                const float k1 = a.scale * inv * a.w;
 #pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-                float av[32], bv[32];
-                if (n > 0) {
-                    tc_ld32(tmem + lane_addr + cA + 32 * hc, av);
-                    tc_ld32(tmem + lane_addr + cB + 32 * hc, bv);
-                    tc_wait_ld();
-                }
-                if (i < S) {
-                    const float k1 = a.scale * inv * a.w;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (live) o4 = make_float4((av[j] - dlt * bv[j]) * k1, (av[j + 1] - dlt * bv[j + 1]) * k1,
-                                                   (av[j + 2] - dlt * bv[j + 2]) * k1, (av[j + 3] - dlt * bv[j + 3]) * k1);
-                        *reinterpret_cast<float4*>(dst + 32 * hc + j) = o4;
-                    }
+                for (int j = 0; j < 32; j += 4) {
+                    float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (live) o4 = make_float4((av[j] - dlt * bv[j]) * k1, (av[j + 1] - dlt * bv[j + 1]) * k1,
+                                               (av[j + 2] - dlt * bv[j + 2]) * k1, (av[j + 3] - dlt * bv[j + 3]) * k1);
+                    *reinterpret_cast<float4*>(dst + j) = o4;
                 }
             }
             tc_fence_before();
@@ -296,7 +333,7 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     tc_fence_before();
     __syncthreads();
     if (*abort_flag && tid == 0) atomicExch(a.status, (*abort_flag & ~0xffff) | ((*abort_flag - (int)(bar0 & 0xffffu)) & 0xffff));
-    if (warp == 4) {
+    if (warp == kRowsCtrl) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -608,7 +645,7 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
         CUtensorMap mq, mv;
         if (!make_map_bwd(&mq, Qx, BH, S, f16) || !make_map_bwd(&mv, Vx, BH, S, f16))
             return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
-        bwd_tc_rows_kernel<<<grid, kBwdTcThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        bwd_tc_rows_kernel<<<grid, kRowsThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_rows_kernel");
         bwd_tc_keys_kernel<<<grid, kKeysThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_keys_kernel");
