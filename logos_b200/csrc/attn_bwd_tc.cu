@@ -224,9 +224,15 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                     mx = fmaxf(mx, s[j]);
                 }
             } else {
+                // allowed(i, j) as in key_allowed() (cuda/VedicGEMM.cu:987-996), with the landmark rule's remainder
+                // carried along the row instead of divided out per key
+                int rem = (shun && a.stride > 0) ? kh % a.stride : 1;
 #pragma unroll
                 for (int j = 0; j < 64; ++j) {
-                    const bool okj = i < S && kh + j < S && key_allowed(i, kh + j, causal, shun, a.window, a.stride);
+                    const int key = kh + j;
+                    bool okj = i < S && key < S && (!causal || key <= i);
+                    if (shun) okj = okj && ((key >= i - a.window && key <= i) || (a.stride > 0 && rem == 0));
+                    rem = (rem + 1 == a.stride) ? 0 : rem + 1;
                     s[j] = okj ? s[j] * a.c : -INFINITY;
                     mx = fmaxf(mx, s[j]);
                 }
@@ -487,9 +493,14 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 #pragma unroll
                 for (int q = 0; q < 64; ++q) s[q] = ex2(s[q] * a.c - st_lse[64 * half + q]);
             } else {
+                // allowed(i, j) as in key_allowed() (cuda/VedicGEMM.cu:987-996); whether this thread's key is a landmark
+                // does not depend on the query
+                const bool landmark = shun && a.stride > 0 && (j % a.stride) == 0;
 #pragma unroll
                 for (int q = 0; q < 64; ++q) {
-                    const bool okq = j < S && qh + q < S && key_allowed(qh + q, j, causal, shun, a.window, a.stride);
+                    const int qi = qh + q;
+                    bool okq = j < S && qi < S && (!causal || j <= qi);
+                    if (shun) okq = okq && ((j >= qi - a.window && j <= qi) || landmark);
                     s[q] = okq ? ex2(s[q] * a.c - st_lse[64 * half + q]) : 0.0f;   // p_ij; lse = +inf for a dead row gives 0
                 }
             }
