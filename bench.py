@@ -438,7 +438,7 @@ def measure_projection(eng, dev, batch, steps, warmup) -> dict:
             "max_abs_err_vs_fp64_product": float((got - want).abs().max())}
 
 
-def measure_backward(eng, dev, steps, warmup) -> dict:
+def measure_backward(eng, dev, steps, warmup, Bq=4) -> dict:
     """Attention backward at the prefill configuration's shape (B 4, H 16, S 4096, DH 64, fp32, causal with the
     Navier-Stokes prologue): dQ, dK, dV for a given dO.  Flops counted as the five products of the chain over the
     causal half (2.5 x the forward's); checked against the fp64 backward oracle on one short head first."""
@@ -452,7 +452,7 @@ def measure_backward(eng, dev, steps, warmup) -> dict:
     got = eng.attention_bwd(*small, p)
     want = O.attention_bwd(*(t.cpu().numpy() for t in small), O.attn_params(0.125, True, 0, 0, ETA, NU, 1.0, 1))
     err = max(float(np.abs(a.cpu().numpy() - b).max()) for a, b in zip(got, want))
-    Bq, S = 4, 4096
+    S = 4096
     Q, K, V, dO = (torch.randn((Bq, H, S, DH), device=dev, generator=g) for _ in range(4))
     for _ in range(warmup):
         eng.attention_bwd(Q, K, V, dO, p)
@@ -468,6 +468,26 @@ def measure_backward(eng, dev, steps, warmup) -> dict:
            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (causal-halved, 5 products)", "bound": "fp32 FMA pipe",
            "max_abs_err_vs_oracle": err,
            "note": "exact fp32 arithmetic on the FMA pipe (no tensor cores): a first path for a row outside the forward hot path"}
+    # the same gradients on the tensor cores (BF16 operands), checked against the fp32 kernels on the same operands
+    Q16, K16, V16, dO16 = (t.bfloat16() for t in (Q, K, V, dO))
+    ref32 = eng.attention_bwd(Q16.float(), K16.float(), V16.float(), dO16.float(), p)
+    got16 = eng.attention_bwd16(Q16, K16, V16, dO16, p)
+    eng.synchronize()
+    err16 = max(float((a - b).abs().max() / b.abs().max().clamp_min(1.0)) for a, b in zip(got16, ref32))
+    del ref32, got16
+    for _ in range(warmup):
+        eng.attention_bwd16(Q16, K16, V16, dO16, p)
+    ev[0].record()
+    for _ in range(steps):
+        eng.attention_bwd16(Q16, K16, V16, dO16, p)
+    ev[1].record()
+    eng.synchronize()
+    ms16 = ev[0].elapsed_time(ev[1]) / steps
+    peaks = measured_peaks()
+    out["tensor_cores_bf16"] = {"workload": f"attention_bwd16_b{Bq}_h{H}_s{S}_dh{DH}_bf16", "ms_per_step": ms16,
+                                "value": flops / (ms16 * 1e-3) / 1e12, "unit": "TFLOP/s (causal-halved, 5 products)",
+                                "frac_of_bf16_peak": flops / (ms16 * 1e-3) / 1e12 / peaks["tensor"],
+                                "max_err_vs_fp32_kernels_rel_to_largest_gradient": err16}
     # the reference's own chain for one head at a length its seq x seq buffers allow
     path = os.path.join(os.path.dirname(os.path.abspath(O.__file__)), "_ref", "liblogos_refbwd.so")
     if os.path.exists(path):
@@ -624,7 +644,7 @@ def run_ours(args) -> None:
         return
 
     if args.workload == "bwd":
-        r = measure_backward(eng, dev, max(3, args.steps // 4), 3)
+        r = measure_backward(eng, dev, max(3, args.steps // 4), 3, Bq=args.batch if args.batch != 64 else 4)
         print(json.dumps({"metric": r["workload"], "value": r["value"], "unit": r["unit"], "n_gpus": 1, "higher_is_better": True,
                           "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": r["workload"]},
                           "detail": r}))
