@@ -54,7 +54,15 @@ __device__ __forceinline__ bool tile_visible(const BwdTcArgs& a, int q0, int q_l
     return in_win || has_land;
 }
 
-__device__ __forceinline__ uint32_t pack2(float x, float y, bool f16) { return f32_to_16(x, f16) | (f32_to_16(y, f16) << 16); }
+// two values as one word of the operand type; FP16 saturates at +-65504 instead of turning into infinity (a weight
+// e dP or dS beyond that is outside what FP16 operands can carry: BF16 has the range)
+__device__ __forceinline__ uint32_t pack2(float x, float y, bool f16) {
+    if (f16) {
+        x = fminf(fmaxf(x, -65504.0f), 65504.0f);
+        y = fminf(fmaxf(y, -65504.0f), 65504.0f);
+    }
+    return f32_to_16(x, f16) | (f32_to_16(y, f16) << 16);
+}
 
 // MN-major B operand: a [128 rows (the k dimension)][64] tile as TMA wrote it, 16 rows (2048 bytes) per k step
 __device__ __forceinline__ uint64_t desc_rows(uint32_t tile, int kk) { return smem_desc(tile + (uint32_t)kk * 2048u); }
