@@ -175,7 +175,10 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             while (ok && kt < kt_end) {
                 const int st = n & 1;
                 const int kt_next = next_visible(kt + 1);
-                if (!mbar_wait(bar(RB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                // the next tile's scores run while the threads work on this one (they free S and dP as soon as
+                // they hold them in registers)
+                if (kt_next < kt_end) issue_scores(n + 1);
+                if (!ok || !mbar_wait(bar(RB_WFULL), n & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBT / 16; ++kk) {
@@ -186,8 +189,7 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                 }
                 tc_commit(bar(RB_ACC));
                 tc_commit(bar(RB_KVEMPTY0 + st));
-                if (kt_next < kt_end) issue_scores(n + 1);
-                if (ok) load_next();
+                load_next();
                 kt = kt_next;
                 ++n;
             }
@@ -218,10 +220,14 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             const int k0 = kt * kBT, kh = k0 + 64 * half;
             if (!mbar_wait(bar(RB_SFULL), n & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float s[64];
+            float s[64], dp[64];
             tc_ld32(tmem + lane_addr + cS + col_s, s);
             tc_ld32(tmem + lane_addr + cS + col_s + 32, s + 32);
+            tc_ld32(tmem + lane_addr + cP + col_s, dp);
+            tc_ld32(tmem + lane_addr + cP + col_s + 32, dp + 32);
             tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(RB_SEMPTY));      // S and dP are in registers: the next tile's scores may overwrite them
             float mx = -INFINITY;
             // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
             const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
@@ -281,25 +287,21 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             float lsum = 0.0f, dsum = 0.0f;
 #pragma unroll
             for (int cb = 0; cb < 2; ++cb) {
-                float dp[32], w1[32];
-                tc_ld32(tmem + lane_addr + cP + col_s + 32 * cb, dp);
-                tc_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const float e = ex2(s[32 * cb + j] + neg_m);      // -inf gives 0
                     s[32 * cb + j] = e;
                     lsum += e;
-                    w1[j] = e * dp[j];
-                    dsum += w1[j];
+                    dp[32 * cb + j] *= e;                             // e dP
+                    dsum += dp[32 * cb + j];
                 }
-                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, w1, f16);
+                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, dp + 32 * cb, f16);
                 st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, s + 32 * cb, f16);
             }
             l_run += lsum;
             d_run += dsum;
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(RB_SEMPTY));      // S and dP have been read
             mbar_arrive(bar(RB_WFULL));       // the weights are in place
         }
         // the row's sums: this half's plus the other's
@@ -451,7 +453,9 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             while (ok && qt < qt_end) {
                 const int st = n & 1;
                 const int qt_next = next_visible(qt + 1);
-                if (!mbar_wait(bar(KB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                // the next tile's scores run while the threads work on this one
+                if (qt_next < qt_end) issue_scores(n + 1);
+                if (!ok || !mbar_wait(bar(KB_WFULL), n & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBT / 16; ++kk) {
@@ -461,8 +465,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                 }
                 tc_commit(bar(KB_ACC));
                 tc_commit(bar(KB_QGEMPTY0 + st));
-                if (qt_next < qt_end) issue_scores(n + 1);
-                if (ok) load_next();
+                load_next();
                 qt = qt_next;
                 ++n;
             }
@@ -491,10 +494,14 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             if (!mbar_wait(bar(KB_STAT), n & 1, abort_flag)) { ok = false; break; }
             if (!mbar_wait(bar(KB_SFULL), n & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            float s[64];
+            float s[64], dp[64];
             tc_ld32(tmem + lane_addr + cS + col_s, s);
             tc_ld32(tmem + lane_addr + cS + col_s + 32, s + 32);
+            tc_ld32(tmem + lane_addr + cP + col_s, dp);
+            tc_ld32(tmem + lane_addr + cP + col_s + 32, dp + 32);
             tc_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(KB_SEMPTY));      // S^T and dP^T are in registers: the next tile's scores may overwrite them
             // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
             const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
             if (full) {
@@ -518,17 +525,14 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
 #pragma unroll
             for (int cb = 0; cb < 2; ++cb) {
-                float dp[32];
-                tc_ld32(tmem + lane_addr + cP + col_s + 32 * cb, dp);
-                tc_wait_ld();
 #pragma unroll
-                for (int q = 0; q < 32; ++q) dp[q] = s[32 * cb + q] * (dp[q] - st_dlt[64 * half + 32 * cb + q]) * a.scale;   // ds_ij
+                for (int q = 0; q < 32; ++q)
+                    dp[32 * cb + q] = s[32 * cb + q] * (dp[32 * cb + q] - st_dlt[64 * half + 32 * cb + q]) * a.scale;   // ds_ij
                 st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, s + 32 * cb, f16);
-                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, dp, f16);
+                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, dp + 32 * cb, f16);
             }
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(KB_SEMPTY));
             mbar_arrive(bar(KB_WFULL));
         }
         if (ok && n > 0) ok = mbar_wait(bar(KB_ACC), (n - 1) & 1, abort_flag);
