@@ -29,6 +29,9 @@ using namespace tc;
 constexpr int kBT = 128;                     // rows of a tile (queries or keys)
 constexpr int kBD = 64;                      // head dimension
 constexpr int kBTile = kBT * kBD * 2;        // 16 KiB
+// registers per thread after the warpgroups have traded them (the kernels start with 65536 / 384 = 168):
+// 256 weight threads x 224 + 128 control-group threads x 56 = 64512
+constexpr int kRegsWeight = 224, kRegsCtrl = 56;
 constexpr float kLazy = 4.0f;                // the running maximum moves when it would grow by more than 2^4
 
 struct BwdTcArgs {
@@ -87,7 +90,7 @@ constexpr int kRowsSmem = kRowsOffBar + RB_NUM * 8 + 64 + 1024;
 // Eight weight warps: a query row is shared by two threads (warps w and w + 4 own the same tensor-memory lanes), each
 // taking 64 of the tile's 128 keys.  They agree on the row's maximum through shared memory once per tile and keep
 // partial sums of their own until the end.
-constexpr int kRowsThreads = 288;
+constexpr int kRowsThreads = 384;      // three warpgroups: two of weight warps, one that holds the control warp
 constexpr int kRowsCtrl = 8;
 
 __global__ void __launch_bounds__(kRowsThreads, 1)
@@ -136,8 +139,11 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         return kt;
     };
 
-    if (warp == kRowsCtrl) {
-        if (lane == 0) {
+    // registers move from the control warpgroup (one busy warp, three idle) to the weight warpgroups, which hold a
+    // tile's scores and their gradients in registers
+    if (warp >= kRowsCtrl) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsCtrl));
+        if (warp == kRowsCtrl && lane == 0) {
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
             mbar_expect_tx(bar(RB_QG), 2 * kBTile);
@@ -195,6 +201,7 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsWeight));
         // ================= two threads per query row: (lane quarter, half of the key columns) =================
         const int quarter = warp & 3, half = warp >> 2;
         const int r = quarter * 32 + lane, i = q0 + r;
@@ -362,7 +369,7 @@ constexpr int kKeysSmem = kKeysOffBar + KB_NUM * 8 + 64 + 1024;
 
 // Eight weight warps here: a key row is shared by two threads (warps w and w + 4 own the same tensor-memory lanes),
 // each taking 64 of the tile's 128 queries -- no exchange is needed, the statistics come from the rows kernel.
-constexpr int kKeysThreads = 288;
+constexpr int kKeysThreads = 384;      // as in the rows kernel
 constexpr int kKeysCtrl = 8;
 
 __global__ void __launch_bounds__(kKeysThreads, 1)
@@ -414,8 +421,9 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         return qt;
     };
 
-    if (warp == kKeysCtrl) {
-        if (lane == 0) {
+    if (warp >= kKeysCtrl) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsCtrl));
+        if (warp == kKeysCtrl && lane == 0) {
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
             mbar_expect_tx(bar(KB_KV), 2 * kBTile);
@@ -471,6 +479,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsWeight));
         // ================= two threads per key: (lane quarter, half of the query columns) =================
         const int quarter = warp & 3, half = warp >> 2;
         const int r = quarter * 32 + lane, j = k0 + r;
