@@ -70,3 +70,34 @@ def test_shim_exports_the_reference_symbol():
     build()
     out = subprocess.run(["nm", "-D", "--defined-only", SHIM], capture_output=True, text=True, check=True).stdout
     assert "_Z24cuda_flash_attention_fwdPKfS0_S0_PfS1_iifbbii" in out
+
+
+def test_weight_shadow_index_maps():
+    """The K-major shadows that logos_mha_forward takes, as include/logos_attn.h states them:
+    Wt_qkv[(which H + h) 64 + c][k] = W_which[h][k][c]; for the CPU classes Wt_o is block diagonal with
+    Wt_o[h 64 + j][h 64 + c] = W_O[h][c][j]; Wt_proj[n][k] = W_proj[k][n]."""
+    import torch
+    from logos_b200.attention import MultiHeadAttention
+    H, d, dk = 3, 192, 64
+    g = torch.Generator().manual_seed(0)
+    WQ, WK, WV = (torch.randn((H, d, dk), generator=g) for _ in range(3))
+    WO = torch.randn((H, dk, d), generator=g)
+    Wp = torch.randn((d, d), generator=g)
+    mha = MultiHeadAttention(None, WQ, WK, WV, WO, Wp)
+    Wt_qkv, Wt_o, Wt_proj = mha.shadows(torch.float32)
+    assert Wt_qkv.shape == (3 * H * dk, d) and Wt_o.shape == (d, H * dk) and Wt_proj.shape == (d, d)
+    for which, W in enumerate((WQ, WK, WV)):
+        for h in range(H):
+            assert torch.equal(Wt_qkv[(which * H + h) * dk:(which * H + h + 1) * dk], W[h].t())
+    for h in range(H):
+        assert torch.equal(Wt_o[h * dk:(h + 1) * dk, h * dk:(h + 1) * dk], WO[h][:, :dk].t())
+    off = Wt_o.clone()
+    for h in range(H):
+        off[h * dk:(h + 1) * dk, h * dk:(h + 1) * dk] = 0
+    assert not bool(off.any())
+    assert torch.equal(Wt_proj, Wp.t())
+    # what the shadows compute is the class's forward after the attention: concat = first dk columns of head_out W_O[h]
+    head_out = torch.randn((H, 5, dk), generator=g)
+    concat = torch.cat([(head_out[h] @ WO[h])[:, :dk] for h in range(H)], dim=1)
+    tokens = head_out.permute(1, 0, 2).reshape(5, H * dk)
+    assert torch.allclose(tokens @ Wt_o.t(), concat, atol=1e-5)
