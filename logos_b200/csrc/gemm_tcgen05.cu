@@ -15,7 +15,8 @@
 // cuda/MixedPrecision.cuh:149-161), so both operands are loaded as 128-byte-swizzled K-major tiles
 // and one MMA covers a 128 x 128 block.  One CTA per 128 x 128 output tile, two CTAs per SM (the
 // epilogue of one overlaps the main loop of the other), 192 threads:
-//   warp 0    TMA producer: A and W tiles of 128 rows x 64 k into a three-stage ring;
+//   warp 0    TMA producer: A and W tiles of 128 rows x 64 k into a three-stage ring (six stages and one
+//             CTA per SM when the grid has fewer CTAs than the device has SMs);
 //   warp 1    MMA issuer (one elected lane): four M128 N128 K16 MMAs per stage into 128 TMEM columns;
 //   warps 2-5 epilogue: one thread per output row reads its 128 accumulator columns from TMEM.
 // Every mbarrier wait is bounded; a wait that runs out raises the context's status word.
@@ -30,11 +31,9 @@ using namespace tc;
 
 constexpr int kGN = 128;                 // output columns per CTA
 constexpr int kGK = 64;                  // k per stage (one 128-byte swizzle atom of 16-bit values)
-constexpr int kGStages = 3;
 constexpr int kGTile = kBM * kGK * 2;    // 16 KiB: one operand tile
 constexpr int kGThreads = 192;
-constexpr int kGOffBar = 2 * kGStages * kGTile;
-constexpr int kGSmem = kGOffBar + (2 * kGStages + 1) * 8 + 64 + 1024;
+constexpr int gemm_smem(int stages) { return 2 * stages * kGTile + (2 * stages + 1) * 8 + 64 + 1024; }
 
 struct GemmArgs {
     int M, N, K;
@@ -194,17 +193,22 @@ __device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t
     }
 }
 
-__global__ void __launch_bounds__(kGThreads, 2)
+// STAGES = depth of the operand ring: 3 (96 KiB, two CTAs per SM) when the grid fills the device, 6 (192 KiB) for
+// small problems -- a decode-time GEMM has fewer CTAs than SMs and is a chain of TMA round trips, which a deeper
+// ring shortens.
+template <int STAGES>
+__global__ void __launch_bounds__(kGThreads, STAGES == 3 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const GemmArgs a) {
+    constexpr int kOffBarT = 2 * STAGES * kGTile;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bar0 = sbase + kGOffBar;
+    const uint32_t bar0 = sbase + kOffBarT;
     auto full = [&](int s) { return bar0 + 8u * (uint32_t)s; };
-    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(kGStages + s); };
-    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * kGStages);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kGOffBar + (2 * kGStages + 1) * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kGOffBar + (2 * kGStages + 1) * 8 + 16);
+    auto empty = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
+    const uint32_t acc_full = bar0 + 8u * (uint32_t)(2 * STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + kOffBarT + (2 * STAGES + 1) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBarT + (2 * STAGES + 1) * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * kGN;
@@ -221,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
 
     if (warp == 0 && lane == 0) {
-        for (int s = 0; s < kGStages; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -238,8 +242,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % kGStages;
-                if (kb >= kGStages && !mbar_wait(empty(s), ((kb / kGStages) - 1) & 1, abort_flag)) break;
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
                 mbar_expect_tx(full(s), 2 * kGTile);
                 if (a.a_heads) tma_load_3d(sbase + (2 * s) * kGTile, &mapA, 0, a_row, a_slab + kb, full(s));
                 else           tma_load_3d(sbase + (2 * s) * kGTile, &mapA, kb * kGK, m0, 0, full(s));
@@ -254,8 +258,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const uint32_t idesc = instr_desc(fmt, fmt, 0, kGN);
         bool ok = true;
         for (int kb = 0; ok && kb < n_kb; ++kb) {
-            const int s = kb % kGStages;
-            ok = __all_sync(0xffffffffu, mbar_wait(full(s), (kb / kGStages) & 1, abort_flag)) != 0;
+            const int s = kb % STAGES;
+            ok = __all_sync(0xffffffffu, mbar_wait(full(s), (kb / STAGES) & 1, abort_flag)) != 0;
             if (!ok) break;
             tc_fence_after();
             if (leader) {
@@ -493,9 +497,14 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
         LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_wide_kernel");
         return LOGOS_OK;
     }
-    if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel, kGSmem)) return rc;
     dim3 grid((a.N + kGN - 1) / kGN, m_tiles);
-    gemm_tc_kernel<<<grid, kGThreads, kGSmem, ctx->stream>>>(ma, mw, a);
+    if ((int64_t)grid.x * grid.y <= ctx->sm_count) {       // fewer CTAs than SMs: the deep ring
+        if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel<6>, gemm_smem(6))) return rc;
+        gemm_tc_kernel<6><<<grid, kGThreads, gemm_smem(6), ctx->stream>>>(ma, mw, a);
+    } else {
+        if (int rc = ensure_smem_limit(ctx, gemm_tc_kernel<3>, gemm_smem(3))) return rc;
+        gemm_tc_kernel<3><<<grid, kGThreads, gemm_smem(3), ctx->stream>>>(ma, mw, a);
+    }
     LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel");
     return LOGOS_OK;
 }
