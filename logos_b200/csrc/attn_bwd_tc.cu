@@ -64,7 +64,11 @@ __device__ __forceinline__ uint32_t pack2(float x, float y, bool f16) {
         x = fminf(fmaxf(x, -65504.0f), 65504.0f);
         y = fminf(fmaxf(y, -65504.0f), 65504.0f);
     }
-    return f32_to_16(x, f16) | (f32_to_16(y, f16) << 16);
+    // one packed conversion per pair: two scalar conversions would go through the XU pipe, which the
+    // exponentials already keep busy
+    if (f16) { __half2 h = __floats2half2_rn(x, y); return *reinterpret_cast<uint32_t*>(&h); }
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // MN-major B operand: a [128 rows (the k dimension)][64] tile as TMA wrote it, 16 rows (2048 bytes) per k step
