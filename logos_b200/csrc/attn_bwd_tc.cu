@@ -9,8 +9,13 @@
 //       A += (e dP) K,  B += e K                         (weights written back to tensor memory as 16-bit A operands)
 //     and at the end  delta = D / l,  dQx = scale (A - delta B) / l,  lse = m + log2 l.
 //   bwd_tc_keys_kernel   one CTA per 128 keys, over the query tiles that see them, transposed so that a thread
-//     owns a key:  S^T = K Qx^T, dP^T = Vx dO^T,  P^T = 2^(c S^T - lse_i),  dS^T = P^T (dP^T - delta_i) scale,
-//       dVx += P^T dO,  dK += dS^T Qx.
+//     owns a key:  S^T = K Qx^T, dP^T = Vx dO^T,  P^T = 2^(c S^T - lse_i),  dS^T = P^T (dP^T - delta_i),
+//       dVx += P^T dO,  dK += scale dS^T Qx.
+//
+// Threads: eight weight warps (two threads per row or key) and a warpgroup of four issuing threads, one per kind
+// of product (the loads ride with one of them).  What bounds a tile today is the weight threads' pass (tensor-memory
+// load, maximum and its exchange, exponentials, packing, store: some 2500 cycles) with the products (some 1900
+// cycles of tensor-pipe time) running under it.
 //
 // Qx, Vx are the advected queries and diffused values (16-bit, made by a prologue kernel when the Navier-Stokes
 // terms are on); the transposed stencils and the blend are handled around the kernels as in attn_bwd.cu.
@@ -59,14 +64,17 @@ __device__ __forceinline__ bool tile_visible(const BwdTcArgs& a, int q0, int q_l
 
 // two values as one word of the operand type; FP16 saturates at +-65504 instead of turning into infinity (a weight
 // e dP or dS beyond that is outside what FP16 operands can carry: BF16 has the range)
-__device__ __forceinline__ uint32_t pack2(float x, float y, bool f16) {
-    if (f16) {
-        x = fminf(fmaxf(x, -65504.0f), 65504.0f);
-        y = fminf(fmaxf(y, -65504.0f), 65504.0f);
-    }
+// The operand type is a template parameter of the kernels: a run-time switch inside the unrolled passes costs
+// instructions per pair and doubles their code.
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float x, float y) {
     // one packed conversion per pair: two scalar conversions would go through the XU pipe, which the
     // exponentials already keep busy
-    if (f16) { __half2 h = __floats2half2_rn(x, y); return *reinterpret_cast<uint32_t*>(&h); }
+    if (F16) {
+        uint32_t w;      // x in the lower half; the conversion itself saturates
+        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(y), "f"(x));
+        return w;
+    }
     __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
     return *reinterpret_cast<uint32_t*>(&h);
 }
@@ -77,33 +85,39 @@ __device__ __forceinline__ uint64_t desc_rows(uint32_t tile, int kk) { return sm
 __device__ __forceinline__ uint64_t desc_chan(uint32_t tile, int kk) { return smem_desc(tile + (uint32_t)kk * 32u); }
 
 // 32 fp32 values -> 16 packed words written to tensor memory columns [col, col + 16)
-__device__ __forceinline__ void st_packed32(uint32_t taddr, const float* v, bool f16) {
+template <bool F16>
+__device__ __forceinline__ void st_packed32(uint32_t taddr, const float* v) {
     uint32_t pk[8];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) pk[e] = pack2(v[16 * h + 2 * e], v[16 * h + 2 * e + 1], f16);
+        for (int e = 0; e < 8; ++e) pk[e] = pack2<F16>(v[16 * h + 2 * e], v[16 * h + 2 * e + 1]);
         tc_st8(taddr + 8u * (uint32_t)h, pk);
     }
 }
 
-enum { RB_QG = 0, RB_KVFULL0, RB_KVFULL1, RB_KVEMPTY0, RB_KVEMPTY1, RB_SFULL, RB_SEMPTY, RB_WFULL, RB_ACC, RB_XCH, RB_NUM };
-constexpr int kRowsOffXch = 6 * kBTile;                       // [2][2][128] floats: the half rows' maxima (and, at the end, sums)
+// The streamed operand pairs (K and V tiles in the rows kernel, Q and dO tiles in the keys kernel) go through a ring
+// of kStages stages; a load is issued two tiles before its scores are.
+constexpr int kStages = 4;
+enum { RB_QG = 0, RB_KVFULL0 = 1, RB_KVEMPTY0 = RB_KVFULL0 + kStages, RB_SFULL = RB_KVEMPTY0 + kStages, RB_SEMPTY, RB_WFULL,
+       RB_ACC, RB_XCH, RB_NUM };
+constexpr int kRowsOffXch = (2 + 2 * kStages) * kBTile;                       // [2][2][128] floats: the half rows' maxima (and, at the end, sums)
 constexpr int kRowsOffBar = kRowsOffXch + 2 * 2 * kBT * 4;
 constexpr int kRowsSmem = kRowsOffBar + RB_NUM * 8 + 64 + 1024;
 // Eight weight warps: a query row is shared by two threads (warps w and w + 4 own the same tensor-memory lanes), each
 // taking 64 of the tile's 128 keys.  They agree on the row's maximum through shared memory once per tile and keep
 // partial sums of their own until the end.
-constexpr int kRowsThreads = 384;      // three warpgroups: two of weight warps, one that holds the control warp
+constexpr int kRowsThreads = 384;      // three warpgroups: two of weight warps, one of issuing warps
 constexpr int kRowsCtrl = 8;
 
+template <bool F16>
 __global__ void __launch_bounds__(kRowsThreads, 1)
 bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t sQ = sbase, sG = sbase + kBTile, sK = sbase + 2 * kBTile, sV = sbase + 4 * kBTile;
+    const uint32_t sQ = sbase, sG = sbase + kBTile, sK = sbase + 2 * kBTile, sV = sbase + (2 + kStages) * kBTile;
     float* xch = reinterpret_cast<float*>(smem + kRowsOffXch);
     const uint32_t bar0 = sbase + kRowsOffBar;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -114,15 +128,15 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const int S = a.S, bh = blockIdx.y;
     const int q0 = blockIdx.x * kBT, q_last = min(S, q0 + kBT) - 1;
     const int kt_end = (S + kBT - 1) / kBT;
-    const bool f16 = a.f16 != 0;
+    constexpr bool f16 = F16;
 
     if (warp == kRowsCtrl && lane == 0) {
         mbar_init(bar(RB_QG), 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(RB_KVFULL0 + s), 1); mbar_init(bar(RB_KVEMPTY0 + s), 1); }
-        mbar_init(bar(RB_SFULL), 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(RB_KVFULL0 + s), 1); mbar_init(bar(RB_KVEMPTY0 + s), 2); }
+        mbar_init(bar(RB_SFULL), 2);         // two issuing threads commit each of SFULL, ACC and KVEMPTY
         mbar_init(bar(RB_SEMPTY), 256);
         mbar_init(bar(RB_WFULL), 256);
-        mbar_init(bar(RB_ACC), 1);
+        mbar_init(bar(RB_ACC), 2);
         mbar_init(bar(RB_XCH), 256);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -143,65 +157,73 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         return kt;
     };
 
-    // registers move from the control warpgroup (one busy warp, three idle) to the weight warpgroups, which hold a
+    // registers move from the control warpgroup (one thread busy in each warp) to the weight warpgroups, which hold a
     // tile's scores and their gradients in registers
     if (warp >= kRowsCtrl) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsCtrl));
-        if (warp == kRowsCtrl && lane == 0) {
+        if (lane == 0) {
+            // One thread of each warp of this warpgroup issues one kind of product (an MMA costs its issuing thread some
+            // 75 cycles, so one thread issuing a tile's 24 MMAs was the period of the whole CTA):
+            //   role 0: A += (e dP) K        role 1: B += e K
+            //   role 2: the loads and S = Qx K^T      role 3: dP = dO Vx^T
+            const int role = warp - kRowsCtrl;
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
-            mbar_expect_tx(bar(RB_QG), 2 * kBTile);
-            tma_load_3d(sQ, &mapQ, 0, q0, bh, bar(RB_QG));
-            tma_load_3d(sG, &mapG, 0, q0, bh, bar(RB_QG));
-            int kt_load = next_visible(0), n_load = 0;
             bool ok = true;
-            auto load_next = [&]() {         // the next visible tile into the stage that is (or becomes) free
-                if (kt_load >= kt_end) return;
-                const int st = n_load & 1;
-                if (n_load >= 2 && !mbar_wait(bar(RB_KVEMPTY0 + st), ((n_load >> 1) - 1) & 1, abort_flag)) { ok = false; return; }
-                mbar_expect_tx(bar(RB_KVFULL0 + st), 2 * kBTile);
-                tma_load_3d(sK + st * kBTile, &mapK, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
-                tma_load_3d(sV + st * kBTile, &mapV, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
-                ++n_load;
-                kt_load = next_visible(kt_load + 1);
-            };
-            auto issue_scores = [&](int n) {  // S = Qx K^T, dP = dO Vx^T of the n-th visible tile
-                const int st = n & 1;
-                if (n == 0 && !mbar_wait(bar(RB_QG), 0, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(bar(RB_KVFULL0 + st), (n >> 1) & 1, abort_flag)) { ok = false; return; }
-                if (n > 0 && !mbar_wait(bar(RB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; return; }
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < kBD / 16; ++kk) {
-                    tc_mma_f16(tmem + cS, desc_chan(sQ, kk), desc_chan(sK + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
-                    tc_mma_f16(tmem + cP, desc_chan(sG, kk), desc_chan(sV + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+            if (role >= 2) {
+                int kt_load = next_visible(0), n_load = 0;
+                auto load_next = [&]() {         // the next visible tile into its stage, once the products that read it are done
+                    if (kt_load >= kt_end) return;
+                    const int st = n_load % kStages;
+                    if (n_load >= kStages && !mbar_wait(bar(RB_KVEMPTY0 + st), (n_load / kStages - 1) & 1, abort_flag)) { ok = false; return; }
+                    mbar_expect_tx(bar(RB_KVFULL0 + st), 2 * kBTile);
+                    tma_load_3d(sK + st * kBTile, &mapK, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
+                    tma_load_3d(sV + st * kBTile, &mapV, 0, kt_load * kBT, bh, bar(RB_KVFULL0 + st));
+                    ++n_load;
+                    kt_load = next_visible(kt_load + 1);
+                };
+                if (role == 2) {
+                    mbar_expect_tx(bar(RB_QG), 2 * kBTile);
+                    tma_load_3d(sQ, &mapQ, 0, q0, bh, bar(RB_QG));
+                    tma_load_3d(sG, &mapG, 0, q0, bh, bar(RB_QG));
+                    for (int u = 0; u < kStages; ++u) load_next();
                 }
-                tc_commit(bar(RB_SFULL));
-            };
-            load_next();
-            load_next();
-            int kt = next_visible(0), n = 0;
-            if (ok && kt < kt_end) issue_scores(0);
-            while (ok && kt < kt_end) {
-                const int st = n & 1;
-                const int kt_next = next_visible(kt + 1);
-                // the next tile's scores run while the threads work on this one (they free S and dP as soon as
-                // they hold them in registers)
-                if (kt_next < kt_end) issue_scores(n + 1);
-                if (!ok || !mbar_wait(bar(RB_WFULL), n & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
+                int n = 0;
+                for (int kt = next_visible(0); ok && kt < kt_end; kt = next_visible(kt + 1), ++n) {
+                    // the scores of tile n are issued as soon as the threads hold tile n - 1's in registers, so they run
+                    // under the threads' pass over tile n - 1
+                    const int st = n % kStages;
+                    if (n == 0 && !mbar_wait(bar(RB_QG), 0, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(RB_KVFULL0 + st), (n / kStages) & 1, abort_flag)) { ok = false; break; }
+                    if (n > 0 && !mbar_wait(bar(RB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < kBT / 16; ++kk) {
-                    const uint64_t bd = desc_rows(sK + st * kBTile, kk);
-                    const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
-                    tc_mma_f16_ta(tmem + cA, tmem + cW1 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
-                    tc_mma_f16_ta(tmem + cB, tmem + cW2 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
+                    for (int kk = 0; kk < kBD / 16; ++kk) {
+                        if (role == 2) tc_mma_f16(tmem + cS, desc_chan(sQ, kk), desc_chan(sK + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                        else           tc_mma_f16(tmem + cP, desc_chan(sG, kk), desc_chan(sV + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar(RB_SFULL));
+                    // tile n + 2 goes into the stage of tile n - 2, whose accumulating products end about now; this
+                    // thread has the time to wait for them, and the load has two tiles' time to arrive
+                    if (role == 2 && n >= kStages - 2) load_next();
                 }
-                tc_commit(bar(RB_ACC));
-                tc_commit(bar(RB_KVEMPTY0 + st));
-                load_next();
-                kt = kt_next;
-                ++n;
+            } else {
+                int n = 0;
+                for (int kt = next_visible(0); ok && kt < kt_end; kt = next_visible(kt + 1), ++n) {
+                    const int st = n % kStages;
+                    if (!mbar_wait(bar(RB_KVFULL0 + st), (n / kStages) & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(RB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < kBT / 16; ++kk) {
+                        const uint64_t bd = desc_rows(sK + st * kBTile, kk);
+                        const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
+                        if (role == 0) tc_mma_f16_ta(tmem + cA, tmem + cW1 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
+                        else           tc_mma_f16_ta(tmem + cB, tmem + cW2 + 8u * (uint32_t)kk, bd, idesc_acc, accu);
+                    }
+                    tc_commit(bar(RB_ACC));
+                    tc_commit(bar(RB_KVEMPTY0 + st));
+                }
             }
         }
     } else {
@@ -239,16 +261,9 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             tc_wait_ld();
             tc_fence_before();
             mbar_arrive(bar(RB_SEMPTY));      // S and dP are in registers: the next tile's scores may overwrite them
-            float mx = -INFINITY;
             // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
             const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
-            if (full) {
-#pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    s[j] *= a.c;
-                    mx = fmaxf(mx, s[j]);
-                }
-            } else {
+            if (!full) {
                 // allowed(i, j) as in key_allowed() (cuda/VedicGEMM.cu:987-996), with the landmark rule's remainder
                 // carried along the row instead of divided out per key
                 int rem = (shun && a.stride > 0) ? kh % a.stride : 1;
@@ -258,11 +273,21 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                     bool okj = i < S && key < S && (!causal || key <= i);
                     if (shun) okj = okj && ((key >= i - a.window && key <= i) || (a.stride > 0 && rem == 0));
                     rem = (rem + 1 == a.stride) ? 0 : rem + 1;
-                    s[j] = okj ? s[j] * a.c : -INFINITY;
-                    mx = fmaxf(mx, s[j]);
+                    if (!okj) s[j] = -INFINITY;
                 }
             }
+            // the maximum of the raw products (the factor c is positive and goes into the exponent's multiply-add):
+            // three-input maxima on eight independent chains instead of one chain of 64 dependent instructions
+            float mx;
             {
+                float mc[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) mc[q] = fmaxf(s[2 * q], s[2 * q + 1]);
+#pragma unroll
+                for (int j = 16; j < 64; j += 16)
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) mc[q] = fmaxf(fmaxf(mc[q], s[j + 2 * q]), s[j + 2 * q + 1]);
+                mx = fmaxf(fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3])), fmaxf(fmaxf(mc[4], mc[5]), fmaxf(mc[6], mc[7]))) * a.c;
                 float other;
                 if (!exchange(mx, other)) { ok = false; break; }
                 mx = fmaxf(mx, other);           // the row's maximum over the whole tile: the same in both threads
@@ -295,22 +320,28 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             // without `any`, a lane only moves its maximum while its sums are still empty (first tile, or nothing seen yet)
             m_run = m_new;
             const float neg_m = (m_run == -INFINITY) ? 0.0f : -m_run;
-            float lsum = 0.0f, dsum = 0.0f;
+            // the arithmetic runs on register pairs (two-wide fp32 instructions), the sums on two chains each
+            const float2 c2 = make_float2(a.c, a.c), nm2 = make_float2(neg_m, neg_m);
+            float2 lsum[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+            float2 dsum[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int cb = 0; cb < 2; ++cb) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float e = ex2(s[32 * cb + j] + neg_m);      // -inf gives 0
-                    s[32 * cb + j] = e;
-                    lsum += e;
-                    dp[32 * cb + j] *= e;                             // e dP
-                    dsum += dp[32 * cb + j];
+                for (int j = 0; j < 32; j += 2) {
+                    const int x = 32 * cb + j;
+                    const float2 t = __ffma2_rn(make_float2(s[x], s[x + 1]), c2, nm2);
+                    const float2 e = make_float2(ex2(t.x), ex2(t.y));             // -inf gives 0
+                    s[x] = e.x; s[x + 1] = e.y;
+                    lsum[(j >> 1) & 1] = __fadd2_rn(lsum[(j >> 1) & 1], e);
+                    const float2 w = __fmul2_rn(make_float2(dp[x], dp[x + 1]), e);    // e dP
+                    dp[x] = w.x; dp[x + 1] = w.y;
+                    dsum[(j >> 1) & 1] = __fadd2_rn(dsum[(j >> 1) & 1], w);
                 }
-                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, dp + 32 * cb, f16);
-                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, s + 32 * cb, f16);
+                st_packed32<F16>(tmem + lane_addr + cW1 + col_w + 16 * cb, dp + 32 * cb);
+                st_packed32<F16>(tmem + lane_addr + cW2 + col_w + 16 * cb, s + 32 * cb);
             }
-            l_run += lsum;
-            d_run += dsum;
+            l_run += (lsum[0].x + lsum[0].y) + (lsum[1].x + lsum[1].y);
+            d_run += (dsum[0].x + dsum[0].y) + (dsum[1].x + dsum[1].y);
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(bar(RB_WFULL));       // the weights are in place
@@ -366,8 +397,9 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     }
 }
 
-enum { KB_KV = 0, KB_QGFULL0, KB_QGFULL1, KB_QGEMPTY0, KB_QGEMPTY1, KB_SFULL, KB_SEMPTY, KB_WFULL, KB_ACC, KB_STAT, KB_NUM };
-constexpr int kKeysOffStat = 6 * kBTile;                       // [2][2][128] floats: lse, delta of two query tiles in turn
+enum { KB_KV = 0, KB_QGFULL0 = 1, KB_QGEMPTY0 = KB_QGFULL0 + kStages, KB_SFULL = KB_QGEMPTY0 + kStages, KB_SEMPTY, KB_WFULL,
+       KB_ACC, KB_STAT, KB_NUM };
+constexpr int kKeysOffStat = (2 + 2 * kStages) * kBTile;                       // [2][2][128] floats: lse, delta of two query tiles in turn
 constexpr int kKeysOffBar = kKeysOffStat + 2 * 2 * kBT * 4;
 constexpr int kKeysSmem = kKeysOffBar + KB_NUM * 8 + 64 + 1024;
 
@@ -376,13 +408,14 @@ constexpr int kKeysSmem = kKeysOffBar + KB_NUM * 8 + 64 + 1024;
 constexpr int kKeysThreads = 384;      // as in the rows kernel
 constexpr int kKeysCtrl = 8;
 
+template <bool F16>
 __global__ void __launch_bounds__(kKeysThreads, 1)
 bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapG, const BwdTcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t sK = sbase, sV = sbase + kBTile, sQ = sbase + 2 * kBTile, sG = sbase + 4 * kBTile;
+    const uint32_t sK = sbase, sV = sbase + kBTile, sQ = sbase + 2 * kBTile, sG = sbase + (2 + kStages) * kBTile;
     float* stat = reinterpret_cast<float*>(smem + kKeysOffStat);
     const uint32_t bar0 = sbase + kKeysOffBar;
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -392,7 +425,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = a.S, bh = blockIdx.y;
     const int k0 = blockIdx.x * kBT, k_last = min(S, k0 + kBT) - 1;
-    const bool f16 = a.f16 != 0;
+    constexpr bool f16 = F16;
     // query tiles that can see these keys: from the diagonal on (causal); a pure window ends them early
     const int qt_begin = a.causal ? k0 / kBT : 0;
     int qt_end = (S + kBT - 1) / kBT;
@@ -400,11 +433,11 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
     if (warp == kKeysCtrl && lane == 0) {
         mbar_init(bar(KB_KV), 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(bar(KB_QGFULL0 + s), 1); mbar_init(bar(KB_QGEMPTY0 + s), 1); }
-        mbar_init(bar(KB_SFULL), 1);
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar(KB_QGFULL0 + s), 1); mbar_init(bar(KB_QGEMPTY0 + s), 2); }
+        mbar_init(bar(KB_SFULL), 2);
         mbar_init(bar(KB_SEMPTY), 256);
         mbar_init(bar(KB_WFULL), 256);
-        mbar_init(bar(KB_ACC), 1);
+        mbar_init(bar(KB_ACC), 2);
         mbar_init(bar(KB_STAT), 256);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -427,59 +460,63 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 
     if (warp >= kKeysCtrl) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsCtrl));
-        if (warp == kKeysCtrl && lane == 0) {
+        if (lane == 0) {
+            // as in the rows kernel, one issuing thread per kind of product:
+            //   role 0: dVx += P^T dO        role 1: dK += dS^T Qx
+            //   role 2: the loads and S^T = K Qx^T    role 3: dP^T = Vx dO^T
+            const int role = warp - kKeysCtrl;
             const int fmt = f16 ? 0 : 1;
             const uint32_t idesc_s = instr_desc(fmt, fmt, 0, kBT), idesc_acc = instr_desc(fmt, fmt, 1, kBD);
-            mbar_expect_tx(bar(KB_KV), 2 * kBTile);
-            tma_load_3d(sK, &mapK, 0, k0, bh, bar(KB_KV));
-            tma_load_3d(sV, &mapV, 0, k0, bh, bar(KB_KV));
-            int qt_load = next_visible(qt_begin), n_load = 0;
             bool ok = true;
-            auto load_next = [&]() {
-                if (qt_load >= qt_end) return;
-                const int st = n_load & 1;
-                if (n_load >= 2 && !mbar_wait(bar(KB_QGEMPTY0 + st), ((n_load >> 1) - 1) & 1, abort_flag)) { ok = false; return; }
-                mbar_expect_tx(bar(KB_QGFULL0 + st), 2 * kBTile);
-                tma_load_3d(sQ + st * kBTile, &mapQ, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
-                tma_load_3d(sG + st * kBTile, &mapG, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
-                ++n_load;
-                qt_load = next_visible(qt_load + 1);
-            };
-            auto issue_scores = [&](int n) {  // S^T = K Qx^T, dP^T = Vx dO^T of the n-th visible query tile
-                const int st = n & 1;
-                if (n == 0 && !mbar_wait(bar(KB_KV), 0, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(bar(KB_QGFULL0 + st), (n >> 1) & 1, abort_flag)) { ok = false; return; }
-                if (n > 0 && !mbar_wait(bar(KB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; return; }
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < kBD / 16; ++kk) {
-                    tc_mma_f16(tmem + cS, desc_chan(sK, kk), desc_chan(sQ + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
-                    tc_mma_f16(tmem + cP, desc_chan(sV, kk), desc_chan(sG + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+            if (role >= 2) {
+                int qt_load = next_visible(qt_begin), n_load = 0;
+                auto load_next = [&]() {
+                    if (qt_load >= qt_end) return;
+                    const int st = n_load % kStages;
+                    if (n_load >= kStages && !mbar_wait(bar(KB_QGEMPTY0 + st), (n_load / kStages - 1) & 1, abort_flag)) { ok = false; return; }
+                    mbar_expect_tx(bar(KB_QGFULL0 + st), 2 * kBTile);
+                    tma_load_3d(sQ + st * kBTile, &mapQ, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
+                    tma_load_3d(sG + st * kBTile, &mapG, 0, qt_load * kBT, bh, bar(KB_QGFULL0 + st));
+                    ++n_load;
+                    qt_load = next_visible(qt_load + 1);
+                };
+                if (role == 2) {
+                    mbar_expect_tx(bar(KB_KV), 2 * kBTile);
+                    tma_load_3d(sK, &mapK, 0, k0, bh, bar(KB_KV));
+                    tma_load_3d(sV, &mapV, 0, k0, bh, bar(KB_KV));
+                    for (int u = 0; u < kStages; ++u) load_next();
                 }
-                tc_commit(bar(KB_SFULL));
-            };
-            load_next();
-            load_next();
-            int qt = next_visible(qt_begin), n = 0;
-            if (ok && qt < qt_end) issue_scores(0);
-            while (ok && qt < qt_end) {
-                const int st = n & 1;
-                const int qt_next = next_visible(qt + 1);
-                // the next tile's scores run while the threads work on this one
-                if (qt_next < qt_end) issue_scores(n + 1);
-                if (!ok || !mbar_wait(bar(KB_WFULL), n & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
+                int n = 0;
+                for (int qt = next_visible(qt_begin); ok && qt < qt_end; qt = next_visible(qt + 1), ++n) {
+                    const int st = n % kStages;
+                    if (n == 0 && !mbar_wait(bar(KB_KV), 0, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(KB_QGFULL0 + st), (n / kStages) & 1, abort_flag)) { ok = false; break; }
+                    if (n > 0 && !mbar_wait(bar(KB_SEMPTY), (n - 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < kBT / 16; ++kk) {
-                    const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
-                    tc_mma_f16_ta(tmem + cV, tmem + cW1 + 8u * (uint32_t)kk, desc_rows(sG + st * kBTile, kk), idesc_acc, accu);
-                    tc_mma_f16_ta(tmem + cK, tmem + cW2 + 8u * (uint32_t)kk, desc_rows(sQ + st * kBTile, kk), idesc_acc, accu);
+                    for (int kk = 0; kk < kBD / 16; ++kk) {
+                        if (role == 2) tc_mma_f16(tmem + cS, desc_chan(sK, kk), desc_chan(sQ + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                        else           tc_mma_f16(tmem + cP, desc_chan(sV, kk), desc_chan(sG + st * kBTile, kk), idesc_s, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(bar(KB_SFULL));
+                    if (role == 2 && n >= kStages - 2) load_next();
                 }
-                tc_commit(bar(KB_ACC));
-                tc_commit(bar(KB_QGEMPTY0 + st));
-                load_next();
-                qt = qt_next;
-                ++n;
+            } else {
+                int n = 0;
+                for (int qt = next_visible(qt_begin); ok && qt < qt_end; qt = next_visible(qt + 1), ++n) {
+                    const int st = n % kStages;
+                    if (!mbar_wait(bar(KB_QGFULL0 + st), (n / kStages) & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar(KB_WFULL), n & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < kBT / 16; ++kk) {
+                        const uint32_t accu = (n > 0 || kk > 0) ? 1u : 0u;
+                        if (role == 0) tc_mma_f16_ta(tmem + cV, tmem + cW1 + 8u * (uint32_t)kk, desc_rows(sG + st * kBTile, kk), idesc_acc, accu);
+                        else           tc_mma_f16_ta(tmem + cK, tmem + cW2 + 8u * (uint32_t)kk, desc_rows(sQ + st * kBTile, kk), idesc_acc, accu);
+                    }
+                    tc_commit(bar(KB_ACC));
+                    tc_commit(bar(KB_QGEMPTY0 + st));
+                }
             }
         }
     } else {
@@ -492,8 +529,20 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         const bool causal = a.causal != 0, shun = a.shunyam != 0;
         bool ok = true;
         int n = 0;
-        for (int qt = next_visible(qt_begin); ok && qt < qt_end; qt = next_visible(qt + 1), ++n) {
+        // a query tile's statistic is fetched one tile ahead, so its way from global memory is hidden behind the
+        // previous tile's pass
+        auto fetch_stat = [&](int qt) {
+            const int q = qt * kBT + r;
+            if (qt >= qt_end) return 0.0f;
+            // both negated: they enter the pass as addends
+            if (half == 0) return q < S ? -a.lse[(size_t)bh * S + q] : -INFINITY;
+            return q < S ? -a.delta[(size_t)bh * S + q] : 0.0f;
+        };
+        int qt_next = next_visible(qt_begin);
+        float stat_next = fetch_stat(qt_next);
+        for (int qt = qt_next; ok && qt < qt_end; qt = qt_next, ++n) {
             const int q0 = qt * kBT, qh = q0 + 64 * half;
+            qt_next = next_visible(qt + 1);
             // the query tile's statistics go through shared memory: the thread pair of row r fetches query r's
             // log-sum-exp and delta, all threads then read all of them (broadcast reads).  Two buffers in turn: a
             // thread can only write tile n + 2's after every thread has arrived for tile n + 1, i.e. has finished
@@ -501,9 +550,10 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             // cannot get stuck in it.
             float* st_lse = stat + (n & 1) * 2 * kBT;
             float* st_dlt = st_lse + kBT;
-            if (half == 0) st_lse[r] = (q0 + r < S) ? a.lse[(size_t)bh * S + q0 + r] : INFINITY;
-            else           st_dlt[r] = (q0 + r < S) ? a.delta[(size_t)bh * S + q0 + r] : 0.0f;
+            if (half == 0) st_lse[r] = stat_next;
+            else           st_dlt[r] = stat_next;
             mbar_arrive(bar(KB_STAT));
+            stat_next = fetch_stat(qt_next);
             if (!mbar_wait(bar(KB_STAT), n & 1, abort_flag)) { ok = false; break; }
             if (!mbar_wait(bar(KB_SFULL), n & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -517,9 +567,20 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             mbar_arrive(bar(KB_SEMPTY));      // S^T and dP^T are in registers: the next tile's scores may overwrite them
             // a tile wholly inside the sequence and (if causal) wholly below the diagonal needs no mask
             const bool full = !shun && q0 + kBT <= S && k0 + kBT <= S && (!causal || k0 + kBT - 1 <= q0);
+            // the statistics (stored negated) are read four at a time -- every thread reads the same words:
+            // broadcasts -- and the arithmetic runs on register pairs (two-wide fp32 instructions)
+            const float4* lse4 = reinterpret_cast<const float4*>(st_lse + 64 * half);
+            const float4* dlt4 = reinterpret_cast<const float4*>(st_dlt + 64 * half);
+            const float2 c2 = make_float2(a.c, a.c);
             if (full) {
 #pragma unroll
-                for (int q = 0; q < 64; ++q) s[q] = ex2(s[q] * a.c - st_lse[64 * half + q]);
+                for (int q = 0; q < 64; q += 4) {
+                    const float4 l = lse4[q >> 2];
+                    const float2 t0 = __ffma2_rn(make_float2(s[q], s[q + 1]), c2, make_float2(l.x, l.y));
+                    const float2 t1 = __ffma2_rn(make_float2(s[q + 2], s[q + 3]), c2, make_float2(l.z, l.w));
+                    s[q] = ex2(t0.x); s[q + 1] = ex2(t0.y);
+                    s[q + 2] = ex2(t1.x); s[q + 3] = ex2(t1.y);
+                }
             } else {
                 // allowed(i, j) as in key_allowed() (cuda/VedicGEMM.cu:987-996); whether this thread's key is a landmark
                 // does not depend on the query
@@ -529,7 +590,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
                     const int qi = qh + q;
                     bool okq = j < S && qi < S && (!causal || j <= qi);
                     if (shun) okq = okq && ((j >= qi - a.window && j <= qi) || landmark);
-                    s[q] = okq ? ex2(s[q] * a.c - st_lse[64 * half + q]) : 0.0f;   // p_ij; lse = +inf for a dead row gives 0
+                    s[q] = okq ? ex2(fmaf(s[q], a.c, st_lse[64 * half + q])) : 0.0f;   // p_ij; -lse = -inf for a dead row gives 0
                 }
             }
             if (n > 0) {
@@ -538,11 +599,18 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
 #pragma unroll
             for (int cb = 0; cb < 2; ++cb) {
+                // ds_ij without the softmax scale: that factor multiplies the finished dK rows
 #pragma unroll
-                for (int q = 0; q < 32; ++q)
-                    dp[32 * cb + q] = s[32 * cb + q] * (dp[32 * cb + q] - st_dlt[64 * half + 32 * cb + q]) * a.scale;   // ds_ij
-                st_packed32(tmem + lane_addr + cW1 + col_w + 16 * cb, s + 32 * cb, f16);
-                st_packed32(tmem + lane_addr + cW2 + col_w + 16 * cb, dp + 32 * cb, f16);
+                for (int q = 0; q < 32; q += 4) {
+                    const int x = 32 * cb + q;
+                    const float4 d = dlt4[x >> 2];
+                    const float2 w0 = __fmul2_rn(make_float2(s[x], s[x + 1]), __fadd2_rn(make_float2(dp[x], dp[x + 1]), make_float2(d.x, d.y)));
+                    const float2 w1 = __fmul2_rn(make_float2(s[x + 2], s[x + 3]), __fadd2_rn(make_float2(dp[x + 2], dp[x + 3]), make_float2(d.z, d.w)));
+                    dp[x] = w0.x; dp[x + 1] = w0.y;
+                    dp[x + 2] = w1.x; dp[x + 3] = w1.y;
+                }
+                st_packed32<F16>(tmem + lane_addr + cW1 + col_w + 16 * cb, s + 32 * cb);
+                st_packed32<F16>(tmem + lane_addr + cW2 + col_w + 16 * cb, dp + 32 * cb);
             }
             tc_wait_st();
             tc_fence_before();
@@ -554,6 +622,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             // half 0 writes the key's dV row, half 1 its dK row
             float* dst = (half == 0 ? a.dVx : a.dK) + ((size_t)bh * S + j) * kBD;
             const bool acc_out = half == 1 && a.accumulate_dk;
+            const float wo = half == 0 ? a.w : a.w * a.scale;
 #pragma unroll
             for (int hc = 0; hc < 2; ++hc) {
                 float v[32];
@@ -567,7 +636,7 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 #pragma unroll
                     for (int q = 0; q < 32; q += 4) {
                         float4* p4 = reinterpret_cast<float4*>(dst + 32 * hc + q);
-                        float4 o4 = make_float4(v[q] * a.w, v[q + 1] * a.w, v[q + 2] * a.w, v[q + 3] * a.w);
+                        float4 o4 = make_float4(v[q] * wo, v[q + 1] * wo, v[q + 2] * wo, v[q + 3] * wo);
                         if (acc_out) { const float4 old = *p4; o4.x += old.x; o4.y += old.y; o4.z += old.z; o4.w += old.w; }
                         *p4 = o4;
                     }
@@ -671,8 +740,10 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
     a.S = S; a.scale = p->scale; a.c = p->scale * 1.4426950408889634f;
     a.causal = p->causal; a.shunyam = shunyam_active(p->window, S) ? 1 : 0;
     a.window = p->window; a.stride = p->stride; a.f16 = f16; a.status = ctx->tc_status;
-    if (int rc = ensure_smem_limit(ctx, bwd_tc_rows_kernel, kRowsSmem)) return rc;
-    if (int rc = ensure_smem_limit(ctx, bwd_tc_keys_kernel, kKeysSmem)) return rc;
+    auto* rows_fn = f16 ? bwd_tc_rows_kernel<true> : bwd_tc_rows_kernel<false>;
+    auto* keys_fn = f16 ? bwd_tc_keys_kernel<true> : bwd_tc_keys_kernel<false>;
+    if (int rc = ensure_smem_limit(ctx, rows_fn, kRowsSmem)) return rc;
+    if (int rc = ensure_smem_limit(ctx, keys_fn, kKeysSmem)) return rc;
     CUtensorMap mk, mg;
     if (!make_map_bwd(&mk, K, BH, S, f16) || !make_map_bwd(&mg, dO, BH, S, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
@@ -681,9 +752,9 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
         CUtensorMap mq, mv;
         if (!make_map_bwd(&mq, Qx, BH, S, f16) || !make_map_bwd(&mv, Vx, BH, S, f16))
             return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
-        bwd_tc_rows_kernel<<<grid, kRowsThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        rows_fn<<<grid, kRowsThreads, kRowsSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_rows_kernel");
-        bwd_tc_keys_kernel<<<grid, kKeysThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
+        keys_fn<<<grid, kKeysThreads, kKeysSmem, ctx->stream>>>(mq, mk, mv, mg, a);
         LOGOS_LAUNCH_CHECK(ctx, "bwd_tc_keys_kernel");
         return LOGOS_OK;
     };
