@@ -117,9 +117,13 @@ const char* logos_last_error(const logos_ctx* ctx);
  *                            The two give bit-identical results (same products, same order of k).
  *   LOGOS_OPT_DECODE_DEPTH   tiles of 32 keys a warp of the dense decode kernel holds at once: 2 or 4;
  *                            0 (default) = 4 when the launch is a single wave of CTAs, else 2.  The
- *                            arithmetic and its order do not depend on it. */
+ *                            arithmetic and its order do not depend on it.
+ *   LOGOS_OPT_QKV_OUT_F16    1: logos_qkv_project stores Q, K and V as FP16 whatever the operand type
+ *                            (the decode entry points take FP16: a BF16 model's decode step then needs no
+ *                            conversion pass); the max|x| tables are those of the stored FP16 values. */
 typedef enum { LOGOS_OPT_FORCE_GENERAL = 0, LOGOS_OPT_DECODE_CHUNK = 1, LOGOS_OPT_PEER_WAIT_MS = 2,
-               LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4, LOGOS_OPT_DECODE_DEPTH = 5 } logos_option;
+               LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4, LOGOS_OPT_DECODE_DEPTH = 5,
+               LOGOS_OPT_QKV_OUT_F16 = 6 } logos_option;
 int logos_ctx_set_option(logos_ctx* ctx, int option, int value);
 
 /* ---- attention ---------------------------------------------------------- */

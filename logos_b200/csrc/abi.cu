@@ -246,6 +246,9 @@ int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
                 return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: decode depth must be 0, 2 or 4");
             ctx->decode_depth = value;
             return LOGOS_OK;
+        case LOGOS_OPT_QKV_OUT_F16:
+            ctx->qkv_out_f16 = value != 0;
+            return LOGOS_OK;
     }
     return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: unknown option %d", option);
 }

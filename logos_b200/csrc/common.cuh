@@ -28,6 +28,7 @@ struct logos_ctx {
     bool workspace_locked = false;    // LOGOS_OPT_WORKSPACE_LOCK
     bool gemm_narrow = false;         // LOGOS_OPT_GEMM_NARROW
     int decode_depth = 0;             // LOGOS_OPT_DECODE_DEPTH
+    bool qkv_out_f16 = false;         // LOGOS_OPT_QKV_OUT_F16
     logos_alloc_fn alloc_fn = nullptr;   // caller's allocator for the workspace (null: cudaMalloc / cudaFree)
     logos_free_fn free_fn = nullptr;
     void* alloc_user = nullptr;

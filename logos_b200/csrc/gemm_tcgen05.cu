@@ -43,8 +43,8 @@ struct GemmArgs {
     void* C; const void* R;  // [M][N]; R may be null; same dtype as C
     int c_is_f32;
     // mode 1: N = 3 H 64, rows m = b S + s
-    void* q; void* k; void* v;         // [B][H][S][64], 16-bit, operand dtype
-    int S, H;
+    void* q; void* k; void* v;         // [B][H][S][64], 16-bit: the operand dtype, or FP16 with out_f16
+    int S, H, out_f16;
     unsigned* k_absmax; unsigned* v_absmax;   // [B][H] float bits (non-negative), atomicMax; may be null
     // A given head-major, [B][a_heads][a_S][64] (the attention's output layout) with K = 64 a_heads: k block kb
     // is head kb, so the tiles are fetched where they lie and nothing is permuted.  0: A is [M][K] row-major.
@@ -148,7 +148,7 @@ __device__ __forceinline__ void store_c_row(const GemmArgs& a, uint32_t t_row, i
 // max|x| of the stored (rounded) K or V values per (sequence, head) tensor
 __device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t_addr, int m, int n, bool row_live,
                                                    int lane) {
-    const bool f16 = a.f16 != 0;
+    const bool f16 = a.f16 != 0 || a.out_f16 != 0;    // the type Q, K, V are stored in
     const int b = m / a.S, s = m - b * a.S;
     const int hg = n / 64;                           // head slot among 3 H
     const int which = hg / a.H, h = hg - which * a.H;
@@ -553,7 +553,7 @@ int qkv_project(logos_ctx* ctx, int dtype, const void* X, const void* Wt, void* 
     }
     GemmArgs a{};
     a.M = B * S; a.N = 3 * H * 64; a.K = D; a.f16 = dtype == LOGOS_F16; a.mode = 1;
-    a.q = Q; a.k = K; a.v = V; a.S = S; a.H = H;
+    a.q = Q; a.k = K; a.v = V; a.S = S; a.H = H; a.out_f16 = ctx->qkv_out_f16 ? 1 : 0;
     a.k_absmax = reinterpret_cast<unsigned*>(k_absmax); a.v_absmax = reinterpret_cast<unsigned*>(v_absmax);
     return launch_gemm(ctx, X, Wt, a);
 }

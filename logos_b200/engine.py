@@ -106,18 +106,25 @@ class Engine:
         return out
 
     # ---- projections -----------------------------------------------------------
-    def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False, as_block=False):
+    def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False, as_block=False, out_f16=False):
         """X: [B*S, D] 16-bit; Wt_qkv: [3*H*64, D] (K-major shadow of the stacked W_Q | W_K | W_V) ->
         Q, K, V [B, H, S, 64] (three slices of one block, so that they can be converted or moved as one) and,
-        with absmax, the tables max|K|, max|V| [B, H] for the quantiser."""
+        with absmax, the tables max|K|, max|V| [B, H] for the quantiser.  out_f16: Q, K, V come out as FP16
+        whatever X is (LOGOS_OPT_QKV_OUT_F16: what the decode entry points take)."""
         D = X.shape[1]
         assert X.is_contiguous() and Wt_qkv.is_contiguous() and Wt_qkv.shape == (3 * H * 64, D) and X.shape[0] == B * S
-        block = torch.empty((3, B, H, S, 64), dtype=X.dtype, device=X.device)
+        block = torch.empty((3, B, H, S, 64), dtype=torch.float16 if out_f16 else X.dtype, device=X.device)
         Q, K, V = block.unbind(0)
         ka = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None
         va = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None
-        self._check(self.lib.logos_qkv_project(self.h, _DT[X.dtype], _ptr(X), _ptr(Wt_qkv), _ptr(Q), _ptr(K), _ptr(V),
-                                              B, S, H, D, _ptr(ka), _ptr(va)))
+        if out_f16:
+            self.set_option(L.OPT_QKV_OUT_F16, 1)
+        try:
+            self._check(self.lib.logos_qkv_project(self.h, _DT[X.dtype], _ptr(X), _ptr(Wt_qkv), _ptr(Q), _ptr(K), _ptr(V),
+                                                  B, S, H, D, _ptr(ka), _ptr(va)))
+        finally:
+            if out_f16:
+                self.set_option(L.OPT_QKV_OUT_F16, 0)
         if as_block:
             return (block, ka, va) if absmax else block
         return (Q, K, V, ka, va) if absmax else (Q, K, V)

@@ -131,8 +131,8 @@ class AttentionStack:
         lens = self.cache.lens
         for l in range(cfg.num_layers):
             xn = self._norm(x, l)
-            # the decode entry points take FP16: Q, K, V come as one block and are converted as one
-            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True).half().view(3, B, self.Hl, 64).unbind(0)
+            # the decode entry points take FP16: the projection's epilogue stores Q, K, V in that type
+            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True, out_f16=True).view(3, B, self.Hl, 64).unbind(0)
             kc, vc, ks, vs = self.cache.layer(l)
             if self.world == 1:
                 o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params)

@@ -69,6 +69,25 @@ def test_qkv_project_scatter_and_absmax(engine, B, S, H, D):
     assert torch.equal(s1, s2) and torch.equal(kc1, kc2)
 
 
+@pytest.mark.parametrize("B,S,H,D", [(32, 1, 16, 1024), (2, 130, 2, 256)])
+def test_qkv_project_fp16_output_of_bf16_operands(engine, B, S, H, D):
+    """LOGOS_OPT_QKV_OUT_F16: the same accumulators stored as FP16 (what the decode entry points take), the max|x|
+    tables those of the stored values; the option does not outlast the call that asked for it."""
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + S)
+    X = torch.randn((B * S, D), device="cuda", generator=g).bfloat16()
+    Wt = (torch.randn((3 * H * 64, D), device="cuda", generator=g) * 0.05).bfloat16()
+    Q, K, V, ka, va = engine.qkv_project(X, Wt, B, S, H, absmax=True, out_f16=True)
+    Qb, Kb, Vb = engine.qkv_project(X, Wt, B, S, H)
+    engine.synchronize()
+    assert Q.dtype == torch.float16 and Qb.dtype == torch.bfloat16
+    want = (X.double() @ Wt.double().t()).view(B, S, 3, H, 64).permute(2, 0, 3, 1, 4).float()
+    for i, (got, gotb) in enumerate(((Q, Qb), (K, Kb), (V, Vb))):
+        err = (got.float() - want[i]).abs()
+        assert bool((err <= want[i].abs() * 2.0 ** -10 + 1e-3).all()), float(err.max())      # FP16 keeps three more bits
+        assert bool(((gotb.float() - want[i]).abs() <= want[i].abs() * 2.0 ** -7 + 1e-3).all())
+    assert torch.equal(ka, K.float().abs().amax(dim=(2, 3))) and torch.equal(va, V.float().abs().amax(dim=(2, 3)))
+
+
 def test_projection_argument_checks(engine):
     A = torch.zeros((4, 60), device="cuda", dtype=torch.bfloat16)       # K not a multiple of 8
     Wt = torch.zeros((64, 60), device="cuda", dtype=torch.bfloat16)
