@@ -33,7 +33,15 @@ constexpr int kGN = 128;                 // output columns per CTA
 constexpr int kGK = 64;                  // k per stage (one 128-byte swizzle atom of 16-bit values)
 constexpr int kGTile = kBM * kGK * 2;    // 16 KiB: one operand tile
 constexpr int kGThreads = 192;
-constexpr int gemm_smem(int stages) { return 2 * stages * kGTile + (2 * stages + 1) * 8 + 64 + 1024; }
+constexpr int kSkinnyM = 32, kSkinnyN = 64, kSkinnyStages = 16;   // the decode-time form of the 128-row-tile kernel
+// shared memory of the 128-row-tile kernel: the ring, room for the tensor core to read a full 128-row A operand
+// from the last stage when the A box is smaller (see the kernel), barriers, alignment slack
+__host__ __device__ constexpr int gemm_ring(int stages, int arows, int bn) {
+    return stages * (arows + bn) * 128 + ((arows + bn) * 128 < kGTile ? kGTile - (arows + bn) * 128 : 0);
+}
+constexpr int gemm_smem(int stages, int arows = kBM, int bn = kGN) {
+    return gemm_ring(stages, arows, bn) + (2 * stages + 1) * 8 + 64 + 1024;
+}
 
 struct GemmArgs {
     int M, N, K;
@@ -196,10 +204,16 @@ __device__ __forceinline__ void scatter_head_slice(const GemmArgs& a, uint32_t t
 // STAGES = depth of the operand ring: 3 (96 KiB, two CTAs per SM) when the grid fills the device, 6 (192 KiB) for
 // small problems -- a decode-time GEMM has fewer CTAs than SMs and is a chain of TMA round trips, which a deeper
 // ring shortens.
-template <int STAGES>
+// AROWS, BN = rows of the A box and output columns per CTA.  The decode-time form <16, 32, 64> is for M <= 32: a
+// stage is 4 KiB of A and 8 KiB of W, so with K = 1024 every k block of the CTA is in flight at once and the chain
+// of round trips is one long.  The MMA still reads a 128-row A operand: rows AROWS.. are whatever lies behind the A
+// box in shared memory (the W tile, the next stage), they only reach accumulator rows that no one stores.
+template <int STAGES, int AROWS = kBM, int BN = kGN>
 __global__ void __launch_bounds__(kGThreads, STAGES == 3 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW, const GemmArgs a) {
-    constexpr int kOffBarT = 2 * STAGES * kGTile;
+    constexpr int kABytes = AROWS * 128, kStage = (AROWS + BN) * 128;
+    constexpr int kOffBarT = gemm_ring(STAGES, AROWS, BN);
+    static_assert(kABytes % 1024 == 0 && kStage % 1024 == 0, "tiles start on swizzle-atom boundaries");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -211,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffBarT + (2 * STAGES + 1) * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kGN;
+    const int n0 = blockIdx.x * BN;
     const int n_kb = (a.K + kGK - 1) / kGK;
     // rows of this tile: m0 .. m0 + 127, below m_lim.  Head-major A: tiles never straddle two sequences.
     int m0 = blockIdx.y * kBM, m_lim = a.M, a_row = m0, a_slab = 0;
@@ -244,10 +258,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int kb = 0; kb < n_kb; ++kb) {
                 const int s = kb % STAGES;
                 if (kb >= STAGES && !mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(full(s), 2 * kGTile);
-                if (a.a_heads) tma_load_3d(sbase + (2 * s) * kGTile, &mapA, 0, a_row, a_slab + kb, full(s));
-                else           tma_load_3d(sbase + (2 * s) * kGTile, &mapA, kb * kGK, m0, 0, full(s));
-                tma_load_3d(sbase + (2 * s + 1) * kGTile, &mapW, kb * kGK, n0, 0, full(s));
+                mbar_expect_tx(full(s), kStage);
+                if (a.a_heads) tma_load_3d(sbase + s * kStage, &mapA, 0, a_row, a_slab + kb, full(s));
+                else           tma_load_3d(sbase + s * kStage, &mapA, kb * kGK, m0, 0, full(s));
+                tma_load_3d(sbase + s * kStage + kABytes, &mapW, kb * kGK, n0, 0, full(s));
             }
         }
     } else if (warp == 1) {
@@ -255,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(elected));
         const bool leader = elected != 0;
         const int fmt = a.f16 ? 0 : 1;
-        const uint32_t idesc = instr_desc(fmt, fmt, 0, kGN);
+        const uint32_t idesc = instr_desc(fmt, fmt, 0, BN);
         bool ok = true;
         for (int kb = 0; ok && kb < n_kb; ++kb) {
             const int s = kb % STAGES;
@@ -263,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             if (leader) {
-                const uint32_t sa = sbase + (2 * s) * kGTile, sw = sa + kGTile;
+                const uint32_t sa = sbase + s * kStage, sw = sa + kABytes;
 #pragma unroll
                 for (int kk = 0; kk < kGK / 16; ++kk)
                     tc_mma_f16(tmem, smem_desc(sa + 32 * kk), smem_desc(sw + 32 * kk), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
@@ -282,10 +296,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (mbar_wait(acc_full, 0, abort_flag)) {
             tc_fence_after();
             if (a.mode == 0) {
-                store_c_row(a, t_row, m, n0, kGN, m < m_lim, res0);
+                store_c_row(a, t_row, m, n0, BN, m < m_lim, res0);
             } else {
 #pragma unroll 1
-                for (int gi = 0; gi < 2; ++gi) scatter_head_slice(a, t_row + 64 * gi, m, n0 + 64 * gi, m < m_lim, lane);
+                for (int gi = 0; gi < BN / 64; ++gi) scatter_head_slice(a, t_row + 64 * gi, m, n0 + 64 * gi, m < m_lim, lane);
             }
             tc_fence_before();
         }
@@ -485,9 +499,11 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
     // enough 128 x 256 tiles to give every SM one: the persistent wide kernel; otherwise the 128 x 128 kernel,
     // which has twice the CTAs for a small problem
     const bool wide = (int64_t)m_tiles * n_wide >= ctx->sm_count && !ctx->gemm_narrow;
+    // a decode step's projections: at most 32 rows
+    const bool skinny = a.M <= kSkinnyM && !a.a_heads && !wide;
     const bool a_ok = a.a_heads ? make_map_slabs(&ma, A, a.a_S, (a.M / a.a_S) * a.a_heads, a.f16 != 0)
-                                : make_map_2d(&ma, A, a.M, a.K, a.f16 != 0);
-    if (!a_ok || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0, wide ? kWN : kBM))
+                                : make_map_2d(&ma, A, a.M, a.K, a.f16 != 0, skinny ? kSkinnyM : kBM);
+    if (!a_ok || !make_map_2d(&mw, Wt, a.N, a.K, a.f16 != 0, wide ? kWN : (skinny ? kSkinnyN : kBM)))
         return fail(ctx, LOGOS_ERR_CUDA, "projection: cuTensorMapEncodeTiled failed");
     a.status = ctx->tc_status;
     if (wide) {
@@ -495,6 +511,14 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
         const int ctas = (int)std::min<int64_t>((int64_t)m_tiles * n_wide, ctx->sm_count);
         gemm_tc_wide_kernel<<<ctas, kGThreads, kWSmem, ctx->stream>>>(ma, mw, a, m_tiles, n_wide);
         LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_wide_kernel");
+        return LOGOS_OK;
+    }
+    if (skinny) {
+        auto* fn = gemm_tc_kernel<kSkinnyStages, kSkinnyM, kSkinnyN>;
+        constexpr int smem = gemm_smem(kSkinnyStages, kSkinnyM, kSkinnyN);
+        if (int rc = ensure_smem_limit(ctx, fn, smem)) return rc;
+        fn<<<dim3((a.N + kSkinnyN - 1) / kSkinnyN, 1), kGThreads, smem, ctx->stream>>>(ma, mw, a);
+        LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel (decode form)");
         return LOGOS_OK;
     }
     dim3 grid((a.N + kGN - 1) / kGN, m_tiles);

@@ -15,7 +15,7 @@ def _ref(A, W):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 1024), (300, 1024, 1024), (32, 3072, 1024), (1, 64, 72)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 192, 1024), (300, 1024, 1024), (32, 3072, 1024), (1, 64, 72), (7, 1024, 4096), (33, 128, 256)])
 def test_project_matches_fp64_product(engine, dtype, M, N, K):
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
     A = (torch.randn((M, K), device="cuda", generator=g)).to(dtype)
