@@ -120,10 +120,15 @@ const char* logos_last_error(const logos_ctx* ctx);
  *                            arithmetic and its order do not depend on it.
  *   LOGOS_OPT_QKV_OUT_F16    1: logos_qkv_project stores Q, K and V as FP16 whatever the operand type
  *                            (the decode entry points take FP16: a BF16 model's decode step then needs no
- *                            conversion pass); the max|x| tables are those of the stored FP16 values. */
+ *                            conversion pass); the max|x| tables are those of the stored FP16 values.
+ *   LOGOS_OPT_PROJECT_OVERLAP 1: a projection of at most 32 rows (a decode step's) is launched to overlap the
+ *                            kernel before it on the stream: it fetches its weight tiles while that kernel
+ *                            still runs and waits for it before it touches A, the residual or any output.
+ *                            The caller promises that the kernel before such a call does not write the
+ *                            weights.  0 (default): ordinary launches. */
 typedef enum { LOGOS_OPT_FORCE_GENERAL = 0, LOGOS_OPT_DECODE_CHUNK = 1, LOGOS_OPT_PEER_WAIT_MS = 2,
                LOGOS_OPT_WORKSPACE_LOCK = 3, LOGOS_OPT_GEMM_NARROW = 4, LOGOS_OPT_DECODE_DEPTH = 5,
-               LOGOS_OPT_QKV_OUT_F16 = 6 } logos_option;
+               LOGOS_OPT_QKV_OUT_F16 = 6, LOGOS_OPT_PROJECT_OVERLAP = 7 } logos_option;
 int logos_ctx_set_option(logos_ctx* ctx, int option, int value);
 
 /* ---- attention ---------------------------------------------------------- */

@@ -249,6 +249,9 @@ int logos_ctx_set_option(logos_ctx* ctx, int option, int value) {
         case LOGOS_OPT_QKV_OUT_F16:
             ctx->qkv_out_f16 = value != 0;
             return LOGOS_OK;
+        case LOGOS_OPT_PROJECT_OVERLAP:
+            ctx->project_overlap = value != 0;
+            return LOGOS_OK;
     }
     return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "set_option: unknown option %d", option);
 }

@@ -29,6 +29,7 @@ struct logos_ctx {
     bool gemm_narrow = false;         // LOGOS_OPT_GEMM_NARROW
     int decode_depth = 0;             // LOGOS_OPT_DECODE_DEPTH
     bool qkv_out_f16 = false;         // LOGOS_OPT_QKV_OUT_F16
+    bool project_overlap = false;     // LOGOS_OPT_PROJECT_OVERLAP
     logos_alloc_fn alloc_fn = nullptr;   // caller's allocator for the workspace (null: cudaMalloc / cudaFree)
     logos_free_fn free_fn = nullptr;
     void* alloc_user = nullptr;

@@ -253,14 +253,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    // Programmatic dependent launch (a no-op for an ordinary launch): the kernel after this one may start at once,
+    // and this one, when launched to overlap the kernel before it, fetches its weight tiles -- which no kernel
+    // writes -- straight away and waits for that kernel only where it first touches activations.
+    grid_release_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
-                mbar_expect_tx(full(s), kStage);
+            auto load_a = [&](int kb, int s) {
                 if (a.a_heads) tma_load_3d(sbase + s * kStage, &mapA, 0, a_row, a_slab + kb, full(s));
                 else           tma_load_3d(sbase + s * kStage, &mapA, kb * kGK, m0, 0, full(s));
+            };
+            const int first = n_kb < STAGES ? n_kb : STAGES;
+            for (int kb = 0; kb < first; ++kb) {
+                mbar_expect_tx(full(kb), kStage);
+                tma_load_3d(sbase + kb * kStage + kABytes, &mapW, kb * kGK, n0, 0, full(kb));
+            }
+            grid_wait_for_earlier();
+            for (int kb = 0; kb < first; ++kb) load_a(kb, kb);
+            for (int kb = first; kb < n_kb; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(empty(s), ((kb / STAGES) - 1) & 1, abort_flag)) break;
+                mbar_expect_tx(full(s), kStage);
+                load_a(kb, s);
                 tma_load_3d(sbase + s * kStage + kABytes, &mapW, kb * kGK, n0, 0, full(s));
             }
         }
@@ -292,6 +306,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int row = quarter * 32 + lane, m = m0 + row;
         const uint32_t t_row = tmem + (((uint32_t)(quarter * 32)) << 16);
         ResChunk res0;
+        grid_wait_for_earlier();          // the residual, the outputs and the max|x| tables belong to the stream's order
         if (a.mode == 0) load_residual_chunk(a, m, n0, m < m_lim, res0);
         if (mbar_wait(acc_full, 0, abort_flag)) {
             tc_fence_after();
@@ -517,7 +532,12 @@ int launch_gemm(logos_ctx* ctx, const void* A, const void* Wt, GemmArgs& a) {
         auto* fn = gemm_tc_kernel<kSkinnyStages, kSkinnyM, kSkinnyN>;
         constexpr int smem = gemm_smem(kSkinnyStages, kSkinnyM, kSkinnyN);
         if (int rc = ensure_smem_limit(ctx, fn, smem)) return rc;
-        fn<<<dim3((a.N + kSkinnyN - 1) / kSkinnyN, 1), kGThreads, smem, ctx->stream>>>(ma, mw, a);
+        const dim3 sgrid((a.N + kSkinnyN - 1) / kSkinnyN, 1);
+        if (ctx->project_overlap) {      // launched to overlap the kernel before it on the stream: see the kernel
+            LOGOS_CUDA_TRY(ctx, launch_overlapped(fn, sgrid, dim3(kGThreads), (size_t)smem, ctx->stream, ma, mw, a));
+        } else {
+            fn<<<sgrid, kGThreads, smem, ctx->stream>>>(ma, mw, a);
+        }
         LOGOS_LAUNCH_CHECK(ctx, "gemm_tc_kernel (decode form)");
         return LOGOS_OK;
     }

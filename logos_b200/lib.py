@@ -24,7 +24,7 @@ class Strides(C.Structure):
 
 MHA_ATTEND_DEQUANTIZED = 1
 OPT_FORCE_GENERAL, OPT_DECODE_CHUNK, OPT_PEER_WAIT_MS, OPT_WORKSPACE_LOCK, OPT_GEMM_NARROW, OPT_DECODE_DEPTH = 0, 1, 2, 3, 4, 5
-OPT_QKV_OUT_F16 = 6
+OPT_QKV_OUT_F16, OPT_PROJECT_OVERLAP = 6, 7
 COMM_HANDLE_BYTES = 80
 
 

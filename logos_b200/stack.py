@@ -129,6 +129,16 @@ class AttentionStack:
         x = self.embed[ids]                                                # [B, D]
         self.cache.advance(1)                                              # lens = length after the append
         lens = self.cache.lens
+        # the weights are never written during generation: the small projections may fetch them while the kernel
+        # before them still runs
+        eng.set_option(L.OPT_PROJECT_OVERLAP, 1)
+        try:
+            return self._decode_layers(x, lens)
+        finally:
+            eng.set_option(L.OPT_PROJECT_OVERLAP, 0)
+
+    def _decode_layers(self, x, lens):
+        cfg, eng, B = self.cfg, self.eng, self.batch
         for l in range(cfg.num_layers):
             xn = self._norm(x, l)
             # the decode entry points take FP16: the projection's epilogue stores Q, K, V in that type

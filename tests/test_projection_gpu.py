@@ -88,6 +88,29 @@ def test_qkv_project_fp16_output_of_bf16_operands(engine, B, S, H, D):
     assert torch.equal(ka, K.float().abs().amax(dim=(2, 3))) and torch.equal(va, V.float().abs().amax(dim=(2, 3)))
 
 
+def test_small_projections_launched_to_overlap_the_kernel_before(engine):
+    """LOGOS_OPT_PROJECT_OVERLAP: a chain of M <= 32 projections, each reading what the one before wrote, gives the
+    same bits as the ordinary launches (the weights are fetched early, the activations after the wait)."""
+    g = torch.Generator(device="cuda").manual_seed(77)
+    X = torch.randn((32, 1024), device="cuda", generator=g).bfloat16()
+    Ws = [(torch.randn((1024, 1024), device="cuda", generator=g) * 0.03).bfloat16() for _ in range(6)]
+
+    def chain():
+        y = X
+        for W in Ws:
+            y = engine.project(y, W, residual=y)
+        engine.synchronize()
+        return y
+
+    want = chain()
+    engine.set_option(L.OPT_PROJECT_OVERLAP, 1)
+    try:
+        for _ in range(3):
+            assert torch.equal(chain(), want)
+    finally:
+        engine.set_option(L.OPT_PROJECT_OVERLAP, 0)
+
+
 def test_projection_argument_checks(engine):
     A = torch.zeros((4, 60), device="cuda", dtype=torch.bfloat16)       # K not a multiple of 8
     Wt = torch.zeros((64, 60), device="cuda", dtype=torch.bfloat16)
