@@ -273,6 +273,12 @@ int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, co
                            const void* v_new, int8_t* k_cache, int8_t* v_cache, const float* k_scale,
                            const float* v_scale, const int32_t* len, int B, int H, int S_max, int DH,
                            const logos_attn_params* params, float* out);
+/* The same with the rows stored in out_dtype (LOGOS_F32, LOGOS_BF16, LOGOS_F16): a 16-bit `out` is the A operand
+ * of the W_O projection after it (logos_project), with no conversion pass between them.  DH = 64. */
+int logos_decode_step_int8_to(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new,
+                              const void* v_new, int8_t* k_cache, int8_t* v_cache, const float* k_scale,
+                              const float* v_scale, const int32_t* len, int B, int H, int S_max, int DH,
+                              const logos_attn_params* params, int out_dtype, void* out);
 
 /* One whole decode step with HOST buffers for the per-step data: copies q, q_prev,
  * k_new, v_new (FP16 [B][H][DH]) and len (int32 [B], the length AFTER the append)
@@ -347,6 +353,15 @@ int logos_project(logos_ctx* ctx, int dtype, int out_dtype, const void* A, const
  *   never exists in memory. */
 int logos_project_heads(logos_ctx* ctx, int dtype, int out_dtype, const void* head_out, const void* Wt_o,
                         const void* residual, void* C, int B, int S, int H, int N);
+
+/* The LayerNorm in front of a layer's projections (layernorm_kernel, cuda/VedicGEMM.cu:157-199; per layer at
+ * cuda/ModelGPU.cu:772): Y = gamma (X - mean) / sqrt(var + eps) + beta per row, biased variance, fp32 arithmetic,
+ * X and Y [rows][D] in one 16-bit dtype, gamma and beta fp32 [D].  D a multiple of 8, at most 2048; 16-byte
+ * aligned.  It belongs to the layer stack around the attention, not to the attention path: it is here because
+ * a decode step is a chain of small kernels, and this one lets the projection after it start at once (with
+ * LOGOS_OPT_PROJECT_OVERLAP it also starts under the kernel before it; gamma and beta count as weights). */
+int logos_layer_norm(logos_ctx* ctx, int dtype, const void* X, const float* gamma, const float* beta, void* Y,
+                     int rows, int D, float eps);
 
 /* INT8 -> BF16 / FP16: logos_kv_dequantize's fp32 product rounded once to the 16-bit type; tensors of a
  * multiple of 16 values, 16-byte aligned.  (A 16-bit attention over K and V that went through the cache.) */

@@ -222,10 +222,13 @@ int kv_dequantize(logos_ctx*, const int8_t*, int64_t, const float*, float*, int6
 // pos_bias is added to every pos[b]: -1 appends at len - 1 when `pos` is the length after the append
 int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const float*,
               const float*, const int32_t* pos, int, int, int, int, int pos_bias = 0);
+// out_dtype: the type of the rows written to `out` without peers (LOGOS_F32, or 16 bits for the projection after it)
 int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
                 const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
-                float*, const PeerEpilogue* peer = nullptr, bool follows_append = false);
+                float*, const PeerEpilogue* peer = nullptr, bool follows_append = false, int out_dtype = LOGOS_F32);
 size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
+int layer_norm(logos_ctx*, int dtype, const void* X, const float* gamma, const float* beta, void* Y, int rows, int D,
+               float eps);
 int attention_simt(logos_ctx*, int in_dtype, int out_dtype, const void* Q, const void* K,
                    const void* V, void* O, int B, int H, int S, int DH,
                    const logos_attn_params*, const logos_strides* in = nullptr, const logos_strides* out = nullptr);

@@ -49,7 +49,8 @@ struct DecodeArgs {
     const float* k_scale;
     const float* v_scale;
     const int32_t* len;
-    float* out;
+    float* out;            // without peers: [BH][64] in out_dtype
+    int out_dtype;
     float* partials;       // [BH][splits][paths][kPartial]
     unsigned int* counters;  // [BH], zero between launches
     int H, S_max, chunk;
@@ -65,7 +66,10 @@ struct DecodeArgs {
 __device__ __forceinline__ void emit_row(const DecodeArgs& a, int bh, int tid, float value) {
     if (tid >= kDH) return;
     if (a.peer.world == 0) {
-        a.out[(int64_t)bh * kDH + tid] = value;
+        const int64_t at = (int64_t)bh * kDH + tid;
+        if (a.out_dtype == LOGOS_F32) a.out[at] = value;
+        else if (a.out_dtype == LOGOS_BF16) reinterpret_cast<__nv_bfloat16*>(a.out)[at] = __float2bfloat16_rn(value);
+        else reinterpret_cast<__half*>(a.out)[at] = __float2half_rn(value);
         return;
     }
     const unsigned step = *a.peer.step;
@@ -625,6 +629,9 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     extern __shared__ float dyn[];
     float* p_ns = dyn;                 // [t_max]
     float* p_std = dyn + t_max;        // [t_max] when BLEND
+    // the kernel after this one may start at once, if it was launched to overlap (the W_O projection of a decode
+    // step then fetches its weights while the rows are still being computed; it waits before it reads them)
+    grid_release_dependents();
     __shared__ float red[kWarps];
     __shared__ float red_acc[kWarps][kDH];
 
@@ -786,7 +793,9 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH) {
 int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
                 const int8_t* v_cache, const float* k_scale, const float* v_scale,
                 const int32_t* len, int B, int H, int S_max, int DH,
-                const logos_attn_params* p, float* out, const PeerEpilogue* peer, bool follows_append) {
+                const logos_attn_params* p, float* out, const PeerEpilogue* peer, bool follows_append, int out_dtype) {
+    if (!dtype_ok(out_dtype) || (out_dtype != LOGOS_F32 && (peer || DH != kDH)))
+        return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: 16-bit rows are for DH = 64 without peers");
     if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || (!out && !peer) || !p || B <= 0 ||
         H <= 0 || S_max <= 0)
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: bad pointer or extent");
@@ -807,7 +816,7 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
     a.q_prev = (const __half*)q_prev;
     a.k_cache = k_cache; a.v_cache = v_cache;
     a.k_scale = k_scale; a.v_scale = v_scale;
-    a.len = len; a.out = out;
+    a.len = len; a.out = out; a.out_dtype = out_dtype;
     a.H = H; a.S_max = S_max;
     a.scale = p->scale;
     a.window = p->window; a.stride = p->stride;
@@ -972,7 +981,7 @@ extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const
     a.q = (const __half*)q; a.q_prev = (const __half*)q_prev;
     a.k_cache = k_cache; a.v_cache = v_cache;
     a.k_scale = k_scale; a.v_scale = v_scale;
-    a.len = len; a.out = out;
+    a.len = len; a.out = out; a.out_dtype = LOGOS_F32;
     a.H = H; a.S_max = S_max; a.chunk = chunk;
     a.scale = p->scale; a.window = 0; a.stride = 0;
     a.eta = ns_any ? p->ns_eta : 0.0f;

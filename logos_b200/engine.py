@@ -129,6 +129,15 @@ class Engine:
             return (block, ka, va) if absmax else block
         return (Q, K, V, ka, va) if absmax else (Q, K, V)
 
+    def layer_norm(self, X, gamma, beta, eps=1e-5):
+        """X [rows, D] 16-bit, gamma / beta fp32 [D] -> LayerNorm(X) in X's dtype (logos_layer_norm)."""
+        rows, D = X.shape
+        assert X.is_contiguous() and gamma.dtype == torch.float32 and beta.dtype == torch.float32
+        Y = torch.empty_like(X)
+        self._check(self.lib.logos_layer_norm(self.h, _DT[X.dtype], _ptr(X), _ptr(gamma), _ptr(beta), _ptr(Y), rows, D,
+                                             float(eps)))
+        return Y
+
     def project(self, A, Wt, residual=None, out_dtype=None, out=None):
         """A: [M, K] 16-bit, Wt: [N, K] (K-major shadow of W [K, N]) -> A·W (+ residual) [M, N]."""
         M, K = A.shape
@@ -285,16 +294,22 @@ class Engine:
         return out
 
     def decode_step(self, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, lens, params: L.Params,
-                    out=None, comm: "Comm | None" = None):
+                    out=None, comm: "Comm | None" = None, out_dtype=torch.float32):
         """Append the new token at row lens-1 and decode, device tensors throughout.  With `comm` the
-        heads are this rank's share and `out` is the gathered [B, H_local * world, DH] tensor."""
+        heads are this rank's share and `out` is the gathered [B, H_local * world, DH] tensor.  Without it the
+        rows may be stored in a 16-bit out_dtype (the A operand of the projection that follows)."""
         B, H, S_max, DH = k_cache.shape
         if comm is None:
             if out is None:
-                out = torch.empty((B, H, DH), dtype=torch.float32, device=q.device)
-            self._check(self.lib.logos_decode_step_int8(
-                self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale),
-                _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
+                out = torch.empty((B, H, DH), dtype=out_dtype, device=q.device)
+            if out.dtype == torch.float32:
+                self._check(self.lib.logos_decode_step_int8(
+                    self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale),
+                    _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _ptr(out)))
+            else:
+                self._check(self.lib.logos_decode_step_int8_to(
+                    self.h, _ptr(q), _ptr(q_prev), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), _ptr(k_scale),
+                    _ptr(v_scale), _ptr(lens), B, H, S_max, DH, C.byref(params), _DT[out.dtype], _ptr(out)))
         else:
             if out is None:
                 out = torch.empty((B, H * comm.world, DH), dtype=torch.float32, device=q.device)

@@ -75,6 +75,8 @@ SIGNATURES = {
     "logos_decode_int8_collect": (_i, [_vp, _vp, _vp, _i, _i, _i]),
     "logos_decode_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
     "logos_decode_step_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _vp]),
+    "logos_decode_step_int8_to": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _PP, _i, _vp]),
+    "logos_layer_norm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, C.c_float]),
     "logos_decode_step_int8_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                           _PP, _vp]),
     "logos_comm_push": (_i, [_vp, _vp, _vp, _i, _i, _sz]),

@@ -90,6 +90,8 @@ class AttentionStack:
     # ---- pieces ------------------------------------------------------------------------------
     def _norm(self, X, l):
         # one kernel: 16-bit in and out, fp32 statistics inside
+        if self.cfg.d_model <= 2048 and self.cfg.d_model % 8 == 0:
+            return self.eng.layer_norm(X, self.ln_g[l], self.ln_b[l], 1e-5)
         return F.layer_norm(X, (self.cfg.d_model,), self.ln_g16[l], self.ln_b16[l], 1e-5)
 
     def _gather(self, local, shape_tail):
@@ -144,8 +146,8 @@ class AttentionStack:
             # the decode entry points take FP16: the projection's epilogue stores Q, K, V in that type
             q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True, out_f16=True).view(3, B, self.Hl, 64).unbind(0)
             kc, vc, ks, vs = self.cache.layer(l)
-            if self.world == 1:
-                o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params)
+            if self.world == 1:      # the rows come out in the projections' type
+                o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params, out_dtype=self.dtype)
             else:
                 o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params, comm=self.comm)
             self.q_prev[l].copy_(q)

@@ -267,3 +267,32 @@ def test_prefetch_depth_does_not_change_the_bits(engine):
         assert np.array_equal(x, y)
     with pytest.raises(L.LogosError):
         engine.set_option(L.OPT_DECODE_DEPTH, 3)
+
+
+@pytest.mark.parametrize("window,stride", [(0, 0), (64, 16)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_step_with_16_bit_rows(engine, dtype, window, stride):
+    """logos_decode_step_int8_to: the same step, the rows stored as the one rounding of the fp32 rows (dense and
+    sparse kernel); a 16-bit type with another head dimension is refused."""
+    B, H, S_max, DH = 3, 4, 700, 64
+    g = torch.Generator(device="cuda").manual_seed(17 + window)
+    kc = torch.randint(-127, 128, (B, H, S_max, DH), dtype=torch.int8, device="cuda", generator=g)
+    vc = torch.randint(-127, 128, (B, H, S_max, DH), dtype=torch.int8, device="cuda", generator=g)
+    ks = torch.rand((B, H), device="cuda", generator=g) + 0.5
+    vs = torch.rand((B, H), device="cuda", generator=g) + 0.5
+    q, qp, kn, vn = (torch.randn((B, H, DH), device="cuda", generator=g).half() for _ in range(4))
+    lens = torch.tensor([700, 65, 1], dtype=torch.int32, device="cuda")
+    p = L.Params.make(0.125, True, window, stride, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
+    engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
+    kc2, vc2 = kc.clone(), vc.clone()
+    want = engine.decode_step(q, qp, kn, vn, kc, vc, ks, vs, lens, p)
+    got = engine.decode_step(q, qp, kn, vn, kc2, vc2, ks, vs, lens, p, out_dtype=dtype)
+    engine.synchronize()
+    assert got.dtype == dtype and torch.equal(got, want.to(dtype))
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    z = torch.zeros((1, 1, 64, 32), dtype=torch.int8, device="cuda")
+    one = torch.ones((1, 1), device="cuda")
+    q32 = torch.zeros((1, 1, 32), dtype=torch.float16, device="cuda")
+    with pytest.raises(L.LogosError) as e:
+        engine.decode_step(q32, q32, q32, q32, z, z, one, one, torch.ones(1, dtype=torch.int32, device="cuda"), p, out_dtype=dtype)
+    assert e.value.status == L.ERR_UNSUPPORTED

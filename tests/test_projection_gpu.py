@@ -228,3 +228,27 @@ def test_wide_kernel_qkv_scatter_and_heads(engine):
     for a_, b_ in zip(outs, outs_n):
         assert torch.equal(a_, b_)
     assert torch.equal(y, y_n)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,D", [(32, 1024), (5, 264), (300, 2048), (1, 8)])
+def test_layer_norm_matches_the_fp32_formula(engine, dtype, rows, D):
+    """logos_layer_norm: biased variance in a second pass, fp32 arithmetic, one rounding to the 16-bit type
+    (layernorm_kernel, cuda/VedicGEMM.cu:157-199)."""
+    g = torch.Generator(device="cuda").manual_seed(rows * 3 + D)
+    X = (torch.randn((rows, D), device="cuda", generator=g) * 3.0 + 0.5).to(dtype)
+    gamma = torch.randn((D,), device="cuda", generator=g)
+    beta = torch.randn((D,), device="cuda", generator=g)
+    for overlap in (0, 1):
+        engine.set_option(L.OPT_PROJECT_OVERLAP, overlap)
+        try:
+            Y = engine.layer_norm(X, gamma, beta, 1e-5)
+        finally:
+            engine.set_option(L.OPT_PROJECT_OVERLAP, 0)
+        engine.synchronize()
+        x = X.double()
+        mean = x.mean(dim=1, keepdim=True)
+        var = ((x - mean) ** 2).mean(dim=1, keepdim=True)
+        want = (gamma.double() * ((x - mean) / torch.sqrt(var + 1e-5)) + beta.double()).float()
+        ulp = want.abs() * (2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11) + 1e-4
+        assert bool(((Y.float() - want).abs() <= ulp).all()), float((Y.float() - want).abs().max())
