@@ -657,6 +657,8 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     const int8_t* vbase = a.v_cache + (int64_t)bh * a.S_max * kDH + part * 16;
     float qn[16], qs[BLEND ? 16 : 1];
     load_query<BLEND>(a, bh, pos, part, qn, qs);
+    // launched to overlap the append kernel before it (as the dense kernel is): the cache is read from here on
+    grid_wait_for_earlier();
 
     for (int t0 = warp * kRowsPerWarp; t0 < T; t0 += kRowsPerIter * kUnroll) {
         uint4 w[kUnroll];
@@ -847,8 +849,12 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
             else LOGOS_CUDA_TRY(ctx, cudaFuncSetAttribute(decode_sparse_kernel<false>,
                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         }
-        if (blend) decode_sparse_kernel<true><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
-        else       decode_sparse_kernel<false><<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
+        auto* sparse = blend ? decode_sparse_kernel<true> : decode_sparse_kernel<false>;
+        if (follows_append) {      // the kernel before this one on the stream is the engine's append of row len - 1
+            LOGOS_CUDA_TRY(ctx, launch_overlapped(sparse, dim3(BH), dim3(kThreads), smem, ctx->stream, a, t_max));
+        } else {
+            sparse<<<BH, kThreads, smem, ctx->stream>>>(a, t_max);
+        }
         LOGOS_LAUNCH_CHECK(ctx, "decode_sparse_kernel");
         return LOGOS_OK;
     }

@@ -106,14 +106,16 @@ class Engine:
         return out
 
     # ---- projections -----------------------------------------------------------
-    def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False, as_block=False, out_f16=False):
+    def qkv_project(self, X, Wt_qkv, B, S, H, absmax=False, as_block=False, out_f16=False, out=None):
         """X: [B*S, D] 16-bit; Wt_qkv: [3*H*64, D] (K-major shadow of the stacked W_Q | W_K | W_V) ->
         Q, K, V [B, H, S, 64] (three slices of one block, so that they can be converted or moved as one) and,
         with absmax, the tables max|K|, max|V| [B, H] for the quantiser.  out_f16: Q, K, V come out as FP16
         whatever X is (LOGOS_OPT_QKV_OUT_F16: what the decode entry points take)."""
         D = X.shape[1]
         assert X.is_contiguous() and Wt_qkv.is_contiguous() and Wt_qkv.shape == (3 * H * 64, D) and X.shape[0] == B * S
-        block = torch.empty((3, B, H, S, 64), dtype=torch.float16 if out_f16 else X.dtype, device=X.device)
+        want = torch.float16 if out_f16 else X.dtype
+        block = out if out is not None else torch.empty((3, B, H, S, 64), dtype=want, device=X.device)
+        assert block.shape == (3, B, H, S, 64) and block.dtype == want and block.is_contiguous()
         Q, K, V = block.unbind(0)
         ka = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None
         va = torch.empty((B, H), dtype=torch.float32, device=X.device) if absmax else None

@@ -79,6 +79,8 @@ class AttentionStack:
         self.ln_g16, self.ln_b16 = self.ln_g.to(dtype), self.ln_b.to(dtype)
         self.cache = KVCache(cfg.num_layers, batch, self.Hl, cfg.max_seq_len, 64, device=self.embed.device)
         self.q_prev = torch.zeros((cfg.num_layers, batch, self.Hl, 64), dtype=torch.float16, device=self.embed.device)
+        # a decode step's Q, K, V of every layer: the queries become q_prev in one copy at the end of the step
+        self.qkv_step = torch.empty((cfg.num_layers, 3, batch, self.Hl, 1, 64), dtype=torch.float16, device=self.embed.device)
         self.batch = batch
         engine.reserve(engine.decode_workspace_bytes(batch, self.Hl, cfg.max_seq_len, 64))
         ns = cfg.navier_stokes
@@ -144,17 +146,19 @@ class AttentionStack:
         for l in range(cfg.num_layers):
             xn = self._norm(x, l)
             # the decode entry points take FP16: the projection's epilogue stores Q, K, V in that type
-            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True, out_f16=True).view(3, B, self.Hl, 64).unbind(0)
+            q, k, v = eng.qkv_project(xn, self.Wt_qkv[l], B, 1, self.Hl, as_block=True, out_f16=True,
+                                      out=self.qkv_step[l]).view(3, B, self.Hl, 64).unbind(0)
             kc, vc, ks, vs = self.cache.layer(l)
             if self.world == 1:      # the rows come out in the projections' type
                 o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params, out_dtype=self.dtype)
             else:
                 o = eng.decode_step(q, self.q_prev[l], k, v, kc, vc, ks, vs, lens, self.params, comm=self.comm)
-            self.q_prev[l].copy_(q)
             a = o.view(B, cfg.num_heads * 64).to(self.dtype)
             y = eng.project(a, self.Wt_o[l])
             x = eng.project(y, self.Wt_proj[l], residual=x)
-        return eng.project(x, self.Wt_lm, out_dtype=torch.float32)
+        logits = eng.project(x, self.Wt_lm, out_dtype=torch.float32)
+        self.q_prev.copy_(self.qkv_step[:, 0, :, :, 0])
+        return logits
 
 
     def capture_decode(self):
