@@ -267,7 +267,8 @@ size_t logos_decode_workspace_bytes(int B, int H, int S_max, int DH);
 /* One whole decode step on device buffers: the new token's K and V rows (FP16 [B][H][DH]) are
  * quantised into row len[b]-1 of the caches (logos_kv_append with pos = len - 1), then
  * logos_decode_int8 runs over rows [0, len[b]).  len is the length AFTER the append.  Two
- * launches, nothing else; this is the per-layer body of an incremental generate loop, which the
+ * launches, nothing else (one with a window at DH = 64: that kernel quantises the new rows itself, with the
+ * same arithmetic); this is the per-layer body of an incremental generate loop, which the
  * reference does not have (cuda/train_gpu.cu:2037-2046 re-runs the whole forward per token). */
 int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new,
                            const void* v_new, int8_t* k_cache, int8_t* v_cache, const float* k_scale,

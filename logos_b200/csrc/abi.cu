@@ -552,6 +552,20 @@ int logos_decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const i
     return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out);
 }
 
+// append + decode on device buffers.  The window kernel quantises the new rows itself (one launch); the dense kernel
+// follows an append kernel and is launched to overlap it.
+static int decode_step(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new, const void* v_new,
+                       int8_t* k_cache, int8_t* v_cache, const float* k_scale, const float* v_scale, const int32_t* len,
+                       int B, int H, int S_max, int DH, const logos_attn_params* params, int out_dtype, void* out) {
+    if (k_new && v_new && logos::decode_appends_itself(params, DH))
+        return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params,
+                                  static_cast<float*>(out), nullptr, /*follows_append*/ false, out_dtype, k_new, v_new);
+    int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, -1);
+    if (rc != LOGOS_OK) return rc;
+    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params,
+                              static_cast<float*>(out), nullptr, /*follows_append*/ true, out_dtype);
+}
+
 int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, const void* k_new, const void* v_new,
                            int8_t* k_cache, int8_t* v_cache, const float* k_scale, const float* v_scale,
                            const int32_t* len, int B, int H, int S_max, int DH, const logos_attn_params* params,
@@ -559,10 +573,8 @@ int logos_decode_step_int8(logos_ctx* ctx, const void* q, const void* q_prev, co
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
     if (!params_ok(params))
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step: bad parameter block");
-    int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, -1);
-    if (rc != LOGOS_OK) return rc;
-    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params, out,
-                              nullptr, /*follows_append*/ true);
+    return decode_step(ctx, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params,
+                       LOGOS_F32, out);
 }
 
 int logos_layer_norm(logos_ctx* ctx, int dtype, const void* X, const float* gamma, const float* beta, void* Y,
@@ -578,10 +590,8 @@ int logos_decode_step_int8_to(logos_ctx* ctx, const void* q, const void* q_prev,
     if (!ctx) return LOGOS_ERR_INVALID_ARG;
     if (!params_ok(params))
         return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step: bad parameter block");
-    int rc = logos::kv_append(ctx, LOGOS_F16, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, -1);
-    if (rc != LOGOS_OK) return rc;
-    return logos::decode_int8(ctx, q, q_prev, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params,
-                              static_cast<float*>(out), nullptr, /*follows_append*/ true, out_dtype);
+    return decode_step(ctx, q, q_prev, k_new, v_new, k_cache, v_cache, k_scale, v_scale, len, B, H, S_max, DH, params,
+                       out_dtype, out);
 }
 
 int logos_decode_step_int8_gather(logos_ctx* ctx, logos_comm* comm, const void* q, const void* q_prev,

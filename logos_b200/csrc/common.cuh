@@ -225,7 +225,10 @@ int kv_append(logos_ctx*, int, const void*, const void*, int8_t*, int8_t*, const
 // out_dtype: the type of the rows written to `out` without peers (LOGOS_F32, or 16 bits for the projection after it)
 int decode_int8(logos_ctx*, const void*, const void*, const int8_t*, const int8_t*, const float*,
                 const float*, const int32_t*, int, int, int, int, const logos_attn_params*,
-                float*, const PeerEpilogue* peer = nullptr, bool follows_append = false, int out_dtype = LOGOS_F32);
+                float*, const PeerEpilogue* peer = nullptr, bool follows_append = false, int out_dtype = LOGOS_F32,
+                const void* append_k = nullptr, const void* append_v = nullptr);
+// true when decode_int8 takes the new token's rows itself (append_k / append_v): the window kernel at DH = 64
+bool decode_appends_itself(const logos_attn_params* p, int DH);
 size_t decode_workspace_bytes(int B, int H, int S_max, int DH);
 int layer_norm(logos_ctx*, int dtype, const void* X, const float* gamma, const float* beta, void* Y, int rows, int D,
                float eps);

@@ -57,6 +57,12 @@ struct DecodeArgs {
     float scale, eta, nu, alpha;
     int diffuse_mode, window, stride;
     PeerEpilogue peer;     // world == 0: rows go to `out`
+    // Sparse kernel only: the new token's K and V rows (FP16 [BH][64]), quantised into row len - 1 of the caches by
+    // the kernel itself before it reads them (the work of append_kernel, csrc/nikhilam.cu); null: nothing to append.
+    const __half* k_new;
+    const __half* v_new;
+    int8_t* k_cache_w;
+    int8_t* v_cache_w;
 };
 
 // The finished row of pair bh (thread d < 64 holds channel d); called by every thread of the CTA.
@@ -632,6 +638,7 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     // the kernel after this one may start at once, if it was launched to overlap (the W_O projection of a decode
     // step then fetches its weights while the rows are still being computed; it waits before it reads them)
     grid_release_dependents();
+    grid_wait_for_earlier();           // after an append kernel it is launched to overlap that (only the launch does)
     __shared__ float red[kWarps];
     __shared__ float red_acc[kWarps][kDH];
 
@@ -642,6 +649,27 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     const int pos = len - 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row_in_warp = lane >> 2, part = lane & 3;
+    // The new token's rows: quantised with the tensors' stored scales exactly as append_kernel does (same division,
+    // clamp and rounding; a row index outside the cache is rejected, not written), kept in shared memory for this
+    // CTA's own reads -- the streaming loads below may not see a store of the same kernel.
+    __shared__ __align__(16) int8_t new_rows[2][kDH];
+    int pos_new = -1;
+    if (a.k_new) {
+        const int row = a.len[b] - 1;
+        if (row >= 0 && row < a.S_max) {
+            pos_new = row;
+            if (tid < 2 * kDH) {
+                const int which = tid / kDH, d = tid - which * kDH;
+                const float den = __fadd_rn((which ? a.v_scale : a.k_scale)[bh], 1e-8f);
+                float x = __half2float((which ? a.v_new : a.k_new)[(int64_t)bh * kDH + d]);
+                x = fminf(fmaxf(__fdiv_rn(x, den), -127.0f), 127.0f);
+                const int8_t v8 = (int8_t)__float2int_rn(x);
+                new_rows[which][d] = v8;
+                (which ? a.v_cache_w : a.k_cache_w)[((int64_t)bh * a.S_max + row) * kDH + d] = v8;
+            }
+        }
+        __syncthreads();
+    }
     if (len == 0) {
         emit_row(a, bh, tid, 0.0f);
         return;
@@ -655,17 +683,22 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
 
     const int8_t* kbase = a.k_cache + (int64_t)bh * a.S_max * kDH + part * 16;
     const int8_t* vbase = a.v_cache + (int64_t)bh * a.S_max * kDH + part * 16;
+    // this lane's 16 bytes of cache row j: the row appended by this kernel comes from shared memory
+    auto k_row = [&](int j) {
+        return j == pos_new ? *reinterpret_cast<const uint4*>(&new_rows[0][part * 16]) : ld_stream(kbase + (int64_t)j * kDH);
+    };
+    auto v_row = [&](int j) {
+        return j == pos_new ? *reinterpret_cast<const uint4*>(&new_rows[1][part * 16]) : ld_stream(vbase + (int64_t)j * kDH);
+    };
     float qn[16], qs[BLEND ? 16 : 1];
     load_query<BLEND>(a, bh, pos, part, qn, qs);
-    // launched to overlap the append kernel before it (as the dense kernel is): the cache is read from here on
-    grid_wait_for_earlier();
 
     for (int t0 = warp * kRowsPerWarp; t0 < T; t0 += kRowsPerIter * kUnroll) {
         uint4 w[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             int t = t0 + u * kRowsPerIter + row_in_warp;
-            w[u] = (t < T) ? ld_stream(kbase + (int64_t)key_of(t) * kDH) : make_uint4(0, 0, 0, 0);
+            w[u] = (t < T) ? k_row(key_of(t)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -717,7 +750,7 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
     const int mode = a.diffuse_mode;
     for (int t = warp * kRowsPerWarp + row_in_warp; t < T; t += kRowsPerIter) {
         int j = key_of(t);
-        uint4 wc = ld_stream(vbase + (int64_t)j * kDH);
+        uint4 wc = v_row(j);
         float p = p_ns[t];
         if (mode == LOGOS_DIFFUSE_NONE) {
             axpy16(wc, p, acc);
@@ -726,13 +759,13 @@ decode_sparse_kernel(const DecodeArgs a, int t_max) {
             // Vs_j = (1-nu) V_j + nu/2 (V_{j-1}+V_{j+1}) (include/Attention.hpp:173-181),
             // neighbours clamped to [0, len-1]
             int jl = j > 0 ? j - 1 : 0;
-            uint4 wl = ld_stream(vbase + (int64_t)jl * kDH);
+            uint4 wl = v_row(jl);
             if (mode == LOGOS_DIFFUSE_CAUSAL) {
                 axpy16(wc, p * (1.0f - a.nu), acc);
                 axpy16(wl, p * a.nu, acc);
             } else {
                 int jr = j < len - 1 ? j + 1 : len - 1;
-                uint4 wr = ld_stream(vbase + (int64_t)jr * kDH);
+                uint4 wr = v_row(jr);
                 axpy16(wc, p * (1.0f - a.nu), acc);
                 axpy16(wl, p * 0.5f * a.nu, acc);
                 axpy16(wr, p * 0.5f * a.nu, acc);
@@ -792,10 +825,15 @@ size_t decode_workspace_bytes(int B, int H, int S_max, int DH) {
     return kCounterBytes + (size_t)B * H * splits * 2 * kPartial * sizeof(float);
 }
 
+bool decode_appends_itself(const logos_attn_params* p, int DH) { return p->window > 0 && DH == kDH; }
+
 int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t* k_cache,
                 const int8_t* v_cache, const float* k_scale, const float* v_scale,
                 const int32_t* len, int B, int H, int S_max, int DH,
-                const logos_attn_params* p, float* out, const PeerEpilogue* peer, bool follows_append, int out_dtype) {
+                const logos_attn_params* p, float* out, const PeerEpilogue* peer, bool follows_append, int out_dtype,
+                const void* append_k, const void* append_v) {
+    if ((append_k || append_v) && (!append_k || !append_v || !p || !decode_appends_itself(p, DH)))
+        return fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_int8: rows to append need both tensors and the window kernel");
     if (!dtype_ok(out_dtype) || (out_dtype != LOGOS_F32 && (peer || DH != kDH)))
         return fail(ctx, LOGOS_ERR_UNSUPPORTED, "decode_int8: 16-bit rows are for DH = 64 without peers");
     if (!q || !k_cache || !v_cache || !k_scale || !v_scale || !len || (!out && !peer) || !p || B <= 0 ||
@@ -819,6 +857,8 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
     a.k_cache = k_cache; a.v_cache = v_cache;
     a.k_scale = k_scale; a.v_scale = v_scale;
     a.len = len; a.out = out; a.out_dtype = out_dtype;
+    a.k_new = static_cast<const __half*>(append_k); a.v_new = static_cast<const __half*>(append_v);
+    a.k_cache_w = const_cast<int8_t*>(k_cache); a.v_cache_w = const_cast<int8_t*>(v_cache);
     a.H = H; a.S_max = S_max;
     a.scale = p->scale;
     a.window = p->window; a.stride = p->stride;
@@ -850,6 +890,8 @@ int decode_int8(logos_ctx* ctx, const void* q, const void* q_prev, const int8_t*
                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         }
         auto* sparse = blend ? decode_sparse_kernel<true> : decode_sparse_kernel<false>;
+        // Measured and dropped: launching it to overlap the projection before it in a decode step (its 512 waiting
+        // CTAs then sit on the SMs under that projection: 0.54 instead of 0.52 ms per 16-layer step).
         if (follows_append) {      // the kernel before this one on the stream is the engine's append of row len - 1
             LOGOS_CUDA_TRY(ctx, launch_overlapped(sparse, dim3(BH), dim3(kThreads), smem, ctx->stream, a, t_max));
         } else {
@@ -988,6 +1030,7 @@ extern "C" int logos_decode_int8_noalloc(void* cuda_stream, const void* q, const
     a.k_cache = k_cache; a.v_cache = v_cache;
     a.k_scale = k_scale; a.v_scale = v_scale;
     a.len = len; a.out = out; a.out_dtype = LOGOS_F32;
+    a.k_new = nullptr; a.v_new = nullptr; a.k_cache_w = nullptr; a.v_cache_w = nullptr;
     a.H = H; a.S_max = S_max; a.chunk = chunk;
     a.scale = p->scale; a.window = 0; a.stride = 0;
     a.eta = ns_any ? p->ns_eta : 0.0f;

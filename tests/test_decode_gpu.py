@@ -296,3 +296,28 @@ def test_decode_step_with_16_bit_rows(engine, dtype, window, stride):
     with pytest.raises(L.LogosError) as e:
         engine.decode_step(q32, q32, q32, q32, z, z, one, one, torch.ones(1, dtype=torch.int32, device="cuda"), p, out_dtype=dtype)
     assert e.value.status == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("alpha,mode", [(1.0, L.DIFFUSE_CAUSAL), (0.4, L.DIFFUSE_CENTRAL), (1.0, L.DIFFUSE_NONE)])
+def test_window_step_appends_inside_the_decode_kernel(engine, alpha, mode):
+    """With a window the step is one kernel that quantises the new rows itself: the cache bytes and the rows are those
+    of logos_kv_append followed by logos_decode_int8, also at position 0, at the last row of the cache, for a
+    sequence shorter than the window and for a length outside the cache (rejected, nothing written)."""
+    B, H, S_max, DH = 6, 3, 400, 64
+    g = torch.Generator(device="cuda").manual_seed(23 + int(alpha * 10) + mode)
+    kc = torch.randint(-127, 128, (B, H, S_max, DH), dtype=torch.int8, device="cuda", generator=g)
+    vc = torch.randint(-127, 128, (B, H, S_max, DH), dtype=torch.int8, device="cuda", generator=g)
+    ks = torch.rand((B, H), device="cuda", generator=g) * 0.05 + 0.01
+    vs = torch.rand((B, H), device="cuda", generator=g) * 0.05 + 0.01
+    q, qp = (torch.randn((B, H, DH), device="cuda", generator=g).half() for _ in range(2))
+    kn, vn = (torch.randn((B, H, DH), device="cuda", generator=g).half() * 3.0 for _ in range(2))   # some values saturate
+    lens = torch.tensor([400, 1, 2, 66, 200, 401], dtype=torch.int32, device="cuda")
+    p = L.Params.make(0.125, True, 64, 16, 0.1, 0.05, alpha, mode)
+    engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
+    kc2, vc2 = kc.clone(), vc.clone()
+    got = engine.decode_step(q, qp, kn, vn, kc, vc, ks, vs, lens, p)
+    engine.kv_append(kn, vn, kc2, vc2, ks, vs, lens - 1)
+    want = engine.decode_int8(q, qp, kc2, vc2, ks, vs, lens, p)
+    engine.synchronize()
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    assert torch.equal(got, want)
