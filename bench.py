@@ -651,6 +651,30 @@ def run_ours(args) -> None:
         finish()
         return
 
+    if args.workload == "mma":
+        # what one tcgen05.mma of the attention kernels' shapes costs a CTA that does nothing else
+        # (logos_selftest_umma, timing modes): 32 x (4 | 8 | 8) MMAs back to back, clock cycles on the SM
+        import torch
+        from logos_b200 import lib as L
+        res = {}
+        for mode, n, name in ((0, 4, "ss_m128_n128_k16"), (1, 8, "ss_m128_n64_k16_b_mn_major"), (3, 8, "ts_m128_n64_k16")):
+            A = torch.zeros((128, 64 if mode == 0 else 128), device=dev, dtype=torch.bfloat16)
+            Bm = torch.zeros((128, 64), device=dev, dtype=torch.bfloat16)
+            D = torch.zeros((128, 128 if mode == 0 else 64), device=dev)
+            runs = []
+            for _ in range(7):
+                eng._check(eng.lib.logos_selftest_umma(eng.h, 16 + mode, L.BF16, A.data_ptr(), Bm.data_ptr(), D.data_ptr()))
+                eng.synchronize()
+                runs.append(float(D[0, 0]))
+            nominal = 128 * (128 if mode == 0 else 64) * 16 * 2 / 8192.0
+            res[name] = {"cycles_per_mma": sorted(runs)[3] / (32 * n), "cycles_at_8192_flop_per_clock": nominal}
+        if rank == 0:
+            print(json.dumps({"metric": "tcgen05_mma_cycles", "value": res["ss_m128_n128_k16"]["cycles_per_mma"], "unit": "cycles",
+                              "n_gpus": world, "higher_is_better": False, "vs_baseline": None, "dtype": "bf16",
+                              "data": "synthetic", "config": {"workload": "tcgen05_mma_back_to_back"}, "detail": res}))
+        finish()
+        return
+
     if args.workload == "stack":
         r = measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks)
         if rank == 0:
@@ -842,7 +866,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU legs and the reference's GPU kernels")
     ap.add_argument("--no-secondary", action="store_true", help="skip the prefill / window side measurements")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack", "qkv", "bwd"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "prefill8k", "window", "window_lm", "stack", "qkv", "bwd", "mma"],
                     help="decode is the benchmark; the others time one attention kernel alone (profiling)")
     ap.add_argument("--batch", type=int, default=B,
                     help="sequences in the batch; anything but the default is a profiling case, not the benchmark")

@@ -826,6 +826,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 //           status word is raised (a check of the time-out path that cannot hang)
 //   mode 3: as mode 1, but A is written by the threads into tensor memory (lane = row, two K
 //           elements per column) and read from there by the MMA (how the prefill kernel passes W)
+//   mode 16 + m (m = 0, 1, 3): the MMAs of mode m issued kSelftestReps times back to back into the same
+//           accumulator; D[0] receives the clock cycles from the first issue to the completion of the last (what
+//           one MMA of that shape costs a CTA that does nothing else); the rest of D is not meaningful
+constexpr int kSelftestReps = 32;
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      const unsigned short* __restrict__ a_rows, float* __restrict__ D, int mode, int fmt,
@@ -838,6 +842,8 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + offBar + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + offBar + 32);
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int reps = mode >= 16 ? kSelftestReps : 1;
+    mode &= 15;
 
     if (tid == 0) {
         mbar_init(bar_load, 1);
@@ -883,29 +889,35 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
     bool ok = mbar_wait(bar_load, 0, abort_flag, mode == 2 ? (1u << 14) : kSpinLimit);
     __syncthreads();
+    long long t_begin = 0;
     if (tid == 0 && ok) {
         tc_fence_after();
-        if (mode == 3) {
-            const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
+        t_begin = clock64();
+        for (int rp = 0; rp < reps; ++rp) {
+            if (mode == 3) {
+                const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                tc_mma_f16_ta(tmem, tmem + 64u + 8u * (uint32_t)k, smem_desc(sbase + offB + k * 2048), idesc,
-                              k > 0 ? 1u : 0u);
-        } else if (mode == 0) {
-            const uint32_t idesc = instr_desc(fmt, fmt, 0, 128);
+                for (int k = 0; k < 8; ++k)
+                    tc_mma_f16_ta(tmem, tmem + 64u + 8u * (uint32_t)k, smem_desc(sbase + offB + k * 2048), idesc,
+                                  (k > 0 || rp > 0) ? 1u : 0u);
+            } else if (mode == 0) {
+                const uint32_t idesc = instr_desc(fmt, fmt, 0, 128);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                tc_mma_f16(tmem, smem_desc(sbase + offA + k * 32), smem_desc(sbase + offB + k * 32), idesc, k > 0 ? 1u : 0u);
-        } else {
-            const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
+                for (int k = 0; k < 4; ++k)
+                    tc_mma_f16(tmem, smem_desc(sbase + offA + k * 32), smem_desc(sbase + offB + k * 32), idesc,
+                               (k > 0 || rp > 0) ? 1u : 0u);
+            } else {
+                const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                tc_mma_f16(tmem, smem_desc(sbase + offA + (k >> 2) * kTileBytes + (k & 3) * 32),
-                           smem_desc(sbase + offB + k * 2048), idesc, k > 0 ? 1u : 0u);
+                for (int k = 0; k < 8; ++k)
+                    tc_mma_f16(tmem, smem_desc(sbase + offA + (k >> 2) * kTileBytes + (k & 3) * 32),
+                               smem_desc(sbase + offB + k * 2048), idesc, (k > 0 || rp > 0) ? 1u : 0u);
+            }
         }
         tc_commit(bar_mma);
     }
     ok = ok && mbar_wait(bar_mma, 0, abort_flag);
+    const long long t_end = clock64();
     if (ok) {
         tc_fence_after();
         const uint32_t lane_addr = ((uint32_t)(warp * 32)) << 16;
@@ -920,6 +932,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
+    if (reps > 1 && ok && tid == 0) D[0] = (float)(t_end - t_begin);
     if (*abort_flag && tid == 0) atomicExch(status, 1);
     if (warp == 0) {
         tc_fence_after();
@@ -950,12 +963,14 @@ bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16, int row
 }  // namespace
 
 int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
-    if (!A || !B || !D || mode < 0 || mode > 3 || (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
+    const int base_mode = mode & 15;
+    if (!A || !B || !D || mode < 0 || mode > 19 || base_mode > 3 || (mode >= 16 && base_mode == 2) ||
+        (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "selftest: bad argument");
     const bool f16 = dtype == LOGOS_F16;
     CUtensorMap ma, mb;
     // modes 1 and 3 do not load A by TMA; its map then simply aliases B's
-    if (!make_map(&ma, mode == 0 ? A : B, 1, kBM, f16) || !make_map(&mb, B, 1, kBM, f16))
+    if (!make_map(&ma, base_mode == 0 ? A : B, 1, kBM, f16) || !make_map(&mb, B, 1, kBM, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "selftest: cuTensorMapEncodeTiled failed");
     const int smem = 3 * kTileBytes + 64 + 1024;
     if (int rc = ensure_smem_limit(ctx, umma_selftest_kernel, smem)) return rc;

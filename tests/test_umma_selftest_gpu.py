@@ -50,3 +50,19 @@ def test_pv_shape_weights_in_tmem_bf16(engine):
 
 def test_pv_shape_weights_in_tmem_f16(engine):
     _run(engine, 3, torch.float16)
+
+
+def test_timing_modes_report_a_plausible_cost(engine):
+    """mode 16 + m: 32 x the MMAs of mode m back to back, D[0] = clock cycles.  An MMA of these shapes cannot take
+    less than its flops at the tensor pipe's rate (32 or 64 cycles) and should stay within a few times that."""
+    for mode, n, floor in ((0, 4, 64.0), (1, 8, 32.0), (3, 8, 32.0)):
+        A = torch.zeros((128, 64 if mode == 0 else 128), device="cuda", dtype=torch.bfloat16)
+        B = torch.zeros((128, 64), device="cuda", dtype=torch.bfloat16)
+        D = torch.zeros((128, 128 if mode == 0 else 64), device="cuda")
+        rc = engine.lib.logos_selftest_umma(engine.h, 16 + mode, L.BF16, A.data_ptr(), B.data_ptr(), D.data_ptr())
+        assert rc == L.OK, engine.lib.logos_last_error(engine.h)
+        engine.synchronize()
+        per_mma = float(D[0, 0]) / (32 * n)
+        assert 0.9 * floor <= per_mma <= 8 * floor, (mode, per_mma)
+    with pytest.raises(L.LogosError):
+        engine._check(engine.lib.logos_selftest_umma(engine.h, 18, L.BF16, A.data_ptr(), B.data_ptr(), D.data_ptr()))
