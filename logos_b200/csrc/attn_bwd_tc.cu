@@ -125,8 +125,10 @@ bwd_tc_rows_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kRowsOffBar + RB_NUM * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = a.S, bh = blockIdx.y;
-    const int q0 = blockIdx.x * kBT, q_last = min(S, q0 + kBT) - 1;
+    // grid (B H, query blocks), the last query block first: under a causal mask it sees the most key tiles, and CTAs
+    // are handed out in this order, so the long ones start first and the short ones fill the end of the grid
+    const int S = a.S, bh = blockIdx.x;
+    const int q0 = (gridDim.y - 1 - blockIdx.y) * kBT, q_last = min(S, q0 + kBT) - 1;
     const int kt_end = (S + kBT - 1) / kBT;
     constexpr bool f16 = F16;
 
@@ -423,8 +425,9 @@ bwd_tc_keys_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kKeysOffBar + KB_NUM * 8 + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = a.S, bh = blockIdx.y;
-    const int k0 = blockIdx.x * kBT, k_last = min(S, k0 + kBT) - 1;
+    // grid (B H, key blocks), the first key block first: under a causal mask it is seen by the most query tiles
+    const int S = a.S, bh = blockIdx.x;
+    const int k0 = blockIdx.y * kBT, k_last = min(S, k0 + kBT) - 1;
     constexpr bool f16 = F16;
     // query tiles that can see these keys: from the diagonal on (causal); a pure window ends them early
     const int qt_begin = a.causal ? k0 / kBT : 0;
@@ -707,7 +710,7 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
     if (dtype != LOGOS_BF16 && dtype != LOGOS_F16)
         return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: operands are BF16 or FP16");
     if (DH != kBD) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: DH must be 64, got %d", DH);
-    if ((int64_t)B * H > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: B*H > 65535");
+    if ((S + kBT - 1) / kBT > 65535) return fail(ctx, LOGOS_ERR_UNSUPPORTED, "attention_bwd16: more than 65535 blocks of 128 tokens");
     if (!(p->scale > 0.0f)) return fail(ctx, LOGOS_ERR_INVALID_ARG, "attention_bwd16: scale must be positive");
     const void* ptrs[7] = {Q, K, V, dO, dQ, dK, dV};
     for (const void* q : ptrs)
@@ -747,7 +750,7 @@ int attention_bwd16(logos_ctx* ctx, int dtype, const void* Q, const void* K, con
     CUtensorMap mk, mg;
     if (!make_map_bwd(&mk, K, BH, S, f16) || !make_map_bwd(&mg, dO, BH, S, f16))
         return fail(ctx, LOGOS_ERR_CUDA, "attention_bwd16: cuTensorMapEncodeTiled failed");
-    dim3 grid((S + kBT - 1) / kBT, BH);
+    dim3 grid(BH, (S + kBT - 1) / kBT);
     auto run = [&](const void* Qx, const void* Vx) -> int {
         CUtensorMap mq, mv;
         if (!make_map_bwd(&mq, Qx, BH, S, f16) || !make_map_bwd(&mv, Vx, BH, S, f16))
