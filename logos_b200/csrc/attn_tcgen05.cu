@@ -49,6 +49,8 @@ namespace {
 
 using namespace tc;
 
+template <bool V> struct SkipDead { static constexpr bool value = V; };   // compile-time switch of the weight pass
+
 constexpr int kTiles = 2;             // query tiles per CTA (2: both share every K/V tile, one CTA per SM)
 constexpr int kCtasPerSm = kTiles == 1 ? 2 : 1;   // one tile per CTA: two CTAs share an SM and its 512 TMEM columns
 constexpr int kBQ = kBM * kTiles;     // query rows per CTA
@@ -117,7 +119,9 @@ struct TcArgs {
 // the weights: the converter warp mixes the landmark's V row with the row before it (mapVp: the same view
 // one row earlier) into V[j] + rho V[j-1] -- the same "everything divided by 1 - nu" units as the window
 // part -- and the row sum takes (1 + rho) p.
-template <bool DIFF, bool LM>
+// WIN: the launch has a window.  Only then does the weight pass carry its second copy that skips the 16-column chunks
+// no row of a warp sees; the causal instantiations are the straight-line code alone.
+template <bool DIFF, bool LM, bool WIN>
 __global__ void __launch_bounds__(kTcThreads, kCtasPerSm)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                   const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapKl,
@@ -604,6 +608,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             const int r_first = q0 + g * kBM;
             const bool edge = lm || (k0 + kBN - 1 > r_first) || (k0 + kBN > S) ||
                               (a.window > 0 && k0 < r_first + kBM - 1 - a.window);
+            // Chunks of 16 columns that no row of this warp sees (bit cb of `dead`) take no part in the maximum and get
+            // no exponentials -- under a window a row sees 65 of the 384 columns its item visits -- and only the chunks
+            // that some row sees in part are masked element by element.  The visible columns of a row are one range
+            // and both of its ends grow with the row, so the warp's first and last lane decide for the warp.
+            uint32_t dead = 0;
             if (edge) {
                 // visible columns of the row, relative to the tile's first key: [lo_rel, hi_rel]; in a landmark
                 // tile column c is key (k0 + c) * stride, visible when it lies strictly below the row's window
@@ -614,22 +623,48 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     hi_rel = (top < 0 ? -1 : top / a.stride) - k0;
                     lo_rel = -(1 << 30);
                 }
+                if (WIN) {
+                    const int hi_min = __shfl_sync(0xffffffffu, hi_rel, 0), hi_max = __shfl_sync(0xffffffffu, hi_rel, 31);
+                    const int lo_min = __shfl_sync(0xffffffffu, lo_rel, 0), lo_max = __shfl_sync(0xffffffffu, lo_rel, 31);
 #pragma unroll
-                for (int j = 0; j < kBN; ++j) s[j] = (j <= hi_rel && j >= lo_rel) ? s[j] : -INFINITY;
+                    for (int cb = 0; cb < kBN / 16; ++cb) {
+                        const int c_lo = 16 * cb, c_hi = 16 * cb + 15;
+                        if (c_lo > hi_max || c_hi < lo_min) {
+                            dead |= 1u << cb;
+                        } else if (c_hi > hi_min || c_lo < lo_max) {
+#pragma unroll
+                            for (int j = c_lo; j <= c_hi; ++j) s[j] = (j <= hi_rel && j >= lo_rel) ? s[j] : -INFINITY;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kBN; ++j) s[j] = (j <= hi_rel && j >= lo_rel) ? s[j] : -INFINITY;
+                }
             }
             float mxr;
             {
                 float mc[8];                            // three-input maxima, eight independent chains
+                if (WIN && dead) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) mc[q] = fmaxf(s[2 * q], s[2 * q + 1]);
+                    for (int q = 0; q < 8; ++q) mc[q] = -INFINITY;
 #pragma unroll
-                for (int j = 16; j < kBN; j += 16)
+                    for (int j = 0; j < kBN; j += 16) {
+                        if (dead & (1u << (j >> 4))) continue;
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) mc[q] = fmaxf(fmaxf(mc[q], s[j + 2 * q]), s[j + 2 * q + 1]);
+                        for (int q = 0; q < 8; ++q) mc[q] = fmaxf(fmaxf(mc[q], s[j + 2 * q]), s[j + 2 * q + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) mc[q] = fmaxf(s[2 * q], s[2 * q + 1]);
+#pragma unroll
+                    for (int j = 16; j < kBN; j += 16)
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) mc[q] = fmaxf(fmaxf(mc[q], s[j + 2 * q]), s[j + 2 * q + 1]);
+                }
                 mxr = fmaxf(fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3])), fmaxf(fmaxf(mc[4], mc[5]), fmaxf(mc[6], mc[7])));
             }
             const float mx = mxr * c;                 // c > 0
-            const float s_first = s[0] * c;           // the tile below needs it for its last column's stencil
+            const float s_first = (WIN && (dead & 1u)) ? -INFINITY : s[0] * c;   // the tile below needs it for its last column's stencil
             // move the reference maximum only when it would grow by more than the threshold (weights
             // stay below 2^9, well inside FP16); the decision is warp-wide because the O correction is
             // a warp-collective TMEM access
@@ -673,7 +708,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             // chunks of 16 keys, highest first (the stencil walks downwards); the exponentials of the
             // next chunk are issued before the current chunk's stencil, sum, pack and store, so that the
             // exponential unit and the arithmetic pipes of this warp work at the same time
-            auto expo16 = [&](int cb, float2 (&P)[9]) {                // p = 2^(c s - m) as pairs (key j, key j + 8)
+            // (the tiles with dead chunks run a second copy of this code that tests for them: the tests would cost
+            // the straight-line copy its overlap of exponentials and arithmetic)
+            auto expo16 = [&](auto skip, int cb, float2 (&P)[9]) {     // p = 2^(c s - m) as pairs (key j, key j + 8)
+                if (decltype(skip)::value && (dead & (1u << cb))) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) P[e] = make_float2(0.0f, 0.0f);
+                    return;
+                }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float2 tt = __ffma2_rn(make_float2(s[16 * cb + 2 * e], s[16 * cb + 2 * e + 1]), c2, nm2);
@@ -709,30 +751,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 }
                 tc_st8(tmem_P + 8 * cb, pk);
             };
-            {
+            auto all_chunks = [&](auto skip) {
                 float2 Pa[9], Pb[9];
-                expo16(7, Pa);
-                expo16(6, Pb);
+                expo16(skip, 7, Pa);
+                expo16(skip, 6, Pb);
                 if (!pv_done) {
                     // the weight columns are still being read by the previous O += W V until it is done
                     if (!mbar_wait(bar(B_PVDONE0 + g), (s_run - 1) & 1, abort_flag)) ok = false;
                     tc_fence_after();
                 }
                 store16(7, Pa);
-                expo16(5, Pa);
+                expo16(skip, 5, Pa);
                 store16(6, Pb);
-                expo16(4, Pb);
+                expo16(skip, 4, Pb);
                 store16(5, Pa);
-                expo16(3, Pa);
+                expo16(skip, 3, Pa);
                 store16(4, Pb);
-                expo16(2, Pb);
+                expo16(skip, 2, Pb);
                 store16(3, Pa);
-                expo16(1, Pa);
+                expo16(skip, 1, Pa);
                 store16(2, Pb);
-                expo16(0, Pb);
+                expo16(skip, 0, Pb);
                 store16(1, Pa);
                 store16(0, Pb);
-            }
+            };
+            if (WIN && dead) all_chunks(SkipDead<true>{}); else all_chunks(SkipDead<false>{});
             if (!ok) break;
             lsum2 = __fadd2_rn(lsum2, lsum2b);
             // a landmark's weight stands for V[j] + rho V[j-1]: it counts (1 + rho) times in the row sum
@@ -1056,15 +1099,19 @@ int attention_tc(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q, con
     a.BH = BH;
     a.n_items = a.n_qb * BH;
     dim3 grid(a.n_items < ctx->sm_count ? a.n_items : ctx->sm_count);   // persistent: one CTA per SM
-#define LOGOS_LAUNCH_TC(DIFF_, LM_)                                                                             \
+#define LOGOS_LAUNCH_TC(DIFF_, LM_, WIN_)                                                                       \
     do {                                                                                                        \
-        if (int rc = ensure_smem_limit(ctx, prefill_tc_kernel<DIFF_, LM_>, kSmemBytes)) return rc;              \
-        prefill_tc_kernel<DIFF_, LM_><<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mkl, mvl, mvp, a); \
+        auto* fn = prefill_tc_kernel<DIFF_, LM_, WIN_>;                                                         \
+        if (int rc = ensure_smem_limit(ctx, fn, kSmemBytes)) return rc;                                         \
+        fn<<<grid, kTcThreads, kSmemBytes, ctx->stream>>>(mq, mk, mv, mkl, mvl, mvp, a);                        \
     } while (0)
-    if (a.diffuse && lm_stride) LOGOS_LAUNCH_TC(true, true);
-    else if (a.diffuse) LOGOS_LAUNCH_TC(true, false);
-    else if (lm_stride) LOGOS_LAUNCH_TC(false, true);
-    else LOGOS_LAUNCH_TC(false, false);
+    const bool win = a.window > 0;
+    if (a.diffuse && lm_stride) LOGOS_LAUNCH_TC(true, true, true);
+    else if (a.diffuse && win) LOGOS_LAUNCH_TC(true, false, true);
+    else if (a.diffuse) LOGOS_LAUNCH_TC(true, false, false);
+    else if (lm_stride) LOGOS_LAUNCH_TC(false, true, true);
+    else if (win) LOGOS_LAUNCH_TC(false, false, true);
+    else LOGOS_LAUNCH_TC(false, false, false);
 #undef LOGOS_LAUNCH_TC
     LOGOS_LAUNCH_CHECK(ctx, "prefill_tc_kernel");
     return LOGOS_OK;
