@@ -657,16 +657,19 @@ def run_ours(args) -> None:
         import torch
         from logos_b200 import lib as L
         res = {}
-        for mode, n, name in ((0, 4, "ss_m128_n128_k16"), (1, 8, "ss_m128_n64_k16_b_mn_major"), (3, 8, "ts_m128_n64_k16")):
-            A = torch.zeros((128, 64 if mode == 0 else 128), device=dev, dtype=torch.bfloat16)
+        for mode, n, name in ((0, 4, "ss_m128_n128_k16"), (1, 8, "ss_m128_n64_k16_b_mn_major"), (3, 8, "ts_m128_n64_k16"),
+                              (32, 4, "ss_m128_n128_k16_elected_lane"), (33, 8, "ss_m128_n64_k16_b_mn_major_elected_lane"),
+                              (35, 8, "ts_m128_n64_k16_elected_lane")):
+            qk = (mode & 15) == 0
+            A = torch.zeros((128, 64 if qk else 128), device=dev, dtype=torch.bfloat16)
             Bm = torch.zeros((128, 64), device=dev, dtype=torch.bfloat16)
-            D = torch.zeros((128, 128 if mode == 0 else 64), device=dev)
+            D = torch.zeros((128, 128 if qk else 64), device=dev)
             runs = []
             for _ in range(7):
                 eng._check(eng.lib.logos_selftest_umma(eng.h, 16 + mode, L.BF16, A.data_ptr(), Bm.data_ptr(), D.data_ptr()))
                 eng.synchronize()
                 runs.append(float(D[0, 0]))
-            nominal = 128 * (128 if mode == 0 else 64) * 16 * 2 / 8192.0
+            nominal = 128 * (128 if qk else 64) * 16 * 2 / 8192.0
             res[name] = {"cycles_per_mma": sorted(runs)[3] / (32 * n), "cycles_at_8192_flop_per_clock": nominal}
         if rank == 0:
             print(json.dumps({"metric": "tcgen05_mma_cycles", "value": res["ss_m128_n128_k16"]["cycles_per_mma"], "unit": "cycles",

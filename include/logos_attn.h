@@ -213,6 +213,7 @@ int logos_prefill_fwd(logos_ctx* ctx, int in_dtype, int out_dtype, const void* Q
  *   mode 3: as mode 1 with A held in tensor memory (the way the prefill kernel passes W)
  *   mode 16 + m (m = 0, 1, 3): a timing run -- the MMAs of mode m (4, 8, 8 of them) issued 32 times back to back;
  *           D[0] receives the clock cycles they took, the rest of D is not meaningful
+ *   mode 48 + m: the same timing run with a whole warp running the issue loop and one elected lane issuing
  * D is fp32, row-major.  Check the result with logos_ctx_synchronize. */
 int logos_selftest_umma(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D);
 

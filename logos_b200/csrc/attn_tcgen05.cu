@@ -872,6 +872,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
 //   mode 16 + m (m = 0, 1, 3): the MMAs of mode m issued kSelftestReps times back to back into the same
 //           accumulator; D[0] receives the clock cycles from the first issue to the completion of the last (what
 //           one MMA of that shape costs a CTA that does nothing else); the rest of D is not meaningful
+//   mode 48 + m: the same with the whole first warp running the issue loop and one elected lane issuing (the form the
+//           kernels' issuing warps take) instead of a single thread in a divergent branch
 constexpr int kSelftestReps = 32;
 __global__ void __launch_bounds__(128, 1)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
@@ -886,6 +888,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + offBar + 32);
     const int tid = threadIdx.x, warp = tid >> 5;
     const int reps = mode >= 16 ? kSelftestReps : 1;
+    const bool uniform_issue = (mode & 32) != 0;     // the whole first warp runs the issue loop, one elected lane issues
     mode &= 15;
 
     if (tid == 0) {
@@ -933,10 +936,14 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     bool ok = mbar_wait(bar_load, 0, abort_flag, mode == 2 ? (1u << 14) : kSpinLimit);
     __syncthreads();
     long long t_begin = 0;
-    if (tid == 0 && ok) {
+    uint32_t elected = 0;
+    if (warp == 0) asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(elected));
+    const bool issuer = uniform_issue ? elected != 0 : tid == 0;
+    if ((uniform_issue ? warp == 0 : tid == 0) && ok) {
         tc_fence_after();
         t_begin = clock64();
         for (int rp = 0; rp < reps; ++rp) {
+            if (!issuer) continue;
             if (mode == 3) {
                 const uint32_t idesc = instr_desc(fmt, fmt, 1, 64);
 #pragma unroll
@@ -957,7 +964,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
                                smem_desc(sbase + offB + k * 2048), idesc, (k > 0 || rp > 0) ? 1u : 0u);
             }
         }
-        tc_commit(bar_mma);
+        if (issuer) tc_commit(bar_mma);
     }
     ok = ok && mbar_wait(bar_mma, 0, abort_flag);
     const long long t_end = clock64();
@@ -975,7 +982,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
     tc_fence_before();
     __syncthreads();
-    if (reps > 1 && ok && tid == 0) D[0] = (float)(t_end - t_begin);
+    if (reps > 1 && ok && issuer) D[0] = (float)(t_end - t_begin);
     if (*abort_flag && tid == 0) atomicExch(status, 1);
     if (warp == 0) {
         tc_fence_after();
@@ -1007,7 +1014,7 @@ bool make_map(CUtensorMap* m, const void* base, int BH, int S, bool f16, int row
 
 int umma_selftest(logos_ctx* ctx, int mode, int dtype, const void* A, const void* B, float* D) {
     const int base_mode = mode & 15;
-    if (!A || !B || !D || mode < 0 || mode > 19 || base_mode > 3 || (mode >= 16 && base_mode == 2) ||
+    if (!A || !B || !D || mode < 0 || mode > 51 || (mode & 32 && !(mode & 16)) || base_mode > 3 || (mode >= 16 && base_mode == 2) ||
         (dtype != LOGOS_BF16 && dtype != LOGOS_F16))
         return fail(ctx, LOGOS_ERR_INVALID_ARG, "selftest: bad argument");
     const bool f16 = dtype == LOGOS_F16;
