@@ -82,9 +82,9 @@ constexpr int kOffQ = 0;                                       // two buffers (w
 constexpr int kQBufBytes = 2 * kTiles * kTileBytes;
 constexpr int kOffK = kOffQ + 2 * kQBufBytes;                  // kStages tiles
 constexpr int kOffV = kOffK + kStages * kTileBytes;            // kStages tiles
-constexpr int kOffVP = kOffV + kStages * kTileBytes;           // one tile: the V[j-1] rows of a landmark tile (landmark kernels only)
-constexpr int kOffBar = kOffVP + kTileBytes;
-constexpr int kNumBars = 8 + 5 * kStages + 8 + 1;
+constexpr int kOffVP = kOffV + kStages * kTileBytes;           // two tiles in turn: the V[j-1] rows of a landmark tile (landmark kernels only)
+constexpr int kOffBar = kOffVP + 2 * kTileBytes;
+constexpr int kNumBars = 8 + 5 * kStages + 8 + 2;
 constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 64 + 1024; // + tmem slot/abort + alignment slack
 
 enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buffer
@@ -93,7 +93,7 @@ enum Bar { B_QLOAD0 = 0,                                   // two: one per Q buf
            B_KFULL0 = 8, B_KEMPTY0 = B_KFULL0 + kStages, B_VFULL0 = B_KEMPTY0 + kStages,     // kStages of each
            B_VEMPTY0 = B_VFULL0 + kStages, B_VREADY0 = B_VEMPTY0 + kStages,
            B_SFULL0 = B_VREADY0 + kStages, B_SFULL1, B_SEMPTY0, B_SEMPTY1, B_PFULL0, B_PFULL1, B_PVDONE0, B_PVDONE1,
-           B_VPEMPTY,                                      // the V[j-1] buffer has been mixed into its V tile
+           B_VPEMPTY0, B_VPEMPTY1,                         // a V[j-1] buffer has been mixed into its V tile
            B_NUM };
 static_assert(B_NUM <= kNumBars, "barrier count");
 
@@ -205,15 +205,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         if (LM && i >= n_win) tma_load_3d(sbase + kOffK + st * kTileBytes, &mapKl, 0, (i - n_win) * kBN, bh, bar(B_KFULL0 + st));
         else tma_load_3d(sbase + kOffK + st * kTileBytes, &mapK, 0, (jt_hi - i) * kBN, bh, bar(B_KFULL0 + st));
     };
-    int n_vp = 0;       // V[j-1] tiles requested so far (the buffer is single: wait until the last one was mixed)
+    // V[j-1] tiles requested so far.  Two buffers in turn: with one, the loads of a landmark tile could only start when
+    // the tile before it had been mixed, and their latency (strided gathers) was the period of a landmark tile.
+    int n_vp = 0;
     auto load_v_tile = [&](int i, int st) -> bool {
         if (LM && i >= n_win) {
             const int m0 = (i - n_win) * kBN;
             if (DIFF) {
-                if (n_vp > 0 && !mbar_wait(bar(B_VPEMPTY), (n_vp - 1) & 1, abort_flag)) return false;
+                const int vb = n_vp & 1;
+                if (n_vp >= 2 && !mbar_wait(bar(B_VPEMPTY0 + vb), ((n_vp >> 1) - 1) & 1, abort_flag)) return false;
                 ++n_vp;
                 mbar_expect_tx(bar(B_VFULL0 + st), 2 * kTileBytes);
-                tma_load_3d(sbase + kOffVP, &mapVp, 0, m0 - 1, bh, bar(B_VFULL0 + st));   // row -1 of the first tile: zeros
+                tma_load_3d(sbase + kOffVP + vb * kTileBytes, &mapVp, 0, m0 - 1, bh, bar(B_VFULL0 + st));   // row -1 of the first tile: zeros
             } else {
                 mbar_expect_tx(bar(B_VFULL0 + st), kTileBytes);
             }
@@ -244,7 +247,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             mbar_init(bar(B_PFULL0 + g), kBM);
             mbar_init(bar(B_PVDONE0 + g), 1);
         }
-        mbar_init(bar(B_VPEMPTY), kCvtThreads);
+        mbar_init(bar(B_VPEMPTY0), kCvtThreads);
+        mbar_init(bar(B_VPEMPTY1), kCvtThreads);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -349,7 +353,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
         } else if (!f16 || DIFF) {
             const int ct = tid - kCvtWarp * 32;
             const float rho_c = DIFF ? a.nu / (1.0f - a.nu) : 0.0f;
-            int nv = 0;
+            int nv = 0, n_vpc = 0;       // V tiles, V[j-1] tiles taken so far
             bool ok = true;
             for (int it = 0, t = item_at(0); ok && t < a.n_items; ++it, t = item_at(it)) {
                 set_item(t);
@@ -358,7 +362,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                     if (!mbar_wait(bar(B_VFULL0 + st), (nv / kStages) & 1, abort_flag)) { ok = false; break; }
                     unsigned char* vt = smem + kOffV + st * kTileBytes;
                     if (LM && DIFF && i >= n_win) {
-                        const unsigned char* vp = smem + kOffVP;
+                        const int vb = n_vpc & 1;
+                        const unsigned char* vp = smem + kOffVP + vb * kTileBytes;
                         const bool first_tile = i == n_win;          // its row 0 is key 0: V_s[0] = V[0]
 #pragma unroll 2
                         for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
@@ -382,7 +387,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                             }
                             *reinterpret_cast<uint4*>(vt + ch * 16) = v;
                         }
-                        mbar_arrive(bar(B_VPEMPTY));
+                        mbar_arrive(bar(B_VPEMPTY0 + vb));
+                        ++n_vpc;
                     } else if (!f16) {
 #pragma unroll 4
                         for (int q = 0; q < kTileBytes / 16 / kCvtThreads; ++q) {
@@ -828,7 +834,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                                 uint32_t w[4];
 #pragma unroll
                                 for (int e = 0; e < 4; ++e)
-                                    w[e] = f32_to_16(o[8 * j + 2 * e] * inv, f16) | (f32_to_16(o[8 * j + 2 * e + 1] * inv, f16) << 16);
+                                    w[e] = f32x2_to_16(o[8 * j + 2 * e] * inv, o[8 * j + 2 * e + 1] * inv, f16);
                                 w4[j] = make_uint4(w[0], w[1], w[2], w[3]);
                             }
 #pragma unroll

@@ -148,6 +148,13 @@ __host__ __device__ constexpr uint32_t instr_desc(int a_fmt, int b_fmt, int b_mn
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// two values as one word of the 16-bit type, x in the lower half: one packed conversion (two scalar ones go
+// through the XU pipe, four times slower)
+__device__ __forceinline__ uint32_t f32x2_to_16(float x, float y, bool f16) {
+    if (f16) { __half2 h = __floats2half2_rn(x, y); return *reinterpret_cast<uint32_t*>(&h); }
+    __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
 __device__ __forceinline__ uint32_t f32_to_16(float x, bool f16) {
     return f16 ? (uint32_t)__half_as_ushort(__float2half_rn(x))
                : (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
