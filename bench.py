@@ -351,14 +351,12 @@ def measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks, layers=1
     ev[1].record()
     barrier()
     prefill_ms = max_over_ranks(ev[0].elapsed_time(ev[1]))
-    graph, gids, glogits = st.capture_decode()
-    tok = logits.argmax(dim=1)
+    graph, gids, glogits = st.capture_decode(greedy=True)     # the graph feeds its arg-max tokens back into gids
+    gids.copy_(logits.argmax(dim=1))
     barrier()
     ev[0].record()
     for _ in range(steps):
-        gids.copy_(tok)
         graph.replay()
-        tok = glogits.argmax(dim=1)
     ev[1].record()
     barrier()
     decode_ms = max_over_ranks(ev[0].elapsed_time(ev[1]))
@@ -396,7 +394,7 @@ def measure_stack(eng, dev, world, rank, comm, barrier, max_over_ranks, layers=1
             "n_gpus": world, "tokens_per_s_decode": batch * steps / (decode_ms * 1e-3),
             "tokens_per_s_prefill": batch * prompt / (prefill_ms * 1e-3),
             "prefill_ms": prefill_ms, "decode_ms_per_step": decode_ms / steps, "logits_finite": finite,
-            "launch": "prefill eager, decode step replayed as one CUDA graph (all layers)",
+            "launch": "prefill eager, decode step replayed as one CUDA graph (all layers, the arg-max token fed back inside the graph)",
             "attention_only": {
                 "prefill_attention_ms_per_layer": attn_ms,
                 "prefill_attention_share_of_phase": attn_ms * layers / prefill_ms,

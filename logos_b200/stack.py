@@ -161,10 +161,11 @@ class AttentionStack:
         return logits
 
 
-    def capture_decode(self):
+    def capture_decode(self, greedy: bool = False):
         """Record one decode step (all layers) into a CUDA graph.  Returns (graph, ids, logits): fill `ids`
-        ([B] int64) in place, replay, read `logits`.  No library collective is captured: with several ranks the
-        gather inside the step is the engine's own peer exchange."""
+        ([B] int64) in place, replay, read `logits`.  With `greedy` the graph ends by writing the arg-max token of
+        every sequence back into `ids`, so a greedy loop is replay after replay with nothing between them.  No library
+        collective is captured: with several ranks the gather inside the step is the engine's own peer exchange."""
         ids = torch.zeros((self.batch,), dtype=torch.long, device=self.embed.device)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -178,6 +179,8 @@ class AttentionStack:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                     logits = self.decode(ids)
+                    if greedy:
+                        ids.copy_(logits.argmax(dim=1))
                 self.cache.lens.copy_(lens0)          # the warm-up step is taken back
                 self.q_prev.copy_(qp0)
         finally:

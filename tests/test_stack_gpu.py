@@ -130,3 +130,32 @@ def test_generate_loop_bookkeeping(engine):
     assert amps == sorted(amps, reverse=True)
     assert all(math.isclose(b.log_amplitude, -b.action / 0.7, rel_tol=1e-5, abs_tol=1e-6) for b in beams)
     assert len({tuple(b.tokens) for b in beams}) == 4
+
+
+def test_captured_decode_step_replays_the_eager_steps(engine):
+    """capture_decode: the whole step as one CUDA graph gives the eager step's logits, step after step; with
+    greedy=True the graph feeds its own arg-max tokens back and reproduces the eager greedy loop."""
+    w = make_weights(CFG, seed=9, std=0.3)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    ids = torch.randint(0, CFG.vocab_size, (3, 40), device="cuda", generator=g)
+    eager = AttentionStack(engine, CFG, w, batch=3)
+    first = eager.prefill(ids).argmax(dim=1)
+    tok, want_logits, want_tokens = first.clone(), [], []
+    for _ in range(5):
+        lg = eager.decode(tok)
+        tok = lg.argmax(dim=1)
+        want_logits.append(lg.clone())
+        want_tokens.append(tok.clone())
+    st = AttentionStack(engine, CFG, w, batch=3)
+    st.prefill(ids)
+    graph, gids, glogits = st.capture_decode(greedy=True)
+    try:
+        gids.copy_(first)
+        for k in range(5):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(glogits, want_logits[k])
+            assert torch.equal(gids, want_tokens[k])
+    finally:
+        graph.reset()
+        engine.set_option(L.OPT_WORKSPACE_LOCK, 0)
