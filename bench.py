@@ -729,10 +729,15 @@ def run_ours(args) -> None:
     dblock = torch.randn((4, B, Hl, DH), device=dev, generator=g).half()     # q | q_prev | k_new | v_new
     q, qp, kn, vn = dblock[0], dblock[1], dblock[2], dblock[3]
     lens = torch.full((B,), S_MAX, dtype=torch.int32, device=dev)
-    # the step's four host tensors in one pinned block, one after the other: the entry point sends them as one copy
-    hblock = dblock.cpu().pin_memory()
+    # the step's host tensors in one pinned block, one after the other (q | q_prev | k_new | v_new | len): the entry
+    # point sends them as one copy
+    n16 = 4 * B * Hl * DH * 2
+    hbuf = torch.empty(n16 + B * 4, dtype=torch.uint8).pin_memory()
+    hblock = hbuf[:n16].view(torch.float16).view(4, B, Hl, DH)
+    hblock.copy_(dblock.cpu())
     hq, hqp, hkn, hvn = hblock[0], hblock[1], hblock[2], hblock[3]
-    hlens = lens.cpu().pin_memory()
+    hlens = hbuf[n16:].view(torch.int32)
+    hlens.copy_(lens.cpu())
     hout = torch.empty((B, H, DH), dtype=torch.float32).pin_memory()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
 

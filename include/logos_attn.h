@@ -290,7 +290,7 @@ int logos_decode_step_int8_to(logos_ctx* ctx, const void* q, const void* q_prev,
  * FP32 result back to out_host; returns when out_host is complete.  The caches
  * and scales stay resident on the device (they are engine state, like HeadCache in
  * cuda/ModelGPU.cuh:42-49).  Staging memory comes from the workspace.  Host tensors that lie
- * one after the other in memory in the order q, q_prev, k_new, v_new are sent as one copy. */
+ * one after the other in memory in the order q, q_prev, k_new, v_new, len are sent as one copy. */
 int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* q_prev_host,
                                 const void* k_new_host, const void* v_new_host,
                                 int8_t* k_cache, int8_t* v_cache, const float* k_scale,

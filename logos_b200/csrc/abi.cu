@@ -653,40 +653,41 @@ int logos_decode_step_int8_host(logos_ctx* ctx, const void* q_host, const void* 
         if (len_host[b] < 1 || len_host[b] > S_max)
             return logos::fail(ctx, LOGOS_ERR_INVALID_ARG, "decode_step_host: len[%d]=%d outside [1,%d]", b,
                                len_host[b], S_max);
-    // staging layout behind the kernel workspace: q | q_prev | k_new | v_new (fp16), out (fp32), len (int32)
+    // staging layout behind the kernel workspace: q | q_prev | k_new | v_new (fp16), len (int32), out (fp32)
     char* base = (char*)ctx->workspace + ((kernel_ws + 255) & ~(size_t)255);
     __half* d_q = (__half*)base;
     __half* d_qp = d_q + vec;
     __half* d_k = d_qp + vec;
     __half* d_v = d_k + vec;
-    float* d_out = (float*)(d_v + vec);
-    int32_t* d_len = (int32_t*)(d_out + vec);
+    int32_t* d_len = (int32_t*)(d_v + vec);
+    float* d_out = (float*)((char*)d_len + (((size_t)B * sizeof(int32_t) + 15) & ~(size_t)15));
     cudaStream_t st = ctx->stream;
     const size_t hb = vec * sizeof(__half);
-    // Host tensors that lie one after the other (q | q_prev | k_new | v_new, the order of the staging area)
+    // Host tensors that lie one after the other (q | q_prev | k_new | v_new | len, the order of the staging area)
     // travel as one copy: each copy costs a few microseconds of issue and engine turnaround on top of its bytes.
     {
-        const char* src[4] = {(const char*)q_host, (const char*)q_prev_host, (const char*)k_new_host, (const char*)v_new_host};
-        char* dst[4] = {(char*)d_q, (char*)d_qp, (char*)d_k, (char*)d_v};
-        for (int i = 0; i < 4;) {
+        const char* src[5] = {(const char*)q_host, (const char*)q_prev_host, (const char*)k_new_host, (const char*)v_new_host,
+                              (const char*)len_host};
+        char* dst[5] = {(char*)d_q, (char*)d_qp, (char*)d_k, (char*)d_v, (char*)d_len};
+        const size_t bytes[5] = {hb, hb, hb, hb, sizeof(int32_t) * (size_t)B};
+        for (int i = 0; i < 5;) {
             if (!src[i]) { ++i; continue; }
             int j = i + 1;
-            while (j < 4 && src[j] == src[j - 1] + hb) ++j;
-            if (j - i > 1 &&
-                cudaMemcpyAsync(dst[i], src[i], hb * (size_t)(j - i), cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            size_t run = bytes[i];
+            while (j < 5 && src[j] == src[j - 1] + bytes[j - 1]) run += bytes[j++];
+            if (j - i > 1 && cudaMemcpyAsync(dst[i], src[i], run, cudaMemcpyHostToDevice, st) != cudaSuccess) {
                 // neighbours in address space but separate page-locked allocations: the runtime refuses a copy
                 // that spans them -- send them one by one
                 cudaGetLastError();
                 j = i;
             }
             if (j - i <= 1) {
-                LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(dst[i], src[i], hb, cudaMemcpyHostToDevice, st));
+                LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(dst[i], src[i], bytes[i], cudaMemcpyHostToDevice, st));
                 j = i + 1;
             }
             i = j;
         }
     }
-    LOGOS_CUDA_TRY(ctx, cudaMemcpyAsync(d_len, len_host, sizeof(int32_t) * B, cudaMemcpyHostToDevice, st));
     int rc = logos::kv_append(ctx, LOGOS_F16, d_k, d_v, k_cache, v_cache, k_scale, v_scale, d_len, B, H, S_max, DH, -1);
     if (rc != LOGOS_OK) return rc;
     rc = logos::decode_int8(ctx, d_q, q_prev_host ? d_qp : nullptr, k_cache, v_cache, k_scale, v_scale, d_len, B,

@@ -125,11 +125,12 @@ def test_full_size_benchmark_shape(engine):
     assert np.abs(a - b_).max() < 1e-5
 
 
-@pytest.mark.parametrize("pinned", [True, False, "one block"])
+@pytest.mark.parametrize("pinned", [True, False, "one block", "one block with the lengths"])
 def test_host_step_entry_point(engine, pinned):
     """logos_decode_step_int8_host == append + decode on device tensors, with page-locked host
     buffers (separate allocations, which may be neighbours in address space but must not be copied as one),
-    with pageable ones, and with the four tensors in one page-locked block (sent as one copy)."""
+    with pageable ones, with the four tensors in one page-locked block (sent as one copy), and with the lengths
+    directly behind them in that block."""
     B, H, S_max, DH = 4, 4, 512, 64
     lens0 = np.array([10, 100, 300, 511], np.int32)
     kq, vq, ks, vs = make_cache(B, H, S_max, lens0, 21)
@@ -137,15 +138,25 @@ def test_host_step_entry_point(engine, pinned):
     kc, vc, ksd, vsd = dev(kq), dev(vq), dev(ks), dev(vs)
     kc2, vc2 = kc.clone(), vc.clone()
     host = (lambda t: t.pin_memory()) if pinned else (lambda t: t)
+    lens = None
     if pinned == "one block":
         block = torch.randn(4, B, H, DH).half().pin_memory()
         q, qp, kn, vn = block[0], block[1], block[2], block[3]
+    elif pinned == "one block with the lengths":
+        n16 = 4 * B * H * DH * 2
+        buf = torch.empty(n16 + 4 * B, dtype=torch.uint8).pin_memory()
+        block = buf[:n16].view(torch.float16).view(4, B, H, DH)
+        block.copy_(torch.randn(4, B, H, DH).half())
+        q, qp, kn, vn = block[0], block[1], block[2], block[3]
+        lens = buf[n16:].view(torch.int32)
+        lens.copy_(torch.from_numpy(lens0 + 1))
     else:
         q = host(torch.randn(B, H, DH).half())
         qp = host(torch.randn(B, H, DH).half())
         kn = host(torch.randn(B, H, DH).half())
         vn = host(torch.randn(B, H, DH).half())
-    lens = host(torch.from_numpy(lens0 + 1))
+    if lens is None:
+        lens = host(torch.from_numpy(lens0 + 1))
     out = host(torch.full((B, H, DH), float("nan")))
     p = L.Params.make(0.125, True, 0, 0, 0.1, 0.05, 1.0, L.DIFFUSE_CAUSAL)
     engine.reserve(engine.decode_workspace_bytes(B, H, S_max, DH))
