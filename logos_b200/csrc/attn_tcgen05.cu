@@ -650,7 +650,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
             float mxr;
             {
                 float mc[8];                            // three-input maxima, eight independent chains
-                if (WIN && dead) {
+                if (WIN) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) mc[q] = -INFINITY;
 #pragma unroll
@@ -781,7 +781,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constan
                 store16(1, Pa);
                 store16(0, Pb);
             };
-            if (WIN && dead) all_chunks(SkipDead<true>{}); else all_chunks(SkipDead<false>{});
+            // one copy per instantiation: the loop lives on the instruction cache, and under a window nearly every
+            // tile has dead chunks
+            all_chunks(SkipDead<WIN>{});
             if (!ok) break;
             lsum2 = __fadd2_rn(lsum2, lsum2b);
             // a landmark's weight stands for V[j] + rho V[j-1]: it counts (1 + rho) times in the row sum
